@@ -1,0 +1,110 @@
+"""ctypes binding of ``libbsx.so``, the C-ABI CUDA library (``include/bsx.h``).
+
+The library is the only compute path of this package: there is no CPU or
+PyTorch fallback.  If the shared object is missing, :func:`lib` raises; if a call
+fails, :class:`BsxError` carries the library's status and message.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, 'libbsx.so')
+
+BSX_OK = 0
+BSX_ERR_INVALID_ARG = -1
+BSX_ERR_CUDA = -2
+BSX_ERR_INDEX_RANGE = -3
+BSX_ERR_WORKSPACE = -4
+BSX_ERR_UNSUPPORTED = -5
+BSX_ERR_TIMEOUT = -6
+
+SPK_BOOL8, SPK_F32, SPK_BITS32, SPK_LIST = 0, 1, 2, 3
+
+
+class BsxError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f'bsx call failed with status {status}: {message}')
+        self.status = status
+
+
+class BsxConn(C.Structure):
+    """Mirror of ``bsx_conn_t``."""
+    _fields_ = [
+        ('n_pre', C.c_int64),
+        ('n_post', C.c_int64),
+        ('conn_num', C.c_int64),
+        ('nnz', C.c_int64),
+        ('indices', C.c_void_p),
+        ('indptr', C.c_void_p),
+        ('indptr_is_64', C.c_int32),
+        ('hetero', C.c_int32),
+        ('weights', C.c_void_p),
+    ]
+
+
+_i64, _i32, _vp, _sz, _f32 = C.c_int64, C.c_int, C.c_void_p, C.c_size_t, C.c_float
+_connp = C.POINTER(BsxConn)
+
+# name -> (restype, argtypes); every symbol include/bsx.h declares
+SIGNATURES = {
+    'bsx_version': (_i32, []),
+    'bsx_last_error_string': (C.c_char_p, []),
+    'bsx_status_name': (C.c_char_p, [_i32]),
+    'bsx_device_count': (_i32, []),
+    'bsx_read_status': (_i32, [_vp, C.POINTER(C.c_int32), _vp]),
+    'bsx_host_fixed_num_indices': (_i64, [C.c_uint32, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
+    'bsx_validate_conn': (_i32, [_connp, _vp, _vp]),
+    'bsx_pack_spikes': (_i32, [_vp, _i32, _i64, _i64, _vp, _vp]),
+    'bsx_transpose_workspace_bytes': (_sz, [_i64, _i64, _i64]),
+    'bsx_transpose_build': (_i32, [_connp, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
+    'bsx_permute_f32': (_i32, [_vp, _vp, _i64, _vp, _vp]),
+    'bsx_event_vecmat_workspace_bytes': (_sz, [_i64, _i64]),
+    'bsx_event_vecmat': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp, _sz, _vp]),
+    'bsx_event_vecmat_tuned': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp, _sz, _i32, _i32, _vp]),
+    'bsx_float_vecmat': (_i32, [_connp, _vp, _i64, _vp, _i32, _vp, _sz, _vp]),
+    'bsx_event_matvec_workspace_bytes': (_sz, [_i64, _i64]),
+    'bsx_event_matvec': (_i32, [_connp, _vp, _i32, _i64, _vp, _vp, _sz, _vp]),
+    'bsx_event_matvec_tuned': (_i32, [_connp, _vp, _i32, _i64, _vp, _vp, _sz, _i32, _i32, _vp]),
+    'bsx_float_matvec': (_i32, [_connp, _vp, _i64, _vp, _vp]),
+    'bsx_vecmat_vjp': (_i32, [_connp, _vp, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
+    'bsx_dense_event_vecmat': (_i32, [_vp, _i32, _vp, _i64, _i64, _i64, _vp, _vp]),
+    'bsx_fill_f32': (_i32, [_vp, _i64, _f32, _vp]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library.  Raises if ``libbsx.so`` has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f'{LIB_PATH} is missing: build it with `python -m brainstate_b200.build` '
+                '(nvcc, sm_100a).  This package has no fallback implementation.')
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)      # AttributeError here = header/library mismatch
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(status: int) -> int:
+    """Raises :class:`BsxError` for a negative status; returns it otherwise."""
+    if status < 0:
+        raise BsxError(int(status), lib().bsx_last_error_string().decode())
+    return status
+
+
+def current_stream() -> int:
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t) -> int | None:
+    """Device address of a torch tensor (``None`` passes NULL)."""
+    return None if t is None else t.data_ptr()

@@ -1,0 +1,94 @@
+// Shared host/device helpers of the bsx library (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "bsx.h"
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
+#error "bsx is written for sm_100a (B200) only"
+#endif
+
+namespace bsx {
+
+// ---- host-side error plumbing (thread-local message, integer codes) --------
+void set_error(const char* fmt, ...);
+int fail(int status, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define BSX_CUDA(call)                                          \
+  do {                                                          \
+    cudaError_t bsx_e_ = (call);                                \
+    if (bsx_e_ != cudaSuccess) return ::bsx::cuda_fail(bsx_e_, #call); \
+  } while (0)
+
+#define BSX_LAUNCH_CHECK(name)                                  \
+  do {                                                          \
+    cudaError_t bsx_e_ = cudaGetLastError();                    \
+    if (bsx_e_ != cudaSuccess) return ::bsx::cuda_fail(bsx_e_, name); \
+  } while (0)
+
+// Validates a connectivity descriptor on the host (pointers, sizes, layout).
+int check_conn(const bsx_conn_t* c);
+// Number of SMs of the current device (148 on B200); <= 0 on failure.
+int sm_count();
+
+inline cudaStream_t as_stream(bsx_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- row addressing shared by the fixed-number and CSR layouts -------------
+struct RowMap {
+  const int32_t* p32;
+  const int64_t* p64;
+  int64_t K;
+  __device__ __forceinline__ void range(int64_t i, int64_t& s, int64_t& e) const {
+    if (p64) {
+      s = p64[i];
+      e = p64[i + 1];
+    } else if (p32) {
+      s = p32[i];
+      e = p32[i + 1];
+    } else {
+      s = i * K;
+      e = s + K;
+    }
+  }
+};
+
+inline RowMap make_rowmap(const bsx_conn_t* c) {
+  RowMap r;
+  r.p32 = (c->indptr && !c->indptr_is_64) ? static_cast<const int32_t*>(c->indptr) : nullptr;
+  r.p64 = (c->indptr && c->indptr_is_64) ? static_cast<const int64_t*>(c->indptr) : nullptr;
+  r.K = c->conn_num;
+  return r;
+}
+
+// Header of the active-row queue kept at the start of a vecmat workspace.
+struct QueueHeader {
+  int32_t count;     // number of queued entries
+  int32_t pad[3];    // keeps the entries 16-byte aligned
+};
+
+#ifdef __CUDACC__
+// ---- device helpers ---------------------------------------------------------
+__device__ __forceinline__ void red_add(float* addr, float v) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// 1 where the spike at flat position p is active, for the byte/float formats.
+template <int FORMAT>
+__device__ __forceinline__ bool spike_at(const void* spikes, int64_t p) {
+  if (FORMAT == BSX_SPK_BOOL8) return static_cast<const uint8_t*>(spikes)[p] != 0;
+  return static_cast<const float*>(spikes)[p] != 0.0f;
+}
+#endif
+
+}  // namespace bsx

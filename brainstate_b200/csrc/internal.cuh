@@ -1,0 +1,17 @@
+// Launchers shared between the translation units of the bsx library.
+#pragma once
+#include "common.cuh"
+
+namespace bsx {
+
+// Packs (batch, n) byte/float spikes into (batch, ceil(n/32)) words.
+int launch_pack(const void* spikes, int format, int64_t batch, int64_t n, uint32_t* bits, cudaStream_t st);
+
+// Clears hdr, queues the flat positions of all active spikes and, in the same
+// launch, zeroes zero_n floats at zero_ptr (may be NULL).
+int launch_compact(const void* spikes, int format, int64_t batch, int64_t n_pre, QueueHeader* hdr,
+                   uint32_t* entries, float* zero_ptr, int64_t zero_n, cudaStream_t st);
+
+int launch_zero(float* z, int64_t n, cudaStream_t st);
+
+}  // namespace bsx

@@ -1,0 +1,409 @@
+"""Event-driven sparse products on the GPU: the operator layer.
+
+This module plays the part ``brainevent`` plays under the reference's
+``brainstate/nn/_event_fixedprob.py``: container types for the connectivity
+(``FixedPostNumConn``, ``CSR``), the spike wrapper ``EventArray`` and the ``@``
+products between them, each differentiable (reverse and forward mode) and
+accepting leading batch dimensions.  All arithmetic is done by ``libbsx.so``
+through its C ABI on CUDA tensors; there is no other implementation.
+
+Reference call sites replaced (``brainstate/nn/_event_fixedprob.py``):
+``:176-181`` (``FixedPostNumConn``), ``:191-196`` (``CSR``), ``:204-205``
+(``with_data`` + ``x @ csr``), ``:251`` (``EventArray``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import BsxConn, check, lib, ptr
+
+__all__ = ['EventArray', 'FixedPostNumConn', 'CSR', 'event_vecmat', 'float_vecmat',
+           'event_matvec', 'float_matvec', 'pack_spikes', 'spike_format_of']
+
+
+def _require_cuda(t: torch.Tensor, what: str):
+    if not t.is_cuda:
+        raise RuntimeError(f'{what} must be a CUDA tensor: this package computes on the GPU only '
+                           '(no CPU fallback exists)')
+
+
+def spike_format_of(x: torch.Tensor) -> int:
+    """C-ABI spike format of a tensor by dtype (bool/uint8 -> BOOL8, float32 -> F32)."""
+    if x.dtype in (torch.bool, torch.uint8):
+        return _lib.SPK_BOOL8
+    if x.dtype == torch.float32:
+        return _lib.SPK_F32
+    raise TypeError(f'spikes must be bool, uint8 or float32, got {x.dtype}')
+
+
+class EventArray:
+    """Marks a tensor as a spike (event) vector: every nonzero entry is a unit
+    event in the forward product (``brainstate/nn/_event_linear.py:82-85``)."""
+
+    __slots__ = ('value',)
+
+    def __init__(self, value):
+        self.value = value.value if isinstance(value, EventArray) else value
+
+    @property
+    def shape(self):
+        return self.value.shape
+
+    def __matmul__(self, other):
+        if isinstance(other, _SparseConn):
+            return other._vecmat(self.value, event=True)
+        if isinstance(other, torch.Tensor):       # dense event product (EventLinear)
+            from .nn._event_linear import dense_event_matmul
+            return dense_event_matmul(self.value, other)
+        return NotImplemented
+
+
+class _Transposed:
+    """Postsynaptic-major copy of a connectivity (built once on the device)."""
+
+    def __init__(self, indptr, indices, perm, n_rows, n_cols):
+        self.indptr, self.indices, self.perm = indptr, indices, perm
+        self.n_rows, self.n_cols = n_rows, n_cols   # n_rows = n_post of the original
+
+
+class _SparseConn:
+    """Shared behaviour of the two out-degree layouts."""
+
+    def __init__(self, data, indices: torch.Tensor, indptr: Optional[torch.Tensor], shape):
+        _require_cuda(indices, 'indices')
+        if indices.dtype != torch.int32:
+            raise TypeError('indices must be int32')
+        self.shape = (int(shape[0]), int(shape[1]))
+        self.indices = indices.contiguous()
+        self.indptr = None
+        if indptr is not None:
+            _require_cuda(indptr, 'indptr')
+            if indptr.dtype not in (torch.int32, torch.int64):
+                raise TypeError('indptr must be int32 or int64')
+            if indptr.numel() != self.shape[0] + 1:
+                raise ValueError('indptr must have n_pre + 1 entries')
+            self.indptr = indptr.contiguous()
+        self._transposed: Optional[_Transposed] = None
+        self._set_data(data)
+
+    # -- data ---------------------------------------------------------------
+    def _set_data(self, data):
+        if not isinstance(data, torch.Tensor):
+            data = torch.as_tensor(np.asarray(data, dtype=np.float32), device=self.indices.device)
+        _require_cuda(data, 'weights')
+        if data.dtype != torch.float32:
+            data = data.to(torch.float32)
+        if data.dim() > 0 and data.numel() == self.indices.numel() and data.numel() > 0 \
+                and tuple(data.shape) == tuple(self.indices.shape):
+            self.hetero = True
+        elif data.numel() == 1:
+            self.hetero = False
+        else:
+            raise ValueError(f'weights of shape {tuple(data.shape)} match neither a scalar nor the '
+                             f'indices {tuple(self.indices.shape)}')
+        self.data = data
+
+    def with_data(self, data):
+        """A view of the same connectivity with other weights
+        (``brainevent`` ``with_data``, used at ``_event_fixedprob.py:204``)."""
+        new = object.__new__(type(self))
+        new.__dict__.update(self.__dict__)
+        new._set_data(data)
+        return new
+
+    @property
+    def nnz(self) -> int:
+        return self.indices.numel()
+
+    @property
+    def conn_num(self) -> int:
+        return 0 if self.indptr is not None else (self.indices.shape[-1] if self.indices.dim() == 2 else 0)
+
+    def _struct(self, weights: Optional[torch.Tensor] = None, hetero: Optional[bool] = None) -> BsxConn:
+        w = self.data if weights is None else weights
+        h = self.hetero if hetero is None else hetero
+        wc = w if w.is_contiguous() else w.contiguous()
+        s = BsxConn()
+        s.n_pre, s.n_post = self.shape
+        s.conn_num = self.conn_num
+        s.nnz = self.nnz
+        s.indices = self.indices.data_ptr() if self.nnz else None
+        s.indptr = None if self.indptr is None else self.indptr.data_ptr()
+        s.indptr_is_64 = int(self.indptr is not None and self.indptr.dtype == torch.int64)
+        s.hetero = int(h)
+        s.weights = wc.data_ptr()
+        s._keep = (wc,)            # keeps a contiguous copy alive for the call
+        return s
+
+    # -- validation / derived layouts ------------------------------------------
+    def validate(self):
+        """Range-checks the indices on the device; raises ``ValueError`` on a bad
+        layout.  (The reference has no such check: a malformed layout aborts the
+        process inside brainevent, ``_event_fixedprob.py:124-134``.)"""
+        status = torch.zeros(1, dtype=torch.int32, device=self.indices.device)
+        st = self._struct()
+        check(lib().bsx_validate_conn(C.byref(st), ptr(status), _lib.current_stream()))
+        host = C.c_int32(0)
+        check(lib().bsx_read_status(ptr(status), C.byref(host), _lib.current_stream()))
+        if host.value != 0:
+            raise ValueError('connectivity indices out of range or malformed indptr '
+                             f'({lib().bsx_status_name(host.value).decode()})')
+        return self
+
+    def transposed(self) -> _Transposed:
+        """Builds (once) and returns the postsynaptic-major copy."""
+        if self._transposed is None:
+            n_pre, n_post = self.shape
+            dev = self.indices.device
+            nnz = self.nnz
+            t_indptr = torch.empty(n_post + 1, dtype=torch.int64, device=dev)
+            t_indices = torch.empty(nnz, dtype=torch.int32, device=dev)
+            t_perm = torch.empty(nnz, dtype=torch.int32, device=dev)
+            ws_bytes = lib().bsx_transpose_workspace_bytes(n_pre, n_post, nnz)
+            ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+            st = self._struct()
+            check(lib().bsx_transpose_build(C.byref(st), nnz, ptr(t_indptr), ptr(t_indices), ptr(t_perm),
+                                            ptr(ws), ws_bytes, _lib.current_stream()))
+            self._transposed = _Transposed(t_indptr, t_indices, t_perm, n_post, n_pre)
+        return self._transposed
+
+    def _transposed_struct(self, weights: torch.Tensor):
+        """``bsx_conn_t`` of the transposed copy with the given (original-order) weights."""
+        t = self.transposed()
+        if self.hetero:
+            wt = torch.empty(self.nnz, dtype=torch.float32, device=weights.device)
+            wsrc = weights.contiguous()
+            check(lib().bsx_permute_f32(ptr(wsrc), ptr(t.perm), self.nnz, ptr(wt), _lib.current_stream()))
+        else:
+            wt = weights.contiguous()
+        s = BsxConn()
+        s.n_pre, s.n_post = t.n_rows, t.n_cols
+        s.conn_num = 0
+        s.nnz = self.nnz
+        s.indices = t.indices.data_ptr() if self.nnz else None
+        s.indptr = t.indptr.data_ptr()
+        s.indptr_is_64 = 1
+        s.hetero = int(self.hetero)
+        s.weights = wt.data_ptr()
+        s._keep = (wt,)
+        return s
+
+    # -- products ------------------------------------------------------------------
+    def _vecmat(self, x, event: bool, method: str = 'scatter'):
+        return _VecMat.apply(x, self.data, self, event, method)
+
+    def __rmatmul__(self, x):
+        if isinstance(x, EventArray):
+            return self._vecmat(x.value, event=True)
+        if isinstance(x, torch.Tensor):
+            return self._vecmat(x, event=False)
+        return NotImplemented
+
+    def __matmul__(self, v):
+        if isinstance(v, EventArray):
+            return event_matvec(self, v.value)
+        if isinstance(v, torch.Tensor):
+            return float_matvec(self, v)
+        return NotImplemented
+
+
+class FixedPostNumConn(_SparseConn):
+    """``(weight, indices)`` with a fixed number of targets per presynaptic row
+    (``brainevent.FixedPostNumConn``, ``_event_fixedprob.py:176-181``)."""
+
+    def __init__(self, data_indices, shape):
+        data, indices = data_indices
+        if indices.dim() != 2 or indices.shape[0] != shape[0]:
+            raise ValueError('indices must have shape (n_pre, conn_num)')
+        super().__init__(data, indices, None, shape)
+
+
+class CSR(_SparseConn):
+    """``(weight, indices, indptr)`` compressed sparse rows
+    (``brainevent.CSR``, ``_event_fixedprob.py:191-196``)."""
+
+    def __init__(self, data_indices_indptr, shape):
+        data, indices, indptr = data_indices_indptr
+        if indices.dim() != 1:
+            raise ValueError('CSR indices must be one-dimensional')
+        super().__init__(data, indices, indptr, shape)
+
+
+# ----------------------------------------------------------------------------
+# raw calls (no autograd)
+# ----------------------------------------------------------------------------
+
+def _flatten_batch(x: torch.Tensor, n: int):
+    if x.shape[-1] != n:
+        raise ValueError(f'last dimension is {x.shape[-1]}, expected {n}')
+    lead = tuple(x.shape[:-1])
+    xb = x.reshape(-1, n)
+    if not xb.is_contiguous():
+        xb = xb.contiguous()
+    return xb, lead
+
+
+def _raw_vecmat(conn: _SparseConn, x: torch.Tensor, weights: torch.Tensor, event: bool,
+                method: str = 'scatter', out: Optional[torch.Tensor] = None, accumulate: bool = False):
+    _require_cuda(x, 'input')
+    n_pre, n_post = conn.shape
+    xb, lead = _flatten_batch(x, n_pre)
+    batch = xb.shape[0]
+    if out is None:
+        out = torch.empty((batch, n_post), dtype=torch.float32, device=x.device)
+        accumulate = False
+    stream = _lib.current_stream()
+    if event and method == 'gather':
+        # deterministic post-centric form: event matvec over the transposed copy
+        st = conn._transposed_struct(weights)
+        fmt = spike_format_of(xb)
+        ws_bytes = lib().bsx_event_matvec_workspace_bytes(batch, n_pre)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
+        if accumulate:
+            tmp = torch.empty_like(out)
+            check(lib().bsx_event_matvec(C.byref(st), ptr(xb), fmt, batch, ptr(tmp), ptr(ws), ws_bytes, stream))
+            out += tmp
+        else:
+            check(lib().bsx_event_matvec(C.byref(st), ptr(xb), fmt, batch, ptr(out), ptr(ws), ws_bytes, stream))
+        return out.reshape(lead + (n_post,))
+    if method not in ('scatter', 'gather'):
+        raise ValueError(f"method must be 'scatter' or 'gather', got {method!r}")
+    st = conn._struct(weights)
+    ws_bytes = lib().bsx_event_vecmat_workspace_bytes(batch, n_pre)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
+    if event:
+        fmt = spike_format_of(xb)
+        check(lib().bsx_event_vecmat(C.byref(st), ptr(xb), fmt, batch, ptr(out), int(accumulate),
+                                     ptr(ws), ws_bytes, stream))
+    else:
+        if xb.dtype != torch.float32:
+            xb = xb.to(torch.float32)
+        check(lib().bsx_float_vecmat(C.byref(st), ptr(xb), batch, ptr(out), int(accumulate),
+                                     ptr(ws), ws_bytes, stream))
+    return out.reshape(lead + (n_post,))
+
+
+def event_vecmat(conn: _SparseConn, spk: torch.Tensor, method: str = 'scatter'):
+    """``EventArray(spk) @ conn`` (differentiable when ``spk`` is float)."""
+    return conn._vecmat(spk, event=True, method=method)
+
+
+def float_vecmat(conn: _SparseConn, x: torch.Tensor):
+    """``x @ conn`` for float ``x``."""
+    return conn._vecmat(x, event=False)
+
+
+def event_matvec(conn: _SparseConn, spk: torch.Tensor, bits: bool = False):
+    """``conn @ EventArray(spk)``: ``y[i] = sum_k w[i,k] [spk[idx[i,k]] != 0]``.
+    ``bits=True`` takes packed uint32/int32 words (``(…, ceil(n_post/32))``)."""
+    _require_cuda(spk, 'spikes')
+    n_pre, n_post = conn.shape
+    if bits:
+        words = (n_post + 31) // 32
+        xb, lead = _flatten_batch(spk, words)
+        fmt = _lib.SPK_BITS32
+    else:
+        xb, lead = _flatten_batch(spk, n_post)
+        fmt = spike_format_of(xb)
+    batch = xb.shape[0]
+    out = torch.empty((batch, n_pre), dtype=torch.float32, device=spk.device)
+    st = conn._struct()
+    ws_bytes = lib().bsx_event_matvec_workspace_bytes(batch, n_post)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=spk.device)
+    check(lib().bsx_event_matvec(C.byref(st), ptr(xb), fmt, batch, ptr(out), ptr(ws), ws_bytes,
+                                 _lib.current_stream()))
+    return out.reshape(lead + (n_pre,))
+
+
+def float_matvec(conn: _SparseConn, v: torch.Tensor, weights: Optional[torch.Tensor] = None):
+    """``conn @ v`` for float ``v``."""
+    _require_cuda(v, 'v')
+    n_pre, n_post = conn.shape
+    vb, lead = _flatten_batch(v.to(torch.float32), n_post)
+    out = torch.empty((vb.shape[0], n_pre), dtype=torch.float32, device=v.device)
+    st = conn._struct(weights)
+    check(lib().bsx_float_matvec(C.byref(st), ptr(vb), vb.shape[0], ptr(out), _lib.current_stream()))
+    return out.reshape(lead + (n_pre,))
+
+
+def pack_spikes(spk: torch.Tensor) -> torch.Tensor:
+    """Packs ``(…, n)`` spikes into ``(…, ceil(n/32))`` int32 words (bit ``i % 32`` of word ``i // 32``)."""
+    _require_cuda(spk, 'spikes')
+    n = spk.shape[-1]
+    xb, lead = _flatten_batch(spk, n)
+    words = (n + 31) // 32
+    out = torch.empty((xb.shape[0], words), dtype=torch.int32, device=spk.device)
+    check(lib().bsx_pack_spikes(ptr(xb), spike_format_of(xb), xb.shape[0], n, ptr(out), _lib.current_stream()))
+    return out.reshape(lead + (words,))
+
+
+def _raw_vjp(conn: _SparseConn, x: torch.Tensor, weights: torch.Tensor, ct: torch.Tensor, event: bool,
+             need_dx: bool, need_dw: bool):
+    n_pre, n_post = conn.shape
+    xb, lead = _flatten_batch(x, n_pre)
+    ctb, _ = _flatten_batch(ct.to(torch.float32), n_post)
+    batch = xb.shape[0]
+    if xb.dtype not in (torch.bool, torch.uint8, torch.float32):
+        xb = xb.to(torch.float32)
+    dx = torch.empty((batch, n_pre), dtype=torch.float32, device=ct.device) if need_dx else None
+    dw = None
+    if need_dw:
+        dw = torch.empty(conn.indices.shape if conn.hetero else (1,), dtype=torch.float32, device=ct.device)
+    st = conn._struct(weights)
+    check(lib().bsx_vecmat_vjp(C.byref(st), ptr(xb), spike_format_of(xb), int(event), ptr(ctb), batch,
+                               ptr(dx), ptr(dw), _lib.current_stream()))
+    if dx is not None:
+        dx = dx.reshape(lead + (n_pre,))
+    if dw is not None and not conn.hetero:
+        dw = dw.reshape(weights.shape)
+    return dx, dw
+
+
+class _VecMat(torch.autograd.Function):
+    """``y = x @ W`` with the reverse- and forward-mode rules the reference's tests
+    pin (``brainstate/nn/_event_fixedprob_test.py:56-126``).
+
+    ``dx = ct @ W^T`` is dense also for an event input (the gradient flows through
+    the value, ``_event_linear.py:84-91``); ``dw`` uses the event indicator for the
+    event product and the value for the float product.
+    """
+
+    @staticmethod
+    def forward(x, weights, conn, event, method):
+        return _raw_vecmat(conn, x, weights, event, method)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        x, weights, conn, event, method = inputs
+        ctx.conn, ctx.event = conn, event
+        ctx.save_for_backward(x, weights)
+        ctx.save_for_forward(x, weights)
+        ctx.x_differentiable = x.dtype.is_floating_point
+
+    @staticmethod
+    def backward(ctx, ct):
+        x, weights = ctx.saved_tensors
+        need_dx = ctx.needs_input_grad[0] and ctx.x_differentiable
+        need_dw = ctx.needs_input_grad[1]
+        dx, dw = _raw_vjp(ctx.conn, x, weights, ct.contiguous(), ctx.event, need_dx, need_dw)
+        if dx is not None and dx.dtype != x.dtype:
+            dx = dx.to(x.dtype)
+        return dx, dw, None, None, None
+
+    @staticmethod
+    def jvp(ctx, x_dot, w_dot, *_):
+        x, weights = ctx.saved_tensors
+        conn = ctx.conn
+        out = None
+        if x_dot is not None:
+            out = _raw_vecmat(conn, x_dot.to(torch.float32), weights, event=False)
+        if w_dot is not None:
+            wd = w_dot.to(torch.float32)
+            term = _raw_vecmat(conn.with_data(wd), x, wd, event=ctx.event)
+            out = term if out is None else out + term
+        return out

@@ -1,0 +1,211 @@
+/*
+ * bsx — event-driven synaptic propagation on NVIDIA B200 (sm_100a), C ABI.
+ *
+ * This is the boundary a binding of brainstate's event-connection layers binds
+ * to.  In the reference, brainstate/nn/_event_fixedprob.py builds the
+ * connectivity and hands every product to the third-party package brainevent
+ * (`x @ brainevent.FixedPostNumConn(...)`, `x @ brainevent.CSR(...)`); each entry
+ * point below replaces one of those dispatches, cited beside it by the
+ * reference file:line that reaches it.
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer unless its name starts with `host_`.
+ *    The caller owns every buffer, workspace included; nothing here allocates.
+ *  - All work is enqueued on the caller's stream (a cudaStream_t passed as
+ *    void*); functions return as soon as the work is enqueued.
+ *  - Return value: BSX_OK or a negative bsx_status_t.  Nothing is thrown across
+ *    the boundary; bsx_last_error_string() describes the calling thread's last
+ *    failure.  Kernel-side checks (index range, queue overflow) are reported
+ *    through a caller-provided device status word, read with bsx_read_status().
+ *  - There is no CPU implementation behind these symbols.  Without a CUDA
+ *    device every compute entry point returns BSX_ERR_CUDA.
+ *  - Re-entrant: no mutable global state except the thread-local error string.
+ */
+#ifndef BSX_H_
+#define BSX_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BSX_VERSION 100
+
+typedef void* bsx_stream_t; /* cudaStream_t */
+
+typedef enum {
+  BSX_OK = 0,
+  BSX_ERR_INVALID_ARG = -1, /* null pointer, negative size, inconsistent layout */
+  BSX_ERR_CUDA = -2,        /* a CUDA runtime call failed (no device, launch error) */
+  BSX_ERR_INDEX_RANGE = -3, /* a connectivity index lies outside [0, n_post) */
+  BSX_ERR_WORKSPACE = -4,   /* workspace pointer null, misaligned or too small */
+  BSX_ERR_UNSUPPORTED = -5, /* a size beyond what the kernels address */
+  BSX_ERR_TIMEOUT = -6      /* a bounded device-side wait ran out */
+} bsx_status_t;
+
+/* How a spike vector is stored. */
+typedef enum {
+  BSX_SPK_BOOL8 = 0,  /* one byte per neuron, nonzero = spike (jax bool) */
+  BSX_SPK_F32 = 1,    /* float32, nonzero = unit event (brainevent.EventArray of a float array,
+                         brainstate/nn/_event_linear.py:82-85) */
+  BSX_SPK_BITS32 = 2, /* packed: bit (i % 32) of uint32 word (i / 32); rows padded to whole words */
+  BSX_SPK_LIST = 3    /* compacted active indices: int32 count at list[0], then the indices */
+} bsx_spike_format_t;
+
+/*
+ * Sparse connectivity with out-degree layout, the data of
+ * brainevent.FixedPostNumConn((weight, indices), shape=(n_pre, n_post))
+ * (brainstate/nn/_event_fixedprob.py:176-181) when indptr == NULL, and of
+ * brainevent.CSR((weight, indices, indptr), shape=...) (:191-196) otherwise.
+ */
+typedef struct bsx_conn {
+  int64_t n_pre;          /* rows */
+  int64_t n_post;         /* columns */
+  int64_t conn_num;       /* K: entries per row when indptr == NULL */
+  int64_t nnz;            /* stored entries: n_pre*K, or indptr[n_pre] */
+  const int32_t* indices; /* (n_pre*K) row-major, or (nnz) */
+  const void* indptr;     /* NULL, or (n_pre+1) row offsets */
+  int32_t indptr_is_64;   /* 0: int32 offsets (the reference's dtype), 1: int64 */
+  int32_t hetero;         /* 0: weights points at ONE float; 1: one float per index */
+  const float* weights;
+} bsx_conn_t;
+
+/* ---- diagnostics ------------------------------------------------------- */
+int bsx_version(void);
+const char* bsx_last_error_string(void);
+const char* bsx_status_name(int status);
+/* Number of CUDA devices visible, or 0 (never fails). */
+int bsx_device_count(void);
+/* Copies the device status word to *host_status after synchronising `stream`.
+ * The word is 0 or a bsx_status_t written by a kernel. */
+int bsx_read_status(const int32_t* status_word, int32_t* host_status, bsx_stream_t stream);
+
+/* ---- connectivity generation (host) ------------------------------------ */
+/*
+ * Replaces `rng.randint(0, n_post, size=(n_pre, conn_num))` + the int32 cast of
+ * brainstate/nn/_event_fixedprob.py:165-171, bit for bit (MT19937, masked
+ * rejection), without the int64 intermediate.  Rows [row_begin, row_end) of the
+ * matrix are written to host_out; entries of the other rows are drawn and
+ * dropped, so every rank of a sharded job can replay the one stream.
+ * If col_begin < col_end only targets inside [col_begin, col_end) are kept
+ * (stored minus col_begin) and host_row_counts[row - row_begin] receives how
+ * many each row kept (a CSR block for one postsynaptic shard); host_out then
+ * needs room for (row_end-row_begin)*conn_num entries in the worst case.
+ * Returns the number of entries written, or a negative status.
+ */
+int64_t bsx_host_fixed_num_indices(uint32_t seed, int64_t n_pre, int64_t n_post, int64_t conn_num,
+                                   int64_t row_begin, int64_t row_end,
+                                   int64_t col_begin, int64_t col_end,
+                                   int32_t* host_out, int32_t* host_row_counts);
+
+/* ---- construction-time checks and derived layouts ---------------------- */
+/* Writes BSX_ERR_INDEX_RANGE to *status_word if any index is outside [0, n_post)
+ * or indptr is not non-decreasing; leaves it untouched otherwise.  The reference
+ * performs no such check (a malformed layout aborts inside brainevent,
+ * brainstate/nn/_event_fixedprob.py:124-134). */
+int bsx_validate_conn(const bsx_conn_t* conn, int32_t* status_word, bsx_stream_t stream);
+
+/* Spike packing: any format except LIST -> BITS32 words ((n+31)/32 per batch row). */
+int bsx_pack_spikes(const void* spikes, int spike_format, int64_t batch, int64_t n,
+                    uint32_t* bits, bsx_stream_t stream);
+
+/*
+ * Transposed (postsynaptic-major) copy of a connectivity: for every column j the
+ * source rows that target it, in ascending (row, k) order.
+ *   t_indptr  (n_post+1) int64   row offsets of the transposed matrix
+ *   t_indices (nnz)      int32   presynaptic row of each entry
+ *   t_perm    (nnz)      int32   position of the entry in the original arrays
+ *                                (gathers weights after `with_data`,
+ *                                 brainstate/nn/_event_fixedprob.py:204)
+ * Requires nnz < 2^31.  The transposed matrix, read as a bsx_conn_t with
+ * n_pre/n_post swapped, turns bsx_event_matvec into the deterministic
+ * post-centric form of the forward product.
+ */
+size_t bsx_transpose_workspace_bytes(int64_t n_pre, int64_t n_post, int64_t nnz);
+int bsx_transpose_build(const bsx_conn_t* conn, int64_t nnz, int64_t* t_indptr, int32_t* t_indices,
+                        int32_t* t_perm, void* workspace, size_t workspace_bytes,
+                        bsx_stream_t stream);
+/* dst[p] = src[perm[p]] — weights of the transposed copy. */
+int bsx_permute_f32(const float* src, const int32_t* perm, int64_t n, float* dst, bsx_stream_t stream);
+
+/* ---- forward products -------------------------------------------------- */
+/*
+ * y = EventArray(spk) @ conn            brainstate/nn/_event_fixedprob.py:249-252 -> :204-205
+ *   y[b, idx[i,k]] += w[i,k]  for every i with spk[b,i] != 0   (pre-centric scatter)
+ * spikes: (batch, n_pre) in `spike_format`; out: (batch, n_post) float32.
+ * accumulate == 0 zeroes `out` first.  Workspace: bsx_event_vecmat_workspace_bytes.
+ * Duplicate targets accumulate (brainstate/nn/_event_fixedprob_test.py:256-259).
+ * Summation order of heterogeneous weights is not fixed between runs (atomic adds).
+ */
+size_t bsx_event_vecmat_workspace_bytes(int64_t batch, int64_t n_pre);
+int bsx_event_vecmat(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
+                     float* out, int accumulate, void* workspace, size_t workspace_bytes,
+                     bsx_stream_t stream);
+/* Same, with explicit launch geometry for tuning (0 = default): entries per
+ * work item of a fixed-number row, and resident blocks per SM. */
+int bsx_event_vecmat_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
+                           float* out, int accumulate, void* workspace, size_t workspace_bytes,
+                           int chunk, int blocks_per_sm, bsx_stream_t stream);
+
+/*
+ * y = x @ conn for float x               brainstate/nn/_event_fixedprob.py:202-205
+ *   y[b, idx[i,k]] += x[b,i] * w[i,k]   (rows with x == 0 are skipped)
+ * Also the two terms of the forward-mode rule (_event_fixedprob_test.py:90-126).
+ */
+int bsx_float_vecmat(const bsx_conn_t* conn, const float* x, int64_t batch, float* out,
+                     int accumulate, void* workspace, size_t workspace_bytes, bsx_stream_t stream);
+
+/*
+ * y = conn @ EventArray(s): y[b,i] = sum_k w[i,k] * [s[b, idx[i,k]] != 0]
+ * (the "W @ spike" product; deterministic gather, one warp per row, spike
+ * bitmask staged in shared memory).  spikes: (batch, n_post); out: (batch, n_pre).
+ * Workspace holds the packed spike words when the input is not BITS32 already.
+ */
+size_t bsx_event_matvec_workspace_bytes(int64_t batch, int64_t n_post);
+int bsx_event_matvec(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
+                     float* out, void* workspace, size_t workspace_bytes, bsx_stream_t stream);
+/* Same, with explicit launch geometry for tuning (0 = default).  mask_mode: 1 spike
+ * words staged in shared memory by a bulk-async (TMA) copy, 2 staged by ordinary
+ * loads, 3 read from global memory. */
+int bsx_event_matvec_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
+                           float* out, void* workspace, size_t workspace_bytes, int blocks_per_sm,
+                           int mask_mode, bsx_stream_t stream);
+
+/*
+ * y = conn @ v for float v: y[b,i] = sum_k w[i,k] * v[b, idx[i,k]].
+ * This is the input cotangent of the vecmat (transpose product used by jax.grad,
+ * brainstate/nn/_event_fixedprob_test.py:56-88).
+ */
+int bsx_float_matvec(const bsx_conn_t* conn, const float* v, int64_t batch, float* out,
+                     bsx_stream_t stream);
+
+/*
+ * y = EventArray(spk) @ W for a dense row-major W (n_pre, n_post)
+ *                                          brainstate/nn/_event_linear.py:99-100
+ *   y[b, :] = sum over i with spk[b,i] != 0 of W[i, :]   (ascending i, no atomics)
+ */
+int bsx_dense_event_vecmat(const void* spikes, int spike_format, const float* weight, int64_t batch,
+                           int64_t n_pre, int64_t n_post, float* out, bsx_stream_t stream);
+
+/* ---- reverse-mode products --------------------------------------------- */
+/*
+ * Cotangents of y = x @ conn for output cotangent ct (batch, n_post), one pass
+ * over the indices (brainstate/nn/_event_fixedprob_test.py:56-88):
+ *   dx[b,i]  = sum_k w[i,k] ct[b, idx[i,k]]                     (dx may be NULL)
+ *   hetero:  dw[i,k] = sum_b a[b,i] ct[b, idx[i,k]]             (dw may be NULL)
+ *   homo:    dw[0]   = sum_b sum_i a[b,i] sum_k ct[b, idx[i,k]]
+ * a = x (x_format == BSX_SPK_F32 and event == 0) or the event indicator [x != 0].
+ * dw is overwritten.  x: (batch, n_pre) in x_format (BOOL8 or F32).
+ */
+int bsx_vecmat_vjp(const bsx_conn_t* conn, const void* x, int x_format, int event,
+                   const float* ct, int64_t batch, float* dx, float* dw, bsx_stream_t stream);
+
+/* ---- small utilities ---------------------------------------------------- */
+int bsx_fill_f32(float* dst, int64_t n, float value, bsx_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BSX_H_ */
