@@ -1,0 +1,449 @@
+#!/usr/bin/env python
+"""Benchmark of the event-driven synaptic propagation path on B200.
+
+Workload (the standalone event-matvec microbenchmark): a 65 536 x 65 536 sparse
+matrix with fixed-probability connectivity p = 0.01 (655 int32 targets per row,
+seed 200), heterogeneous float32 weights ~ N(0.1, 0.01) (seed 201), and T
+distinct Bernoulli(1 %) spike vectors (seed 211).  One step = one pass of the hot
+path over that batch: the forward product ``spike @ W`` of all T vectors (one
+batched scatter launch) and the event matvec ``W @ spike`` of each vector (T
+gather launches).  ``value`` = synaptic events per second = (events of both
+products over the batch) / time, with everything resident in HBM.  ``e2e`` is the
+same pass through the public layer API starting from pinned host spikes and
+ending with the results back in host memory.  Data are synthetic, generated from
+the seeds above; the matrix (343 MB) is larger than the 126 MB L2.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--vectors T] [--cases]
+
+With N > 1 (torchrun, one rank per GPU) every rank runs the same pass on its own
+T spike vectors against its own replica of the matrix: the batch of spike vectors
+is data-parallel, no collective is on the data path (weak scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_NEURONS = 65536
+PROB = 0.01
+RATE = 0.01
+SEED_CONN, SEED_W, SEED_SPK = 200, 201, 211
+
+
+# ----------------------------------------------------------------------------
+# workload
+# ----------------------------------------------------------------------------
+
+def build_workload(vectors, rank=0, rate=RATE, seed_spk=SEED_SPK):
+    from brainstate_b200.nn import fixed_num_indices
+    n = N_NEURONS
+    K = int(n * PROB)
+    idx = fixed_num_indices(SEED_CONN, n, n, K)
+    w = np.random.RandomState(SEED_W).normal(0.1, 0.01, (n, K)).astype(np.float32)
+    spk = np.random.RandomState(seed_spk + 1000 * rank).random_sample((vectors, n)) < rate
+    return n, K, idx, w, spk
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))['hbm_gbs']), 'measured'
+        except Exception:
+            pass
+    return 6650.0, 'fallback'
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+             'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+             'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ['nvidia-smi', f'--query-gpu={self.QUERY}', '--format=csv,noheader,nounits', '-lms', '100',
+                 '-i', str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(',')]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith('active'):
+                    reasons.add(name)
+        if not sm:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['no samples']}
+        return {'sm_mhz': float(np.median(sm)), 'sm_max_mhz': float(max(smax)), 'reasons': sorted(reasons),
+                'samples': len(sm)}
+
+
+# ----------------------------------------------------------------------------
+# CPU baseline (oracle port), bounded sample
+# ----------------------------------------------------------------------------
+
+def cpu_pass(co, idx, w, spk_sample):
+    """One pass of the same hot path on the host: both products for every sampled vector."""
+    n = idx.shape[0]
+    co.event_vecmat_u8(spk_sample, idx, w, n)
+    co.event_matvec_u8(spk_sample, idx, w, n)
+
+
+def cpu_baseline(idx, w, spk, budget_s=12.0, sample_vectors=8):
+    from oracle import c_oracle as co
+    co.build()
+    K = idx.shape[1]
+    sample = np.ascontiguousarray(spk[:sample_vectors]).astype(np.uint8)
+    events = 2 * int(sample.sum()) * K
+    cpu_pass(co, idx, w, sample)                       # warm-up (page-in, thread start)
+    passes, t0 = 0, time.perf_counter()
+    while True:
+        cpu_pass(co, idx, w, sample)
+        passes += 1
+        el = time.perf_counter() - t0
+        if el >= budget_s and passes >= 2:
+            break
+    return {'value': events * passes / el, 'unit': 'synaptic events/s', 'cores': co.num_threads(),
+            'kind': 'port',
+            'sample': f'{passes} passes over {sample.shape[0]} spike vectors (both products each), '
+                      f'{el:.1f} s, C/OpenMP restatement of the reference CPU path'}, events, passes, el
+
+
+def run_reference_arm(args):
+    """``--impl reference``: the reference's CPU implementation of the path.  The
+    reference's own kernels live in the un-vendored package brainevent, which is not
+    installed and cannot be (no network), so the timed code is the C/OpenMP
+    restatement under oracle/ (kind "port"), on all host threads."""
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return 0
+    n, K, idx, w, spk = build_workload(max(args.vectors, 8))
+    from oracle import c_oracle as co
+    co.build()
+    sample = np.ascontiguousarray(spk[:8]).astype(np.uint8)
+    events = 2 * int(sample.sum()) * K
+    for _ in range(max(args.warmup, 1)):
+        cpu_pass(co, idx, w, sample)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_pass(co, idx, w, sample)
+    el = time.perf_counter() - t0
+    value = events * args.steps / el
+    unit = 'synaptic events/s'
+    line = {
+        'impl': 'reference', 'metric': 'synaptic events/s (event matvec microbenchmark, both products)',
+        'value': value, 'unit': unit, 'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup,
+        'ms_per_step': 1e3 * el / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+        'dtype': 'f32', 'data': 'synthetic',
+        'config': workload_config(8, 'host memory (CPU run)'),
+        'cpu_baseline': {'value': value, 'unit': unit, 'cores': co.num_threads(), 'kind': 'port',
+                         'sample': '8 spike vectors per step, both products; brainevent (the reference\'s kernel '
+                                   'package) is not installable here, so the C/OpenMP restatement is timed'},
+        'e2e': {'value': value, 'unit': unit, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def workload_config(vectors, l2_note):
+    return {'workload': 'standalone event matvec microbenchmark: n_pre=n_post=65536, fixed-prob p=0.01 '
+                        '(655 int32 targets/row), heterogeneous f32 weights N(0.1,0.01), Bernoulli 1% spikes, '
+                        'products spike@W and W@spike',
+            'vectors_per_step': vectors, 'firing_rate': RATE,
+            'l2': l2_note, 'parallelism': 'spike vectors data-parallel, one matrix replica per GPU'}
+
+
+# ----------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------
+
+class DevicePass:
+    """Pre-allocated buffers and raw C-ABI calls for one pass of the hot path."""
+
+    def __init__(self, torch, dev, n, K, idx, w, vectors):
+        from brainstate_b200 import _lib, FixedPostNumConn
+        self.torch, self._lib, self.lib = torch, _lib, _lib.lib()
+        self.n, self.K, self.T = n, K, vectors
+        self.ti = torch.from_numpy(idx).to(dev)
+        self.tw = torch.from_numpy(w).to(dev)
+        self.conn = FixedPostNumConn((self.tw, self.ti), shape=(n, n))
+        self.st = self.conn._struct()
+        self.y_vecmat = torch.empty((vectors, n), dtype=torch.float32, device=dev)
+        self.y_matvec = torch.empty((vectors, n), dtype=torch.float32, device=dev)
+        self.words = (n + 31) // 32
+        self.bits = torch.empty((vectors, self.words), dtype=torch.int32, device=dev)
+        self.ws_bytes = self.lib.bsx_event_vecmat_workspace_bytes(vectors, n)
+        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=dev)
+        self.launches_per_pass = 2 + 1 + vectors     # compact + scatter, pack, T gathers
+        self.ev0 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+
+    def vecmat(self, spk_dev, stream):
+        self._lib.check(self.lib.bsx_event_vecmat(C.byref(self.st), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
+                                                  self.T, self.y_vecmat.data_ptr(), 0, self.ws.data_ptr(),
+                                                  self.ws_bytes, stream))
+
+    def matvec(self, spk_dev, stream):
+        lib, _lib = self.lib, self._lib
+        _lib.check(lib.bsx_pack_spikes(spk_dev.data_ptr(), _lib.SPK_BOOL8, self.T, self.n,
+                                       self.bits.data_ptr(), stream))
+        row_bytes = self.words * 4
+        for t in range(self.T):
+            _lib.check(lib.bsx_event_matvec(C.byref(self.st), self.bits.data_ptr() + t * row_bytes,
+                                            _lib.SPK_BITS32, 1, self.y_matvec.data_ptr() + t * self.n * 4,
+                                            None, 0, stream))
+
+    def run(self, spk_dev, stream):
+        self.vecmat(spk_dev, stream)
+        self.matvec(spk_dev, stream)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    if not torch.cuda.is_available():
+        print(json.dumps({'error': 'no CUDA device: bench.py times the CUDA path only'}))
+        return 1
+    torch.cuda.set_device(local_rank)
+    dev = torch.device('cuda', local_rank)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+
+    from brainstate_b200 import _lib
+    from brainstate_b200.nn import EventFixedProb
+    from brainstate_b200 import EventArray
+    T = args.vectors
+    n, K, idx, w, spk = build_workload(T, rank)
+    events_pass = 2 * int(spk.sum()) * K
+    dp = DevicePass(torch, dev, n, K, idx, w, T)
+    spk_dev = torch.from_numpy(spk).to(dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing -------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        dp.run(spk_dev, stream)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    mv = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    e_start.record()
+    for s in range(args.steps):
+        dp.vecmat(spk_dev, stream)
+        mv[s][0].record()
+        dp.matvec(spk_dev, stream)
+        mv[s][1].record()
+    e_end.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = e_start.elapsed_time(e_end)
+    ms_matvec = sum(a.elapsed_time(b) for a, b in mv)
+    t_dev = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t_dev, op=dist.ReduceOp.MAX)
+    ms_total_max = float(t_dev.item())
+    ev_all = torch.tensor([float(events_pass)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ev_all, op=dist.ReduceOp.SUM)
+    events_all = float(ev_all.item())
+    value = events_all * args.steps / (ms_total_max * 1e-3)
+
+    if args.profile:          # device loop only: what the profiler captures
+        if rank == 0:
+            print(json.dumps({'profile_run': True, 'value': value, 'ms_per_step': ms_total_max / args.steps}))
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    # ---- end to end through the layer API, host buffers ---------------------------
+    layer = EventFixedProb(n, n, PROB, dp.tw, seed=SEED_CONN)
+    assert torch.equal(layer.conn.indices, dp.ti)
+    host_spk = torch.from_numpy(spk).pin_memory()
+    host_y1 = torch.empty((T, n), dtype=torch.float32).pin_memory()
+    host_y2 = torch.empty((T, n), dtype=torch.float32).pin_memory()
+
+    def e2e_pass():
+        s = host_spk.to(dev, non_blocking=True)
+        y1 = layer(s)                                  # spike @ W  (public layer call)
+        y2 = layer.conn @ EventArray(s)                # W @ spike  (public operator)
+        host_y1.copy_(y1, non_blocking=True)
+        host_y2.copy_(y2, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(2):
+        e2e_pass()
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_pass()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    t_e2e = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+    e2e_value = events_all * e2e_steps / float(t_e2e.item())
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    # ---- roofline of the dominant kernel (the gather event matvec) ----------------
+    peak, peak_kind = measured_hbm_peak()
+    nnz = n * K
+    mean_events = float(spk.sum()) * K / T
+    bytes_per_launch = nnz * 4 + mean_events * 4 + n / 8 + 4 * n
+    avg_launch_s = (ms_matvec * 1e-3) / (args.steps * T)      # includes the per-pass pack launch (<1 %)
+    achieved = bytes_per_launch / avg_launch_s / 1e9
+    roofline = {'bound': 'hbm', 'kernel': 'event_matvec_kernel<hetero, smem mask>', 'achieved': achieved,
+                'peak': peak, 'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': achieved / peak,
+                'bytes_per_launch': bytes_per_launch, 'avg_launch_us': avg_launch_s * 1e6,
+                'share_of_step': ms_matvec / ms_total, 'traffic': None}
+    prof = os.path.join(ROOT, 'profiles', 'event_matvec_traffic.json')
+    if os.path.exists(prof):
+        try:
+            roofline['traffic'] = float(json.load(open(prof))['dram_bytes_per_launch'])
+        except Exception:
+            pass
+
+    cpu, _, _, _ = cpu_baseline(idx, w, spk)
+
+    line = {
+        'metric': 'synaptic events/s (event matvec microbenchmark, both products)',
+        'value': value, 'unit': 'synaptic events/s', 'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3),
+        'ms_per_step': ms_total_max / args.steps, 'higher_is_better': True, 'scaling': 'weak',
+        'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': workload_config(T, 'inputs larger than L2 (343 MB matrix vs 126 MB L2), no flush'),
+        'clocks': clocks,
+        'e2e': {'value': e2e_value, 'unit': 'synaptic events/s', 'h2d_bytes_per_step': int(spk.nbytes),
+                'd2h_bytes_per_step': int(2 * T * n * 4), 'steps': e2e_steps},
+        'gpu_launches': int(dp.launches_per_pass * args.steps),
+        'roofline': roofline,
+        'cpu_baseline': cpu,
+        'events_per_step': events_all,
+    }
+    if args.cases:
+        line['cases'] = run_cases(torch, dev, dp, idx, w, peak)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_cases(torch, dev, dp, idx, w, peak):
+    """The rest of the microbenchmark grid (rates x weight modes x products), each
+    timed on its own with CUDA events after warm-up; reported beside the headline."""
+    from brainstate_b200 import _lib, FixedPostNumConn
+    lib = _lib.lib()
+    n, K, T = dp.n, dp.K, dp.T
+    stream = torch.cuda.current_stream().cuda_stream
+    homo = FixedPostNumConn((0.1, dp.ti), shape=(n, n))
+    out = []
+    for r_id, rate in enumerate((0.001, 0.01, 0.1)):
+        spk = np.random.RandomState(210 + r_id).random_sample((T, n)) < rate
+        sd = torch.from_numpy(spk).to(dev)
+        events = float(spk.sum()) * K
+        for name, conn in (('homo', homo), ('hetero', dp.conn)):
+            st = conn._struct()
+            h = int(conn.hetero)
+
+            def vecmat():
+                _lib.check(lib.bsx_event_vecmat(C.byref(st), sd.data_ptr(), _lib.SPK_BOOL8, T, dp.y_vecmat.data_ptr(),
+                                                0, dp.ws.data_ptr(), dp.ws_bytes, stream))
+
+            def matvec():
+                _lib.check(lib.bsx_pack_spikes(sd.data_ptr(), _lib.SPK_BOOL8, T, n, dp.bits.data_ptr(), stream))
+                for t in range(T):
+                    _lib.check(lib.bsx_event_matvec(C.byref(st), dp.bits.data_ptr() + t * dp.words * 4, _lib.SPK_BITS32,
+                                                    1, dp.y_matvec.data_ptr() + t * n * 4, None, 0, stream))
+
+            for prod, fn, alg in (('spike@W scatter', vecmat, events * (4 + 4 * h) + T * (n + 4 * n)),
+                                  ('W@spike gather', matvec, T * (n * K * 4 + n / 8 + 4 * n) + events * 4 * h)):
+                for _ in range(3):
+                    fn()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                reps = 5
+                for _ in range(reps):
+                    fn()
+                b.record()
+                torch.cuda.synchronize()
+                s = a.elapsed_time(b) * 1e-3 / reps
+                out.append({'rate': rate, 'weights': name, 'product': prod, 'vectors': T,
+                            'events_per_s': events / s, 'us_per_vector': s / T * 1e6,
+                            'algorithmic_GBps': alg / s / 1e9, 'frac_of_peak': alg / s / 1e9 / peak})
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--vectors', type=int, default=64, help='spike vectors per step (per GPU)')
+    ap.add_argument('--cases', action='store_true', help='also time the full rate x weight x product grid')
+    ap.add_argument('--profile', action='store_true',
+                    help='run only the device-resident loop (for ncu); prints no bench line')
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        return run_reference_arm(args)
+    return run_ours(args)
+
+
+if __name__ == '__main__':
+    sys.exit(main())

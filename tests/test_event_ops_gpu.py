@@ -1,0 +1,392 @@
+"""GPU parity: every product of the C-ABI library against the CPU oracle on the
+same seeded inputs, at the reference's test shapes, at ragged/edge shapes and at
+the full size of the standalone microbenchmark (65 536 x 65 536, p = 0.01).
+
+Tolerances: integer/index work is compared bit for bit; float32 sums within
+rtol 1e-5 / atol 1e-6 (``brainstate/_testing.py:56-57``), with the absolute term
+scaled by the sum of magnitudes where a row mixes signs.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import event_oracle as eo
+
+pytestmark = pytest.mark.gpu
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), 'golden', 'event_golden.npz'))
+RTOL, ATOL = 1e-5, 1e-6
+
+
+def close(actual, desired, scale=1.0):
+    a = actual.detach().cpu().numpy() if isinstance(actual, torch.Tensor) else np.asarray(actual)
+    np.testing.assert_allclose(a, desired, rtol=RTOL, atol=ATOL * scale)
+
+
+def make(n_pre, n_post, K, seed, hetero, cuda, csr_ratio=None):
+    from brainstate_b200 import FixedPostNumConn, CSR
+    rs = np.random.RandomState(seed + 77)
+    if csr_ratio is None:
+        idx = eo.fixed_num_indices(seed, n_pre, n_post, K)
+        indptr = None
+    else:
+        idx, indptr, _ = eo.afferent_csr(seed, n_pre, n_post, K, csr_ratio)
+    w = rs.uniform(0.05, 0.15, size=idx.shape).astype(np.float32) if hetero else np.float32(0.1)
+    ti = torch.from_numpy(idx).to(cuda)
+    tw = torch.as_tensor(w, device=cuda)
+    if indptr is None:
+        conn = FixedPostNumConn((tw, ti), shape=(n_pre, n_post))
+    else:
+        conn = CSR((tw, ti, torch.from_numpy(indptr).to(cuda)), shape=(n_pre, n_post))
+    return conn, idx, indptr, w
+
+
+SHAPES = [(20, 30, 3), (20, 40, 4), (33, 1000, 17), (64, 128, 128), (257, 513, 131), (1000, 96, 7)]
+
+
+@pytest.mark.parametrize('shape', SHAPES)
+@pytest.mark.parametrize('hetero', [False, True])
+@pytest.mark.parametrize('layout', ['fixed', 'csr'])
+def test_event_vecmat_matches_oracle(shape, hetero, layout, cuda):
+    from brainstate_b200 import EventArray
+    n_pre, n_post, K = shape
+    conn, idx, indptr, w = make(n_pre, n_post, K, 5, hetero, cuda, 0.6 if layout == 'csr' else None)
+    conn.validate()
+    rs = np.random.RandomState(9)
+    for rate in (0.0, 0.05, 0.3, 1.0):
+        spk = rs.random_sample(n_pre) < rate
+        ref = eo.event_vecmat(spk, idx, w, n_post, indptr)
+        for t in (torch.from_numpy(spk).to(cuda),                                   # bool
+                  torch.from_numpy(spk.astype(np.uint8)).to(cuda),                  # uint8
+                  torch.from_numpy((spk * rs.uniform(0.5, 2, n_pre)).astype(np.float32)).to(cuda)):  # float events
+            y = EventArray(t) @ conn
+            assert y.shape == (n_post,) and y.dtype == torch.float32
+            if hetero:
+                close(y, ref)
+            else:  # identical addends: any summation order gives the same bits
+                assert np.array_equal(y.cpu().numpy(), ref)
+        yg = conn._vecmat(torch.from_numpy(spk).to(cuda), event=True, method='gather')
+        close(yg, ref)
+
+
+@pytest.mark.parametrize('lead', [(3,), (2, 3), (5, 1)])
+def test_leading_batch_dimensions(lead, cuda):
+    from brainstate_b200 import EventArray
+    n_pre, n_post, K = 70, 90, 9
+    conn, idx, _, w = make(n_pre, n_post, K, 3, True, cuda)
+    rs = np.random.RandomState(1)
+    spk = rs.random_sample(lead + (n_pre,)) < 0.2
+    y = EventArray(torch.from_numpy(spk).to(cuda)) @ conn
+    assert tuple(y.shape) == lead + (n_post,)
+    close(y, eo.event_vecmat(spk, idx, w, n_post))
+    x = rs.standard_normal(lead + (n_pre,)).astype(np.float32)
+    close(torch.from_numpy(x).to(cuda) @ conn, eo.float_vecmat(x, idx, w, n_post), scale=10)
+    v = rs.standard_normal(lead + (n_post,)).astype(np.float32)
+    close(conn @ torch.from_numpy(v).to(cuda), eo.float_matvec(v, idx, w, n_pre), scale=10)
+    s = rs.random_sample(lead + (n_post,)) < 0.3
+    close(conn @ EventArray(torch.from_numpy(s).to(cuda)), eo.event_matvec(s, idx, w, n_pre))
+
+
+@pytest.mark.parametrize('hetero', [False, True])
+def test_unaligned_views_and_ragged_sizes(hetero, cuda):
+    """Sliced tensors start off the 16-byte grid; sizes are not multiples of 4 or 32."""
+    from brainstate_b200 import EventArray
+    n_pre, n_post, K = 101, 203, 13
+    conn, idx, _, w = make(n_pre, n_post, K, 8, hetero, cuda)
+    rs = np.random.RandomState(4)
+    for off in (1, 2, 3, 5):
+        spk = rs.random_sample(n_pre + off) < 0.4
+        t = torch.from_numpy(spk).to(cuda)[off:]
+        close(EventArray(t) @ conn, eo.event_vecmat(spk[off:], idx, w, n_post))
+        tf = torch.from_numpy(spk.astype(np.float32)).to(cuda)[off:]
+        close(EventArray(tf) @ conn, eo.event_vecmat(spk[off:], idx, w, n_post))
+        s = rs.random_sample(n_post + off) < 0.4
+        close(conn @ EventArray(torch.from_numpy(s).to(cuda)[off:]), eo.event_matvec(s[off:], idx, w, n_pre))
+
+
+def test_spike_formats_bits_and_list(bsx, cuda):
+    from brainstate_b200 import _lib
+    from brainstate_b200.event import pack_spikes, event_matvec
+    n_pre, n_post, K = 300, 170, 11
+    conn, idx, _, w = make(n_pre, n_post, K, 2, True, cuda)
+    rs = np.random.RandomState(6)
+    spk = rs.random_sample((3, n_pre)) < 0.25
+    bits = pack_spikes(torch.from_numpy(spk).to(cuda))
+    assert np.array_equal(bits.cpu().numpy().view(np.uint32),
+                          np.stack([eo.pack_bits(s) for s in spk]))
+    ref = eo.event_vecmat(spk, idx, w, n_post)
+    st = conn._struct()
+    ws_bytes = bsx.bsx_event_vecmat_workspace_bytes(3, n_pre)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=cuda)
+    out = torch.empty((3, n_post), dtype=torch.float32, device=cuda)
+    stream = _lib.current_stream()
+    _lib.check(bsx.bsx_event_vecmat(C.byref(st), bits.data_ptr(), _lib.SPK_BITS32, 3, out.data_ptr(), 0,
+                                    ws.data_ptr(), ws_bytes, stream))
+    close(out, ref)
+    # accumulate=1 adds onto what is there
+    _lib.check(bsx.bsx_event_vecmat(C.byref(st), bits.data_ptr(), _lib.SPK_BITS32, 3, out.data_ptr(), 1,
+                                    ws.data_ptr(), ws_bytes, stream))
+    close(out, 2 * ref)
+    # an index list: count first, then the active rows
+    act = np.nonzero(spk[0])[0].astype(np.int32)
+    lst = torch.from_numpy(np.concatenate([[act.size], act]).astype(np.int32)).to(cuda)
+    o1 = torch.empty(n_post, dtype=torch.float32, device=cuda)
+    _lib.check(bsx.bsx_event_vecmat(C.byref(st), lst.data_ptr(), _lib.SPK_LIST, 1, o1.data_ptr(), 0, None, 0, stream))
+    close(o1, ref[0])
+    # matvec from packed words
+    s = rs.random_sample((2, n_post)) < 0.3
+    close(event_matvec(conn, pack_spikes(torch.from_numpy(s).to(cuda)), bits=True), eo.event_matvec(s, idx, w, n_pre))
+    # a too-small workspace is refused, not overrun
+    rc = bsx.bsx_event_vecmat(C.byref(st), bits.data_ptr(), _lib.SPK_BITS32, 3, out.data_ptr(), 0, ws.data_ptr(), 64, stream)
+    assert rc == _lib.BSX_ERR_WORKSPACE
+
+
+@pytest.mark.parametrize('c', [0, 1, 2, 3])
+def test_golden_fixtures(c, cuda):
+    """Committed fixtures (connectivity from the reference's NumPy calls, products
+    from an independent restatement of the reference's in-test oracle)."""
+    from brainstate_b200 import EventArray, FixedPostNumConn
+    from brainstate_b200.nn import EventFixedProb, FixedNumConn
+    seed, n_pre, n_post, K = (int(v) for v in GOLD[f'c{c}_meta'])
+    layer = EventFixedProb(n_pre, n_post, K, 1.5, seed=seed)
+    assert np.array_equal(layer.conn.indices.cpu().numpy(), GOLD[f'c{c}_indices'])     # bit-exact connectivity
+    spk = torch.from_numpy(GOLD[f'c{c}_spk']).to(cuda)
+    assert np.array_equal(layer(spk).cpu().numpy(), GOLD[f'c{c}_y_event_homo'])
+    w = torch.from_numpy(GOLD[f'c{c}_w_het']).to(cuda)
+    het = EventFixedProb(n_pre, n_post, K, w, seed=seed)
+    close(het(spk), GOLD[f'c{c}_y_event_het'])
+    xf = torch.from_numpy(GOLD[f'c{c}_xf']).to(cuda)
+    close(het(xf), GOLD[f'c{c}_y_event_het'])
+    flt = FixedNumConn(n_pre, n_post, K, w, seed=seed)
+    close(flt(xf), GOLD[f'c{c}_y_float_het'])
+    sub = FixedNumConn(n_pre, n_post, K, 1.0, seed=seed, afferent_ratio=0.5)
+    assert np.array_equal(sub.pre_selected, GOLD[f'c{c}_pre_selected'])
+    assert np.array_equal(sub.conn.indices.cpu().numpy(), GOLD[f'c{c}_indices'][GOLD[f'c{c}_pre_selected']].reshape(-1))
+    # reverse mode through autograd
+    ct = torch.from_numpy(GOLD[f'c{c}_ct']).to(cuda)
+    x = xf.clone().requires_grad_(True)
+    wp = w.clone().requires_grad_(True)
+    flt.weight.value = wp
+    (flt(x) * ct).sum().backward()
+    close(x.grad, GOLD[f'c{c}_dx_het'], scale=20)
+    close(wp.grad, GOLD[f'c{c}_dw_het_float'])
+    x2 = xf.clone().requires_grad_(True)
+    wp2 = w.clone().requires_grad_(True)
+    het.weight.value = wp2
+    (het(x2) * ct).sum().backward()
+    close(x2.grad, GOLD[f'c{c}_dx_het'], scale=20)
+    close(wp2.grad, GOLD[f'c{c}_dw_het_event'])
+    wh = torch.tensor(1.5, device=cuda, requires_grad=True)
+    layer.weight.value = wh
+    (layer(spk) * ct).sum().backward()
+    close(wh.grad, GOLD[f'c{c}_dw_homo_event'], scale=20)
+
+
+@pytest.mark.parametrize('homo_w', [True, False])
+def test_vjp_like_the_reference_test(homo_w, cuda):
+    """``brainstate/nn/_event_fixedprob_test.py:56-88``: n_in=20, n_out=30, p=0.1, seed=123."""
+    from brainstate_b200.nn import EventFixedProb
+    n_in, n_out = 20, 30
+    rs = np.random.RandomState(0)
+    xn = (rs.random_sample(n_in) < 0.3).astype(np.float32)
+    init = (lambda shape: rs.uniform(-0.5, 0.5, shape).astype(np.float32))
+    fn = EventFixedProb(n_in, n_out, 0.1, 1.5 if homo_w else init, seed=123)
+    assert fn.conn_num == 3
+    x = torch.from_numpy(xn).to(cuda).requires_grad_(True)
+    w = fn.weight.value.clone().requires_grad_(True)
+    fn.weight.value = w
+    fn(x).sum().backward()
+    idx = fn.conn.indices.cpu().numpy()
+    wn = w.detach().cpu().numpy()
+    dx, dw = eo.vecmat_vjp(xn, np.ones(n_out, np.float32), idx, wn, event=True)
+    close(x.grad, dx)
+    close(w.grad, dw)
+    # a bool spike vector is not differentiable; the weight still is
+    w2 = fn.weight.value.detach().clone().requires_grad_(True)
+    fn.weight.value = w2
+    fn(torch.from_numpy(xn != 0).to(cuda)).sum().backward()
+    close(w2.grad, dw)
+
+
+@pytest.mark.parametrize('homo_w', [True, False])
+def test_jvp_like_the_reference_test(homo_w, cuda):
+    """``brainstate/nn/_event_fixedprob_test.py:90-126`` with forward-mode AD."""
+    import torch.autograd.forward_ad as fwAD
+    from brainstate_b200.nn import EventFixedProb
+    n_in, n_out = 20, 30
+    rs = np.random.RandomState(1)
+    xn = (rs.random_sample(n_in) < 0.3).astype(np.float32)
+    init = (lambda shape: rs.uniform(-0.5, 0.5, shape).astype(np.float32))
+    fn = EventFixedProb(n_in, n_out, 0.1, 1.5 if homo_w else init, seed=123)
+    w = fn.weight.value
+    x = torch.from_numpy(xn).to(cuda)
+    with fwAD.dual_level():
+        fn.weight.restore_value(fwAD.make_dual(w, torch.ones_like(w)))
+        out = fn(fwAD.make_dual(x, torch.ones_like(x)))
+        primal, tangent = fwAD.unpack_dual(out)
+    fn.weight.restore_value(w)
+    idx = fn.conn.indices.cpu().numpy()
+    wn = w.cpu().numpy()
+    close(primal, eo.event_vecmat(xn, idx, wn, n_out))
+    ref = eo.vecmat_jvp(xn, np.ones(n_in, np.float32), np.ones_like(wn), idx, wn, n_out, event=True)
+    np.testing.assert_allclose(tangent.cpu().numpy(), ref, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize('hetero', [False, True])
+@pytest.mark.parametrize('batch', [1, 4])
+def test_raw_vjp_entry_point(hetero, batch, bsx, cuda, c_oracle):
+    from brainstate_b200.event import _raw_vjp
+    n_pre, n_post, K = 150, 220, 21
+    for layout in (None, 0.5):
+        conn, idx, indptr, w = make(n_pre, n_post, K, 12, hetero, cuda, layout)
+        rs = np.random.RandomState(13)
+        x = (rs.standard_normal((batch, n_pre)) * (rs.random_sample((batch, n_pre)) < 0.4)).astype(np.float32)
+        ct = rs.standard_normal((batch, n_post)).astype(np.float32)
+        for event in (False, True):
+            dx_ref, dw_ref = eo.vecmat_vjp(x, ct, idx, w, indptr, event=event)
+            for need_dx in (True, False):
+                dx, dw = _raw_vjp(conn, torch.from_numpy(x).to(cuda), conn.data, torch.from_numpy(ct).to(cuda),
+                                  event, need_dx, True)
+                if need_dx:
+                    close(dx, dx_ref, scale=30)
+                close(dw.reshape(np.shape(dw_ref)), dw_ref, scale=30 * (1 if hetero else 50))
+
+
+def test_transposed_copy_is_canonical(cuda):
+    n_pre, n_post, K = 123, 77, 19
+    for layout in (None, 0.5):
+        conn, idx, indptr, w = make(n_pre, n_post, K, 21, True, cuda, layout)
+        t = conn.transposed()
+        flat = idx.reshape(-1)
+        order = np.argsort(flat, kind='stable')                # ascending column, then position
+        assert np.array_equal(t.perm.cpu().numpy(), order.astype(np.int32))
+        counts = np.bincount(flat, minlength=n_post)
+        assert np.array_equal(t.indptr.cpu().numpy(), np.concatenate([[0], np.cumsum(counts)]))
+        starts = np.arange(n_pre + 1) * K if indptr is None else indptr
+        rows = np.searchsorted(starts, order, side='right') - 1
+        assert np.array_equal(t.indices.cpu().numpy(), rows.astype(np.int32))
+
+
+def test_validate_catches_bad_indices(cuda):
+    from brainstate_b200 import FixedPostNumConn, CSR
+    idx = torch.randint(0, 50, (40, 6), dtype=torch.int32, device=cuda)
+    conn = FixedPostNumConn((1.0, idx), shape=(40, 50))
+    conn.validate()
+    bad = idx.clone()
+    bad[17, 3] = 50
+    with pytest.raises(ValueError):
+        FixedPostNumConn((1.0, bad), shape=(40, 50)).validate()
+    bad[17, 3] = -1
+    with pytest.raises(ValueError):
+        FixedPostNumConn((1.0, bad), shape=(40, 50)).validate()
+    indptr = torch.arange(0, 41, dtype=torch.int32, device=cuda) * 6
+    CSR((1.0, idx.reshape(-1), indptr), shape=(40, 50)).validate()
+    indptr[5] = 100
+    with pytest.raises(ValueError):
+        CSR((1.0, idx.reshape(-1), indptr), shape=(40, 50)).validate()
+
+
+def test_zero_connection_and_empty_inputs(cuda):
+    from brainstate_b200.nn import FixedNumConn, EventFixedProb
+    m = FixedNumConn(20, 40, 0.0, 1.0, seed=1)
+    assert m.conn_num == 0
+    out = m(torch.rand(20, device=cuda))
+    assert out.shape == (40,) and bool((out == 0).all())
+    out = EventFixedProb(20, 40, 0.0, 1.0, seed=1)(torch.rand(3, 20, device=cuda) < 0.5)
+    assert out.shape == (3, 40) and bool((out == 0).all())
+    ev = EventFixedProb(20, 40, 0.1, 1.0, seed=123)
+    assert bool((ev(torch.zeros(20, dtype=torch.bool, device=cuda)) == 0).all())
+    assert ev(torch.zeros((0, 20), dtype=torch.bool, device=cuda)).shape == (0, 40)
+    sub = FixedNumConn(20, 40, 0.2, 1.0, afferent_ratio=0.5, seed=1)
+    assert sub.pre_selected.shape == (20,) and sub(torch.rand(20, device=cuda)).shape == (40,)
+    m1 = FixedNumConn(20, 40, 0.2, 1.0, afferent_ratio=0.5, seed=7)
+    m2 = FixedNumConn(20, 40, 0.2, 1.0, afferent_ratio=0.5, seed=7)
+    assert np.array_equal(m1.pre_selected, m2.pre_selected)
+    nr = FixedNumConn(20, 40, 0.2, 1.0, seed=3, allow_multi_conn=False, conn_init='for_loop')
+    assert nr(torch.rand(20, device=cuda)).shape == (40,)
+
+
+def test_event_update_matches_scatter_reference(cuda):
+    """``brainstate/nn/_event_fixedprob_test.py:247-260``."""
+    from brainstate_b200.nn import EventFixedProb
+    n_in, n_out = 20, 30
+    fn = EventFixedProb(n_in, n_out, 0.2, 1.5, seed=11)
+    spk = (np.random.RandomState(2).random_sample(n_in) < 0.3).astype(np.float32)
+    out = fn(torch.from_numpy(spk).to(cuda)).cpu().numpy()
+    indices = fn.conn.indices.cpu().numpy()
+    ref = np.zeros((n_out,))
+    for i in range(n_in):
+        np.add.at(ref, indices[i], 1.5 * float(spk[i]))
+    assert np.allclose(out, ref, rtol=1e-4, atol=1e-4)
+
+
+def test_event_linear(cuda):
+    from brainstate_b200.nn import EventLinear
+    spk = torch.from_numpy(GOLD['dense_spk']).to(cuda)
+    for fae, expect in ((True, GOLD['dense_event_true']), (False, GOLD['dense_event_false'])):
+        y = EventLinear(10, 6, 1.5, float_as_event=fae)(spk)
+        assert y.shape == (6,) and bool((y == float(expect)).all())
+    rs = np.random.RandomState(3)
+    for (n_in, n_out, lead) in ((10, 6, ()), (300, 1030, (3,)), (2500, 257, (2, 2))):
+        W = rs.standard_normal((n_in, n_out)).astype(np.float32)
+        s = (rs.random_sample(lead + (n_in,)) < 0.3)
+        sf = (s * rs.uniform(0.5, 2, s.shape)).astype(np.float32)
+        layer = EventLinear(n_in, n_out, W, float_as_event=True)
+        for t in (torch.from_numpy(s).to(cuda), torch.from_numpy(sf).to(cuda)):
+            y = layer(t)
+            assert tuple(y.shape) == lead + (n_out,)
+            close(y, eo.event_linear(s, W, n_out, True), scale=100)
+        y2 = EventLinear(n_in, n_out, W, float_as_event=False)(torch.from_numpy(sf).to(cuda))
+        np.testing.assert_allclose(y2.cpu().numpy(), sf @ W, rtol=1e-4, atol=1e-3)
+    # gradients of the event product: d spk = ct @ W^T, dW = [spk != 0]^T ct
+    W = torch.from_numpy(rs.standard_normal((10, 6)).astype(np.float32)).to(cuda).requires_grad_(True)
+    x = spk.clone().requires_grad_(True)
+    layer = EventLinear(10, 6, W)
+    layer(x).sum().backward()
+    close(x.grad, W.detach().sum(dim=1).cpu().numpy(), scale=10)
+    close(W.grad, ((spk != 0).float()[:, None] * torch.ones(6, device=cuda)).cpu().numpy())
+
+
+@pytest.fixture(scope='module')
+def microbench(cuda, c_oracle):
+    """The standalone microbenchmark matrix at full size: 65 536^2, p = 0.01."""
+    n, K = 65536, 655
+    idx = c_oracle.fixed_num_indices(200, n, n, K)
+    w = np.random.RandomState(201).normal(0.1, 0.01, (n, K)).astype(np.float32)
+    return n, K, idx, w, torch.from_numpy(idx).to(cuda), torch.from_numpy(w).to(cuda)
+
+
+@pytest.mark.parametrize('rate_id', [0, 1, 2])
+def test_microbenchmark_size_against_c_oracle(rate_id, microbench, c_oracle, cuda):
+    from brainstate_b200 import EventArray, FixedPostNumConn
+    from brainstate_b200.nn import fixed_num_indices
+    n, K, idx, w, ti, tw = microbench
+    rate = (0.001, 0.01, 0.1)[rate_id]
+    if rate_id == 0:
+        assert np.array_equal(fixed_num_indices(200, n, n, K), idx)
+    spk = np.random.RandomState(210 + rate_id).random_sample((2, n)) < rate
+    ts = torch.from_numpy(spk).to(cuda)
+    het = FixedPostNumConn((tw, ti), shape=(n, n))
+    hom = FixedPostNumConn((0.1, ti), shape=(n, n))
+    ref_het = c_oracle.event_vecmat_u8(spk, idx, w, n)
+    ref_hom = c_oracle.event_vecmat_u8(spk, idx, np.float32(0.1), n)
+    close(EventArray(ts) @ het, ref_het)
+    assert np.array_equal((EventArray(ts) @ hom).cpu().numpy(), ref_hom)
+    close(het @ EventArray(ts), c_oracle.event_matvec_u8(spk, idx, w, n))
+    close(hom @ EventArray(ts), c_oracle.event_matvec_u8(spk, idx, np.float32(0.1), n))
+    # size-independent properties: linearity in the spikes and agreement of the two
+    # forward variants (scatter vs deterministic gather over the transposed copy)
+    a, b = ts[0] & ~ts[1], ts[1] & ~ts[0]
+    both = a | b
+    close((EventArray(a) @ hom) + (EventArray(b) @ hom), (EventArray(both) @ hom).cpu().numpy(), scale=10)
+    if rate_id == 1:
+        yg = het._vecmat(ts, event=True, method='gather')
+        close(yg, ref_het)
+        yg2 = het._vecmat(ts, event=True, method='gather')
+        assert torch.equal(yg, yg2)                    # deterministic
+        ct = np.random.RandomState(221).standard_normal((1, n)).astype(np.float32)
+        dx = het @ torch.from_numpy(ct).to(cuda)
+        close(dx, c_oracle.float_matvec(ct, idx, w, n), scale=30)
