@@ -63,6 +63,7 @@ SIGNATURES = {
     'bsx_event_vecmat_workspace_bytes': (_sz, [_i64, _i64]),
     'bsx_event_vecmat': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp, _sz, _vp]),
     'bsx_event_vecmat_tuned': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp, _sz, _i32, _i32, _vp]),
+    'bsx_event_vecmat_static': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp]),
     'bsx_float_vecmat': (_i32, [_connp, _vp, _i64, _vp, _i32, _vp, _sz, _vp]),
     'bsx_event_matvec_workspace_bytes': (_sz, [_i64, _i64]),
     'bsx_event_matvec': (_i32, [_connp, _vp, _i32, _i64, _vp, _vp, _sz, _vp]),

@@ -14,4 +14,10 @@ int launch_compact(const void* spikes, int format, int64_t batch, int64_t n_pre,
 
 int launch_zero(float* z, int64_t n, cudaStream_t st);
 
+// Shared body of the vecmat entry points (scatter.cu): queue the active rows of
+// `in` in the workspace `ws`, then scatter them.  x != NULL multiplies by the value.
+int vecmat_common(const bsx_conn_t* conn, const void* in, int format, const float* x, int64_t batch,
+                  float* out, int accumulate, void* ws, size_t ws_bytes, int chunk, int blocks_per_sm,
+                  cudaStream_t st);
+
 }  // namespace bsx

@@ -126,7 +126,7 @@ static size_t queue_bytes(int64_t batch, int64_t n_pre) {
   return (b + 255) & ~size_t(255);
 }
 
-static int vecmat_common(const bsx_conn_t* conn, const void* in, int format, const float* x, int64_t batch,
+int vecmat_common(const bsx_conn_t* conn, const void* in, int format, const float* x, int64_t batch,
                          float* out, int accumulate, void* ws, size_t ws_bytes, int chunk,
                          int blocks_per_sm, cudaStream_t st) {
   int rc = check_conn(conn);

@@ -150,6 +150,26 @@ int bsx_event_vecmat_tuned(const bsx_conn_t* conn, const void* spikes, int spike
                            int chunk, int blocks_per_sm, bsx_stream_t stream);
 
 /*
+ * Event vecmat without a workspace argument.  No counterpart in the reference:
+ * it exists for callers that cannot obtain device memory when they call (a
+ * custom-call handler inside a framework that owns the GPU's memory pool; a
+ * latency-critical loop that must avoid the device-wide stall of an allocation).
+ * Same result as bsx_event_vecmat.  The active-row queue lives in a 4 MiB array
+ * built into the library image (each GPU that loads the library holds it until
+ * the process exits), which limits the input to
+ *     batch * n_pre <= BSX_STATIC_QUEUE_MAX_SPIKES
+ * (BSX_SPK_LIST inputs need no queue and are not limited); larger inputs are
+ * refused with BSX_ERR_WORKSPACE.  The call allocates nothing.  Its first call on
+ * a device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current), so make that first call outside any stream capture.  All calls
+ * on one GPU share the one array: calls that may run concurrently on the device
+ * (different streams) race on it and must be serialised by the caller.
+ */
+#define BSX_STATIC_QUEUE_MAX_SPIKES 1048000
+int bsx_event_vecmat_static(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
+                            float* out, int accumulate, bsx_stream_t stream);
+
+/*
  * y = x @ conn for float x               brainstate/nn/_event_fixedprob.py:202-205
  *   y[b, idx[i,k]] += x[b,i] * w[i,k]   (rows with x == 0 are skipped)
  * Also the two terms of the forward-mode rule (_event_fixedprob_test.py:90-126).
