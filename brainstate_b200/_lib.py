@@ -44,8 +44,28 @@ class BsxConn(C.Structure):
     ]
 
 
+class BsxLifParams(C.Structure):
+    """Mirror of ``bsx_lif_params_t``."""
+    _fields_ = [(n, C.c_float) for n in ('dt', 'decay_e', 'decay_i', 'inv_tau_m', 'cuba_gain', 'V_rest', 'V_th',
+                                         'V_reset', 'R', 'I_ext', 'E_e', 'E_i')] + \
+               [('ref_steps', C.c_int32), ('coba', C.c_int32)]
+
+
+class BsxNet(C.Structure):
+    """Mirror of ``bsx_net_t``."""
+    _fields_ = [
+        ('n_global', C.c_int64), ('n_exc', C.c_int64), ('first', C.c_int64), ('n_local', C.c_int64),
+        ('exc', BsxConn), ('inh', BsxConn),
+        ('V', C.c_void_p), ('g_e', C.c_void_p), ('g_i', C.c_void_p), ('ref', C.c_void_p),
+        ('delta_e', C.c_void_p), ('delta_i', C.c_void_p), ('bits', C.c_void_p),
+        ('list', C.c_void_p * 2),
+    ]
+
+
 _i64, _i32, _vp, _sz, _f32 = C.c_int64, C.c_int, C.c_void_p, C.c_size_t, C.c_float
 _connp = C.POINTER(BsxConn)
+_netp = C.POINTER(BsxNet)
+_lifp = C.POINTER(BsxLifParams)
 
 # name -> (restype, argtypes); every symbol include/bsx.h declares
 SIGNATURES = {
@@ -67,10 +87,14 @@ SIGNATURES = {
     'bsx_float_vecmat': (_i32, [_connp, _vp, _i64, _vp, _i32, _vp, _sz, _vp]),
     'bsx_event_matvec_workspace_bytes': (_sz, [_i64, _i64]),
     'bsx_event_matvec': (_i32, [_connp, _vp, _i32, _i64, _vp, _vp, _sz, _vp]),
-    'bsx_event_matvec_tuned': (_i32, [_connp, _vp, _i32, _i64, _vp, _vp, _sz, _i32, _i32, _vp]),
+    'bsx_event_matvec_tuned': (_i32, [_connp, _vp, _i32, _i64, _vp, _vp, _sz, _i32, _i32, _i32, _vp]),
     'bsx_float_matvec': (_i32, [_connp, _vp, _i64, _vp, _vp]),
     'bsx_vecmat_vjp': (_i32, [_connp, _vp, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
     'bsx_dense_event_vecmat': (_i32, [_vp, _i32, _vp, _i64, _i64, _i64, _vp, _vp]),
+    'bsx_net_run': (_i32, [_netp, _lifp, _i32, _i32, _vp, _vp, _i32, _vp]),
+    'bsx_net_update': (_i32, [_netp, _lifp, _vp, _vp]),
+    'bsx_net_list_from_bits': (_i32, [_netp, _i32, _vp]),
+    'bsx_net_scatter': (_i32, [_netp, _i32, _vp]),
     'bsx_fill_f32': (_i32, [_vp, _i64, _f32, _vp]),
 }
 

@@ -83,6 +83,49 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// One warp adds v (times the weight, if heterogeneous) into out[idx[p]] for every
+// entry p of [s, e): scalar head and tail around a body of 128-bit loads.  vec_ok
+// says that idx (and w) start on a 16-byte boundary.
+template <bool HETERO>
+__device__ __forceinline__ void scatter_span(const int32_t* __restrict__ idx, const float* __restrict__ w,
+                                             int64_t s, int64_t e, int lane, float v,
+                                             float* __restrict__ out, bool vec_ok) {
+  if (!vec_ok) {
+    for (int64_t p = s + lane; p < e; p += 32)
+      red_add(out + __ldg(idx + p), HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
+    return;
+  }
+  // [s, a0) scalar head, [a0, a1) 128-bit body, [a1, e) scalar tail
+  int64_t a0 = (s + 3) & ~int64_t(3);
+  if (a0 > e) a0 = e;
+  int64_t a1 = e & ~int64_t(3);
+  if (a1 < a0) a1 = a0;
+  const int nh = (int)(a0 - s), nt = (int)(e - a1);
+  if (lane < nh + nt) {
+    const int64_t p = lane < nh ? s + lane : a1 + (lane - nh);
+    red_add(out + __ldg(idx + p), HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
+  }
+  const int4* __restrict__ idx4 = reinterpret_cast<const int4*>(idx);
+  const float4* __restrict__ w4 = reinterpret_cast<const float4*>(w);
+  const int64_t q1 = a1 >> 2;
+#pragma unroll 2
+  for (int64_t q = (a0 >> 2) + lane; q < q1; q += 32) {
+    const int4 j = __ldg(idx4 + q);
+    if (HETERO) {
+      const float4 ww = __ldg(w4 + q);
+      red_add(out + j.x, __fmul_rn(v, ww.x));
+      red_add(out + j.y, __fmul_rn(v, ww.y));
+      red_add(out + j.z, __fmul_rn(v, ww.z));
+      red_add(out + j.w, __fmul_rn(v, ww.w));
+    } else {
+      red_add(out + j.x, v);
+      red_add(out + j.y, v);
+      red_add(out + j.z, v);
+      red_add(out + j.w, v);
+    }
+  }
+}
+
 // 1 where the spike at flat position p is active, for the byte/float formats.
 template <int FORMAT>
 __device__ __forceinline__ bool spike_at(const void* spikes, int64_t p) {

@@ -83,8 +83,11 @@ __device__ __forceinline__ bool bit_at(const uint32_t* __restrict__ m, int32_t j
 }
 
 // ---- event matvec -------------------------------------------------------------
-template <bool HETERO, bool SMEM>
-__global__ void __launch_bounds__(256)
+// U = number of 128-bit index loads each lane issues before it consumes any of
+// them.  A 655-entry row is 164 such loads, i.e. 6 per lane: with U = 6 a warp has
+// its whole row in flight at once.
+template <bool HETERO, bool SMEM, int U>
+__global__ void __launch_bounds__(256, (U > 2 ? 4 : 8))
 event_matvec_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
                     const uint32_t* __restrict__ bits, int64_t words, int64_t n_rows,
                     float* __restrict__ out, bool vec_ok, bool use_tma) {
@@ -114,6 +117,32 @@ event_matvec_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
       a1 = e & ~int64_t(3);
       if (a1 < a0) a1 = a0;
     }
+    const int64_t q1 = a1 >> 2;
+    for (int64_t qb = (a0 >> 2) + lane; qb < q1 + lane; qb += 32 * U) {
+      int4 j[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t q = qb + 32 * u;
+        if (q < q1) j[u] = __ldg(idx4 + q);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t q = qb + 32 * u;
+        if (q < q1) {
+          const bool h0 = bit_at(mask, j[u].x), h1 = bit_at(mask, j[u].y), h2 = bit_at(mask, j[u].z),
+                     h3 = bit_at(mask, j[u].w);
+          if (HETERO) {
+            const float* wp = w + (q << 2);
+            if (h0) acc += __ldg(wp);
+            if (h1) acc += __ldg(wp + 1);
+            if (h2) acc += __ldg(wp + 2);
+            if (h3) acc += __ldg(wp + 3);
+          } else {
+            hits += (int)h0 + (int)h1 + (int)h2 + (int)h3;
+          }
+        }
+      }
+    }
     // scalar head [s, a0) and tail [a1, e)
     for (int64_t p = s + lane; p < a0; p += 32)
       if (bit_at(mask, __ldg(idx + p))) {
@@ -123,21 +152,6 @@ event_matvec_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
       if (bit_at(mask, __ldg(idx + p))) {
         if (HETERO) acc += __ldg(w + p); else ++hits;
       }
-    const int64_t q1 = a1 >> 2;
-#pragma unroll 2
-    for (int64_t q = (a0 >> 2) + lane; q < q1; q += 32) {
-      const int4 j = __ldg(idx4 + q);
-      const bool h0 = bit_at(mask, j.x), h1 = bit_at(mask, j.y), h2 = bit_at(mask, j.z), h3 = bit_at(mask, j.w);
-      if (HETERO) {
-        const float* wp = w + (q << 2);
-        if (h0) acc += __ldg(wp);
-        if (h1) acc += __ldg(wp + 1);
-        if (h2) acc += __ldg(wp + 2);
-        if (h3) acc += __ldg(wp + 3);
-      } else {
-        hits += (int)h0 + (int)h1 + (int)h2 + (int)h3;
-      }
-    }
     if (HETERO) {
       acc = warp_sum(acc);
     } else {
@@ -276,7 +290,7 @@ size_t bsx_event_matvec_workspace_bytes(int64_t batch, int64_t n_post) {
 
 int bsx_event_matvec_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                            float* out, void* workspace, size_t workspace_bytes, int blocks_per_sm,
-                           int mask_mode, bsx_stream_t stream) {
+                           int mask_mode, int unroll, bsx_stream_t stream) {
   int rc = check_conn(conn);
   if (rc) return rc;
   if (batch < 0) return fail(BSX_ERR_INVALID_ARG, "negative batch");
@@ -300,7 +314,8 @@ int bsx_event_matvec_tuned(const bsx_conn_t* conn, const void* spikes, int spike
   } else {
     return fail(BSX_ERR_INVALID_ARG, "event matvec takes BOOL8, F32 or BITS32 spikes");
   }
-  if (blocks_per_sm <= 0) blocks_per_sm = 8;
+  if (unroll != 1 && unroll != 2 && unroll != 4 && unroll != 6) unroll = 6;
+  if (blocks_per_sm <= 0) blocks_per_sm = unroll > 2 ? 4 : 8;
   dim3 grid;
   rc = row_grid(conn->n_pre, batch, blocks_per_sm, &grid);
   if (rc) return rc;
@@ -313,13 +328,20 @@ int bsx_event_matvec_tuned(const bsx_conn_t* conn, const void* spikes, int spike
   const bool use_tma = use_smem && tma_ok && mask_mode != 2;
   const bool vec_ok = aligned16(conn->indices);
   const RowMap rm = make_rowmap(conn);
-#define BSX_EMV(H, S, SM)                                                                       \
+#define BSX_EMV_U(H, S, SM, UU)                                                                  \
   do {                                                                                          \
     if ((SM) > 48 * 1024)                                                                       \
-      BSX_CUDA(cudaFuncSetAttribute(event_matvec_kernel<H, S>,                                   \
+      BSX_CUDA(cudaFuncSetAttribute(event_matvec_kernel<H, S, UU>,                               \
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SM)));    \
-    event_matvec_kernel<H, S><<<grid, 256, (SM), st>>>(rm, conn->indices, conn->weights, bits, words, \
-                                                       conn->n_pre, out, vec_ok, use_tma);      \
+    event_matvec_kernel<H, S, UU><<<grid, 256, (SM), st>>>(rm, conn->indices, conn->weights, bits, \
+                                                           words, conn->n_pre, out, vec_ok, use_tma); \
+  } while (0)
+#define BSX_EMV(H, S, SM)                        \
+  do {                                           \
+    if (unroll == 1) BSX_EMV_U(H, S, SM, 1);     \
+    else if (unroll == 2) BSX_EMV_U(H, S, SM, 2); \
+    else if (unroll == 4) BSX_EMV_U(H, S, SM, 4); \
+    else BSX_EMV_U(H, S, SM, 6);                 \
   } while (0)
   if (use_smem) {
     if (smem > 24 * 1024) {  // fewer, fatter blocks: one mask copy per resident block
@@ -335,13 +357,14 @@ int bsx_event_matvec_tuned(const bsx_conn_t* conn, const void* spikes, int spike
     if (conn->hetero) BSX_EMV(true, false, 0); else BSX_EMV(false, false, 0);
   }
 #undef BSX_EMV
+#undef BSX_EMV_U
   BSX_LAUNCH_CHECK("event_matvec_kernel");
   return BSX_OK;
 }
 
 int bsx_event_matvec(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                      float* out, void* workspace, size_t workspace_bytes, bsx_stream_t stream) {
-  return bsx_event_matvec_tuned(conn, spikes, spike_format, batch, out, workspace, workspace_bytes, 0, 0,
+  return bsx_event_matvec_tuned(conn, spikes, spike_format, batch, out, workspace, workspace_bytes, 0, 0, 0,
                                 stream);
 }
 

@@ -1,0 +1,360 @@
+// Fused E/I network step: event scatter -> exponential synapses -> LIF (current- or
+// conductance-based) -> threshold / refractory -> packed spikes + spike list.
+//
+// This replaces, for one simulation step, the chain the reference's examples
+// build from separate operators (examples/400_CUBA_2005_bpu.py:47-66:
+// AlignPostProj(comm=EventFixedProb, syn=Expon, out=CUBA|COBA, post=LIFRef)):
+//
+//   phase A  for every neuron that spiked in the previous step, add its row of
+//            weights into delta_e (excitatory rows) or delta_i (inhibitory rows);
+//   phase B  g <- g*decay + delta (delta cleared in the same pass), membrane
+//            update by the exponential-Euler rule of brainstate/nn/_exp_euler.py:226-249,
+//            threshold, reset, refractory count, spike word by __ballot_sync and
+//            append to the next spike list.
+//
+// Synaptic currents never leave the delta/g arrays: there is no current vector
+// written to and re-read from HBM between the product and the neuron update.
+// bsx_net_run keeps both phases of many steps in ONE cooperative launch
+// (grid-wide barriers between phases); the split entry points serve the
+// multi-GPU driver, which exchanges the spike words between phases.
+//
+// Every float operation below is a single IEEE operation (no fused multiply-add)
+// and the exponential factor of the conductance-based rule is evaluated in double
+// and rounded once, so spike rasters can be compared bit for bit with a CPU
+// restatement that does the same.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+#include "internal.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace bsx {
+
+struct ProjDev {
+  RowMap rm;
+  const int32_t* idx;
+  const float* w;
+  int hetero;
+  int cpr;      // chunks per row
+  bool vec_ok;
+};
+
+struct NetDev {
+  int64_t n_global, n_exc, first, n_local;
+  ProjDev exc, inh;
+  int chunk;
+  float *V, *g_e, *g_i, *delta_e, *delta_i;
+  int32_t* ref;
+  uint32_t* bits;
+  int32_t* list0;
+  int32_t* list1;
+  bsx_lif_params_t p;
+};
+
+__device__ __forceinline__ void scatter_one(const ProjDev& pr, int64_t row, int c, int chunk, int lane,
+                                            float* __restrict__ out) {
+  int64_t s, e;
+  pr.rm.range(row, s, e);
+  s += (int64_t)c * chunk;
+  if (s >= e) return;
+  if (s + chunk < e) e = s + chunk;
+  if (pr.hetero) scatter_span<true>(pr.idx, pr.w, s, e, lane, 1.0f, out, pr.vec_ok);
+  else scatter_span<false>(pr.idx, pr.w, s, e, lane, __ldg(pr.w), out, pr.vec_ok);
+}
+
+// Phase A: list = [count, global ids...] of the neurons that spiked last step.
+__device__ __forceinline__ void phase_scatter(const NetDev& a, const int32_t* __restrict__ list, int64_t warp,
+                                              int64_t nwarps, int lane) {
+  const int64_t count = list[0];
+  const int cpr = a.exc.cpr > a.inh.cpr ? a.exc.cpr : a.inh.cpr;
+  const int64_t items = count * cpr;
+  for (int64_t it = warp; it < items; it += nwarps) {
+    const int64_t q = it / cpr;
+    const int c = (int)(it - q * cpr);
+    const int64_t id = list[1 + q];
+    if (id < a.n_exc) {
+      if (c < a.exc.cpr) scatter_one(a.exc, id, c, a.chunk, lane, a.delta_e);
+    } else {
+      if (c < a.inh.cpr) scatter_one(a.inh, id - a.n_exc, c, a.chunk, lane, a.delta_i);
+    }
+  }
+}
+
+__device__ __forceinline__ float exprel_once(float z) {
+  if (z == 0.0f) return 1.0f;
+  const double zd = (double)z;
+  return (float)(expm1(zd) / zd);
+}
+
+// Phase B for the 32 neurons of local word `word`; returns the spike word.
+__device__ __forceinline__ uint32_t update_word(const NetDev& a, int64_t word, int lane, bool* spiked) {
+  const bsx_lif_params_t& p = a.p;
+  const int64_t i = word * 32 + lane;
+  bool spk = false;
+  if (i < a.n_local) {
+    // all loads first: the six arrays never alias, and a store between two loads
+    // would otherwise serialise the memory round trips
+    float* __restrict__ pde = a.delta_e;
+    float* __restrict__ pdi = a.delta_i;
+    float* __restrict__ pge = a.g_e;
+    float* __restrict__ pgi = a.g_i;
+    float* __restrict__ pV = a.V;
+    int32_t* __restrict__ pref = a.ref;
+    const float de = pde[i], di = pdi[i], ge0 = pge[i], gi0 = pgi[i], V = pV[i];
+    const int32_t r = pref[i];
+    const float ge = __fadd_rn(__fmul_rn(ge0, p.decay_e), de);
+    const float gi = __fadd_rn(__fmul_rn(gi0, p.decay_i), di);
+    float cur;
+    if (p.coba) cur = __fadd_rn(__fmul_rn(ge, __fsub_rn(p.E_e, V)), __fmul_rn(gi, __fsub_rn(p.E_i, V)));
+    else cur = __fadd_rn(ge, gi);
+    const float drive = __fmul_rn(p.R, __fadd_rn(cur, p.I_ext));
+    const float num = __fadd_rn(__fsub_rn(p.V_rest, V), drive);
+    float Vn;
+    if (p.coba) {
+      const float f = __fmul_rn(num, p.inv_tau_m);
+      const float gsum = __fadd_rn(ge, gi);
+      const float J = __fmul_rn(-__fadd_rn(1.0f, __fmul_rn(p.R, gsum)), p.inv_tau_m);
+      const float gain = __fmul_rn(p.dt, exprel_once(__fmul_rn(p.dt, J)));
+      Vn = __fadd_rn(V, __fmul_rn(gain, f));
+    } else {
+      Vn = __fadd_rn(V, __fmul_rn(p.cuba_gain, num));
+    }
+    const bool refractory = r > 0;
+    if (refractory) Vn = V;
+    spk = (Vn >= p.V_th) && !refractory;
+    if (de != 0.0f) pde[i] = 0.0f;
+    if (di != 0.0f) pdi[i] = 0.0f;
+    pge[i] = ge;
+    pgi[i] = gi;
+    pV[i] = spk ? p.V_reset : Vn;
+    const int32_t rn = spk ? p.ref_steps : (r > 0 ? r - 1 : 0);
+    if (rn != r) pref[i] = rn;
+  }
+  *spiked = spk;
+  return __ballot_sync(0xffffffffu, spk);
+}
+
+__device__ __forceinline__ void append_spikes(uint32_t m, bool spk, int lane, int64_t gid, int32_t* __restrict__ list) {
+  const int total = __popc(m);
+  if (!total) return;
+  int base = 0;
+  if (lane == 0) base = atomicAdd(list, total);
+  base = __shfl_sync(0xffffffffu, base, 0);
+  if (spk) list[1 + base + __popc(m & ((1u << lane) - 1u))] = (int32_t)gid;
+}
+
+// ---- one cooperative launch for many steps (single GPU) ------------------------
+__global__ void __launch_bounds__(256)
+net_run_kernel(NetDev a, int steps, int cur, uint32_t* __restrict__ raster, int32_t* __restrict__ spike_counts) {
+  cg::grid_group grid = cg::this_grid();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t words = (a.n_local + 31) >> 5;
+  for (int t = 0; t < steps; ++t) {
+    int32_t* lcur = cur ? a.list1 : a.list0;
+    int32_t* lnext = cur ? a.list0 : a.list1;
+    if (warp == 0 && lane == 0) lnext[0] = 0;
+    phase_scatter(a, lcur, warp, nwarps, lane);
+    grid.sync();
+    for (int64_t wd = warp; wd < words; wd += nwarps) {
+      bool spk;
+      const uint32_t m = update_word(a, wd, lane, &spk);
+      if (lane == 0) {
+        a.bits[wd] = m;
+        if (raster) raster[(int64_t)t * words + wd] = m;
+      }
+      append_spikes(m, spk, lane, wd * 32 + lane, lnext);
+    }
+    grid.sync();
+    if (spike_counts && warp == 0 && lane == 0) spike_counts[t] = lnext[0];
+    cur ^= 1;
+  }
+}
+
+// ---- split phases (multi-GPU driver) ----------------------------------------------
+__global__ void __launch_bounds__(256) net_scatter_kernel(NetDev a, int which) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  phase_scatter(a, which ? a.list1 : a.list0, warp, nwarps, lane);
+}
+
+__global__ void __launch_bounds__(256) net_update_kernel(NetDev a, int32_t* __restrict__ local_count) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t words = (a.n_local + 31) >> 5;
+  const int64_t word0 = a.first >> 5;
+  int mine = 0;
+  for (int64_t wd = warp; wd < words; wd += nwarps) {
+    bool spk;
+    const uint32_t m = update_word(a, wd, lane, &spk);
+    if (lane == 0) a.bits[word0 + wd] = m;
+    mine += __popc(m);
+  }
+  if (local_count && lane == 0 && mine) atomicAdd(local_count, mine);
+}
+
+// Compacts the packed spike words of the whole network into a list of global ids.
+__global__ void __launch_bounds__(256)
+net_list_kernel(const uint32_t* __restrict__ bits, int64_t n_global, int32_t* __restrict__ list) {
+  const int lane = threadIdx.x & 31;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int64_t words = (n_global + 31) >> 5;
+  for (int64_t g0 = tid - lane; g0 < words; g0 += nthreads) {
+    const int64_t g = g0 + lane;
+    uint32_t m = 0;
+    if (g < words) {
+      m = bits[g];
+      const int64_t left = n_global - g * 32;
+      if (left < 32) m &= (1u << left) - 1u;
+    }
+    // warp-aggregated reservation of popc(m) slots per lane
+    uint32_t cnt = __popc(m), incl = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+    uint32_t base = 0;
+    if (lane == 31 && total) base = (uint32_t)atomicAdd(list, (int32_t)total);
+    base = __shfl_sync(0xffffffffu, base, 31);
+    uint32_t pos = base + incl - cnt;
+    while (m) {
+      const int k = __ffs(m) - 1;
+      m &= m - 1;
+      list[1 + pos++] = (int32_t)(g * 32 + k);
+    }
+  }
+}
+
+static int make_proj(const bsx_conn_t* c, int chunk, ProjDev* out) {
+  int rc = check_conn(c);
+  if (rc) return rc;
+  out->rm = make_rowmap(c);
+  out->idx = c->indices;
+  out->w = c->weights;
+  out->hetero = c->hetero;
+  out->vec_ok = aligned16(c->indices) && (!c->hetero || aligned16(c->weights));
+  out->cpr = 1;
+  if (!c->indptr && c->conn_num > chunk) out->cpr = (int)((c->conn_num + chunk - 1) / chunk);
+  return BSX_OK;
+}
+
+static int make_net(const bsx_net_t* net, const bsx_lif_params_t* p, NetDev* a) {
+  if (!net) return fail(BSX_ERR_INVALID_ARG, "net is NULL");
+  if (net->n_global <= 0 || net->n_exc < 0 || net->n_exc > net->n_global || net->n_local < 0 ||
+      net->first < 0 || net->first + net->n_local > net->n_global)
+    return fail(BSX_ERR_INVALID_ARG, "inconsistent network sizes");
+  if (net->n_global > INT32_MAX) return fail(BSX_ERR_UNSUPPORTED, "n_global must fit int32");
+  if (net->first % 32) return fail(BSX_ERR_INVALID_ARG, "the first local neuron must be a multiple of 32");
+  if (net->exc.n_pre != net->n_exc || net->inh.n_pre != net->n_global - net->n_exc ||
+      net->exc.n_post != net->n_local || net->inh.n_post != net->n_local)
+    return fail(BSX_ERR_INVALID_ARG, "projection shapes do not match the network (rows: population, columns: local neurons)");
+  if (!net->V || !net->g_e || !net->g_i || !net->ref || !net->delta_e || !net->delta_i || !net->bits ||
+      !net->list[0] || !net->list[1])
+    return fail(BSX_ERR_INVALID_ARG, "a state buffer of the network is NULL");
+  a->chunk = 128;
+  // keep chunks-per-row small for very long rows
+  int64_t kmax = net->exc.conn_num > net->inh.conn_num ? net->exc.conn_num : net->inh.conn_num;
+  while ((kmax + a->chunk - 1) / a->chunk > 64) a->chunk *= 2;
+  int rc = make_proj(&net->exc, a->chunk, &a->exc);
+  if (rc) return rc;
+  rc = make_proj(&net->inh, a->chunk, &a->inh);
+  if (rc) return rc;
+  a->n_global = net->n_global;
+  a->n_exc = net->n_exc;
+  a->first = net->first;
+  a->n_local = net->n_local;
+  a->V = net->V; a->g_e = net->g_e; a->g_i = net->g_i; a->ref = net->ref;
+  a->delta_e = net->delta_e; a->delta_i = net->delta_i;
+  a->bits = net->bits;
+  a->list0 = net->list[0];
+  a->list1 = net->list[1];
+  if (p) a->p = *p;
+  return BSX_OK;
+}
+
+}  // namespace bsx
+
+using namespace bsx;
+
+extern "C" {
+
+int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t steps, int32_t cur_list,
+                uint32_t* raster, int32_t* spike_counts, int32_t blocks, bsx_stream_t stream) {
+  if (!params) return fail(BSX_ERR_INVALID_ARG, "params is NULL");
+  if (steps < 0 || (cur_list != 0 && cur_list != 1)) return fail(BSX_ERR_INVALID_ARG, "bad steps or list index");
+  NetDev a;
+  int rc = make_net(net, params, &a);
+  if (rc) return rc;
+  if (net->first != 0 || net->n_local != net->n_global)
+    return fail(BSX_ERR_INVALID_ARG, "bsx_net_run drives a whole network on one GPU (first = 0, n_local = n_global)");
+  if (steps == 0) return BSX_OK;
+  int sms = sm_count();
+  if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  int per_sm = 0;
+  BSX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, net_run_kernel, 256, 0));
+  if (per_sm < 1) return fail(BSX_ERR_CUDA, "the network kernel does not fit on an SM");
+  int64_t max_blocks = (int64_t)sms * (per_sm < 4 ? per_sm : 4);
+  int64_t want = blocks > 0 ? blocks : (net->n_local + 255) / 256;
+  if (want < 1) want = 1;
+  if (want > max_blocks) want = max_blocks;
+  int steps_i = steps, cur_i = cur_list;
+  void* args[] = {&a, &steps_i, &cur_i, &raster, &spike_counts};
+  BSX_CUDA(cudaLaunchCooperativeKernel((const void*)net_run_kernel, dim3((unsigned)want), dim3(256), args, 0,
+                                       as_stream(stream)));
+  return BSX_OK;
+}
+
+int bsx_net_scatter(const bsx_net_t* net, int32_t list_index, bsx_stream_t stream) {
+  if (list_index != 0 && list_index != 1) return fail(BSX_ERR_INVALID_ARG, "bad list index");
+  NetDev a;
+  int rc = make_net(net, nullptr, &a);
+  if (rc) return rc;
+  int sms = sm_count();
+  if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  net_scatter_kernel<<<(unsigned)(sms * 4), 256, 0, as_stream(stream)>>>(a, list_index);
+  BSX_LAUNCH_CHECK("net_scatter_kernel");
+  return BSX_OK;
+}
+
+int bsx_net_update(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t* local_count,
+                   bsx_stream_t stream) {
+  if (!params) return fail(BSX_ERR_INVALID_ARG, "params is NULL");
+  NetDev a;
+  int rc = make_net(net, params, &a);
+  if (rc) return rc;
+  if (net->n_local == 0) return BSX_OK;
+  int sms = sm_count();
+  if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  int64_t blocks = (net->n_local + 255) / 256;
+  if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
+  net_update_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(a, local_count);
+  BSX_LAUNCH_CHECK("net_update_kernel");
+  return BSX_OK;
+}
+
+int bsx_net_list_from_bits(const bsx_net_t* net, int32_t list_index, bsx_stream_t stream) {
+  if (list_index != 0 && list_index != 1) return fail(BSX_ERR_INVALID_ARG, "bad list index");
+  NetDev a;
+  int rc = make_net(net, nullptr, &a);
+  if (rc) return rc;
+  int sms = sm_count();
+  if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  int32_t* list = list_index ? a.list1 : a.list0;
+  BSX_CUDA(cudaMemsetAsync(list, 0, sizeof(int32_t), as_stream(stream)));
+  const int64_t words = (a.n_global + 31) >> 5;
+  int64_t blocks = (words + 255) / 256;
+  if (blocks > (int64_t)sms * 4) blocks = (int64_t)sms * 4;
+  if (blocks < 1) blocks = 1;
+  net_list_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(a.bits, a.n_global, list);
+  BSX_LAUNCH_CHECK("net_list_kernel");
+  return BSX_OK;
+}
+
+}  // extern "C"

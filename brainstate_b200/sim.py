@@ -1,0 +1,221 @@
+"""Excitatory/inhibitory spiking network driver over the fused step kernels.
+
+``EINet`` stands for the model the reference's examples assemble from
+``brainstate.nn.EventFixedProb`` and ``brainpy.state`` parts
+(``examples/400_CUBA_2005_bpu.py:36-66``: ``LIFRef`` neurons, two
+``AlignPostProj(comm=EventFixedProb, syn=Expon, out=CUBA|COBA)`` projections) and
+for the loop ``brainstate.transform.for_loop(net.update, times)``
+(``brainstate/transform/_loop_collect_return.py:488-572``): ``run(steps)`` advances
+the network and returns the bit-packed spike raster.
+
+On one GPU all steps of a ``run`` are one cooperative kernel launch.  With a
+process group the postsynaptic neurons are split into contiguous blocks, one per
+rank; every rank keeps the synapses that target its block (a CSR block drawn from
+the same seeded stream as the full matrix) and the ranks exchange one all-gather of
+the packed spike words per step.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import BsxLifParams, BsxNet, check, lib
+from .event import CSR, FixedPostNumConn
+from .nn._event_fixedprob import EventFixedProb, _device
+
+__all__ = ['LIFParams', 'EINet', 'shard_bounds', 'words_per_rank', 'sharded_block', 'unpack_raster']
+
+
+@dataclass
+class LIFParams:
+    """Neuron and synapse constants (times in ms, potentials in mV)."""
+    dt: float = 0.1
+    tau_m: float = 20.
+    tau_e: float = 5.
+    tau_i: float = 10.
+    V_rest: float = -49.
+    V_th: float = -50.
+    V_reset: float = -60.
+    tau_ref: float = 5.
+    R: float = 1.
+    I_ext: float = 0.
+    E_e: float = 0.
+    E_i: float = -80.
+    coba: bool = False
+
+    def struct(self) -> BsxLifParams:
+        p = BsxLifParams()
+        f32 = np.float32
+        p.dt = f32(self.dt)
+        p.decay_e = f32(math.exp(-self.dt / self.tau_e))
+        p.decay_i = f32(math.exp(-self.dt / self.tau_i))
+        p.inv_tau_m = f32(1.0 / self.tau_m)
+        p.cuba_gain = f32(-math.expm1(-self.dt / self.tau_m))
+        p.V_rest, p.V_th, p.V_reset = f32(self.V_rest), f32(self.V_th), f32(self.V_reset)
+        p.R, p.I_ext = f32(self.R), f32(self.I_ext)
+        p.E_e, p.E_i = f32(self.E_e), f32(self.E_i)
+        p.ref_steps = int(round(self.tau_ref / self.dt))
+        p.coba = int(self.coba)
+        return p
+
+
+def words_per_rank(n: int, world: int) -> int:
+    """Spike words every rank contributes to the all-gather (the last ranks' share
+    may be partly or wholly padding)."""
+    words = (n + 31) // 32
+    return (words + world - 1) // world
+
+
+def shard_bounds(n: int, world: int, rank: int):
+    """Contiguous block ``[first, last)`` of ``n`` neurons owned by ``rank``: whole
+    32-bit spike words, ``words_per_rank`` of them per rank, clipped to ``n``."""
+    wpr = words_per_rank(n, world)
+    return min(n, 32 * rank * wpr), min(n, 32 * (rank + 1) * wpr)
+
+
+def sharded_block(seed: int, n_pre: int, n_post: int, conn_num: int, col0: int, col1: int):
+    """CSR block (host arrays) of the fixed-number matrix ``RandomState(seed).randint(0,
+    n_post, (n_pre, conn_num))`` restricted to targets in ``[col0, col1)``; column
+    ids are local (minus ``col0``).  Returns ``(indices int32, indptr int64)``."""
+    buf = np.empty(n_pre * conn_num, np.int32)
+    counts = np.empty(n_pre, np.int32)
+    n = lib().bsx_host_fixed_num_indices(C.c_uint32(int(seed) & 0xffffffff), n_pre, n_post, conn_num, 0, n_pre,
+                                        col0, col1, buf.ctypes.data, counts.ctypes.data)
+    check(int(n))
+    indptr = np.zeros(n_pre + 1, np.int64)
+    np.cumsum(counts, out=indptr[1:])
+    return buf[:n].copy(), indptr
+
+
+class EINet:
+    """E/I network of LIF neurons with exponential synapses.
+
+    Parameters
+    ----------
+    n_exc, n_inh : population sizes; global ids ``[0, n_exc)`` are excitatory.
+    conn_num : connection probability (float) or number of targets per neuron (int),
+        as in ``EventFixedProb``.
+    w_e, w_i : homogeneous synaptic weights of the two projections.
+    seed_e, seed_i : connectivity seeds (``EventFixedProb(..., seed=...)``).
+    V0 : initial membrane potentials, ``(n_exc + n_inh,)``.
+    group : optional ``torch.distributed`` process group; with more than one rank
+        the postsynaptic neurons are sharded.
+    """
+
+    def __init__(self, n_exc: int, n_inh: int, conn_num, w_e: float, w_i: float, *, seed_e: int, seed_i: int,
+                 V0, params: Optional[LIFParams] = None, device=None, group=None):
+        self.n_exc, self.n_inh = int(n_exc), int(n_inh)
+        self.n = self.n_exc + self.n_inh
+        self.params = params or LIFParams()
+        self.dev = _device(device)
+        self.group = group
+        self.world, self.rank = 1, 0
+        if group is not None:
+            import torch.distributed as dist
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.first, self.last = shard_bounds(self.n, self.world, self.rank) if self.world > 1 else (0, self.n)
+        self.n_local = self.last - self.first
+        K = conn_num if isinstance(conn_num, int) else int(self.n * conn_num)
+        self.conn_num = K
+        dev = self.dev
+        if self.world == 1:
+            self.E = EventFixedProb(self.n_exc, self.n, K, float(w_e), seed=seed_e, device=dev)
+            self.I = EventFixedProb(self.n_inh, self.n, K, float(w_i), seed=seed_i, device=dev)
+            self.conn_e, self.conn_i = self.E.conn, self.I.conn
+        else:
+            ie, pe = sharded_block(seed_e, self.n_exc, self.n, K, self.first, self.last)
+            ii, pi = sharded_block(seed_i, self.n_inh, self.n, K, self.first, self.last)
+            self.conn_e = CSR((float(w_e), torch.from_numpy(ie).to(dev), torch.from_numpy(pe).to(dev)),
+                              shape=(self.n_exc, self.n_local))
+            self.conn_i = CSR((float(w_i), torch.from_numpy(ii).to(dev), torch.from_numpy(pi).to(dev)),
+                              shape=(self.n_inh, self.n_local))
+        V0 = np.asarray(V0, np.float32)
+        assert V0.shape == (self.n,)
+        self.V = torch.from_numpy(V0[self.first:self.last].copy()).to(dev)
+        z = lambda dt: torch.zeros(self.n_local, dtype=dt, device=dev)
+        self.g_e, self.g_i, self.delta_e, self.delta_i = z(torch.float32), z(torch.float32), z(torch.float32), z(torch.float32)
+        self.ref = z(torch.int32)
+        self.words = (self.n + 31) // 32
+        self.wpr = words_per_rank(self.n, self.world)
+        self.bits = torch.zeros(self.wpr * self.world, dtype=torch.int32, device=dev)
+        self.lists = [torch.zeros(self.n + 1, dtype=torch.int32, device=dev) for _ in range(2)]
+        self.cur = 0
+        self.step_count = 0
+        self._pstruct = self.params.struct()
+        self._net = self._make_struct()
+
+    def _make_struct(self) -> BsxNet:
+        s = BsxNet()
+        s.n_global, s.n_exc, s.first, s.n_local = self.n, self.n_exc, self.first, self.n_local
+        self._se, self._si = self.conn_e._struct(), self.conn_i._struct()
+        s.exc, s.inh = self._se, self._si
+        s.V, s.g_e, s.g_i, s.ref = self.V.data_ptr(), self.g_e.data_ptr(), self.g_i.data_ptr(), self.ref.data_ptr()
+        s.delta_e, s.delta_i = self.delta_e.data_ptr(), self.delta_i.data_ptr()
+        s.bits = self.bits.data_ptr()
+        s.list[0], s.list[1] = self.lists[0].data_ptr(), self.lists[1].data_ptr()
+        return s
+
+    # ------------------------------------------------------------------
+    def run(self, steps: int, record: bool = True, blocks: int = 0):
+        """Advances ``steps`` steps.  Returns ``(raster, counts)``: the packed spike
+        words ``(steps, ceil(n/32))`` int32 (``None`` without ``record``) and the
+        number of spikes of every step ``(steps,)`` int32."""
+        if self.world > 1:
+            return self._run_sharded(steps, record)
+        dev = self.dev
+        raster = torch.empty((steps, self.words), dtype=torch.int32, device=dev) if record else None
+        counts = torch.empty(steps, dtype=torch.int32, device=dev)
+        check(lib().bsx_net_run(C.byref(self._net), C.byref(self._pstruct), steps, self.cur,
+                                _lib.ptr(raster), counts.data_ptr(), blocks, _lib.current_stream()))
+        self.cur = (self.cur + steps) & 1
+        self.step_count += steps
+        return raster, counts
+
+    def _run_sharded(self, steps: int, record: bool):
+        import torch.distributed as dist
+        dev = self.dev
+        l = lib()
+        stream = _lib.current_stream()
+        raster = torch.empty((steps, self.words), dtype=torch.int32, device=dev) if record else None
+        counts = torch.zeros(steps, dtype=torch.int32, device=dev)
+        wpr = self.wpr
+        mine = self.bits[self.rank * wpr:(self.rank + 1) * wpr]
+        net, ps = C.byref(self._net), C.byref(self._pstruct)
+        for t in range(steps):
+            nxt = self.cur ^ 1
+            # scatter the spikes of the previous step (all ranks' spikes, this rank's targets)
+            check(l.bsx_net_scatter(net, self.cur, stream))
+            check(l.bsx_net_update(net, ps, counts[t:t + 1].data_ptr(), stream))
+            dist.all_gather_into_tensor(self.bits, mine, group=self.group)
+            check(l.bsx_net_list_from_bits(net, nxt, stream))
+            if record:
+                raster[t].copy_(self.bits[:self.words])
+            self.cur = nxt
+        self.step_count += steps
+        dist.all_reduce(counts, group=self.group)
+        return raster, counts
+
+    # ------------------------------------------------------------------
+    def spikes(self) -> torch.Tensor:
+        """Spikes of the latest step as a bool vector over the whole network."""
+        w = self.bits[:self.words].cpu().numpy().view(np.uint32)
+        b = np.unpackbits(w.view(np.uint8), bitorder='little')[:self.n].astype(bool)
+        return torch.from_numpy(b)
+
+    def state(self):
+        """Local state tensors (for checkpoints): V, g_e, g_i, ref, bits, current list."""
+        return {'V': self.V, 'g_e': self.g_e, 'g_i': self.g_i, 'ref': self.ref, 'bits': self.bits,
+                'list': self.lists[self.cur], 'step': self.step_count}
+
+
+def unpack_raster(raster: torch.Tensor, n: int) -> np.ndarray:
+    """``(steps, words)`` packed words -> ``(steps, n)`` bool array (host)."""
+    w = raster.cpu().numpy().view(np.uint32)
+    bits = np.unpackbits(w.view(np.uint8).reshape(w.shape[0], -1), axis=1, bitorder='little')
+    return bits[:, :n].astype(bool)

@@ -188,10 +188,11 @@ int bsx_event_matvec(const bsx_conn_t* conn, const void* spikes, int spike_forma
                      float* out, void* workspace, size_t workspace_bytes, bsx_stream_t stream);
 /* Same, with explicit launch geometry for tuning (0 = default).  mask_mode: 1 spike
  * words staged in shared memory by a bulk-async (TMA) copy, 2 staged by ordinary
- * loads, 3 read from global memory. */
+ * loads, 3 read from global memory.  unroll: 128-bit index loads in flight per lane
+ * (1, 2, 4 or 6). */
 int bsx_event_matvec_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                            float* out, void* workspace, size_t workspace_bytes, int blocks_per_sm,
-                           int mask_mode, bsx_stream_t stream);
+                           int mask_mode, int unroll, bsx_stream_t stream);
 
 /*
  * y = conn @ v for float v: y[b,i] = sum_k w[i,k] * v[b, idx[i,k]].
@@ -221,6 +222,65 @@ int bsx_dense_event_vecmat(const void* spikes, int spike_format, const float* we
  */
 int bsx_vecmat_vjp(const bsx_conn_t* conn, const void* x, int x_format, int event,
                    const float* ct, int64_t batch, float* dx, float* dw, bsx_stream_t stream);
+
+/* ---- fused E/I network step ------------------------------------------------ */
+/*
+ * Constants of the leaky integrate-and-fire neurons and exponential synapses of
+ * an excitatory/inhibitory network.  The host computes the exponentials in double
+ * and rounds once, so host and device use the same float32 factors.
+ */
+typedef struct bsx_lif_params {
+  float dt;          /* step */
+  float decay_e;     /* exp(-dt/tau_e) */
+  float decay_i;     /* exp(-dt/tau_i) */
+  float inv_tau_m;   /* 1/tau_m */
+  float cuba_gain;   /* 1 - exp(-dt/tau_m) */
+  float V_rest, V_th, V_reset;
+  float R, I_ext;    /* membrane resistance, constant external current */
+  float E_e, E_i;    /* reversal potentials (conductance-based only) */
+  int32_t ref_steps; /* refractory period in steps */
+  int32_t coba;      /* 0: current-based (CUBA), 1: conductance-based (COBA) */
+} bsx_lif_params_t;
+
+/*
+ * One rank's part of an E/I network.  Global neuron ids [0, n_exc) are excitatory,
+ * [n_exc, n_global) inhibitory.  The rank owns neurons [first, first + n_local)
+ * (first a multiple of 32) and, of both projections, the synapses that TARGET
+ * them: `exc` has n_exc rows, `inh` has n_global - n_exc rows, both have n_local
+ * columns (local ids).  On one GPU first = 0 and n_local = n_global.
+ */
+typedef struct bsx_net {
+  int64_t n_global, n_exc, first, n_local;
+  bsx_conn_t exc, inh;
+  float* V;            /* (n_local) membrane potential */
+  float* g_e;          /* (n_local) excitatory synaptic variable */
+  float* g_i;          /* (n_local) inhibitory synaptic variable */
+  int32_t* ref;        /* (n_local) remaining refractory steps */
+  float* delta_e;      /* (n_local) scatter target, zero between steps */
+  float* delta_i;      /* (n_local) */
+  uint32_t* bits;      /* (ceil(n_global/32)) packed spikes of the latest step, whole network */
+  int32_t* list[2];    /* two spike lists, each [count, global ids...] with room for n_global ids */
+} bsx_net_t;
+
+/*
+ * Runs `steps` steps of a whole network on one GPU in ONE cooperative launch.
+ * This fuses what the reference's examples run as separate operators per step
+ * (examples/400_CUBA_2005_bpu.py:60-66: two EventFixedProb products, two Expon
+ * updates, CUBA/COBA output, LIFRef update).  list[cur_list] holds the spikes of
+ * the step before the first one (count 0 at the start of a run); after the call
+ * the latest spikes are in list[(cur_list + steps) & 1] and in `bits`.
+ * raster (may be NULL): (steps, ceil(n/32)) packed spike words; spike_counts (may
+ * be NULL): spikes per step.  blocks: grid size, 0 = chosen from the network size.
+ */
+int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t steps, int32_t cur_list,
+                uint32_t* raster, int32_t* spike_counts, int32_t blocks, bsx_stream_t stream);
+/* The pieces of one step, for the multi-GPU driver (update -> exchange of the
+ * spike words -> list -> scatter).  bsx_net_update writes the rank's words of
+ * `bits` and adds its spike count to *local_count (may be NULL). */
+int bsx_net_update(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t* local_count,
+                   bsx_stream_t stream);
+int bsx_net_list_from_bits(const bsx_net_t* net, int32_t list_index, bsx_stream_t stream);
+int bsx_net_scatter(const bsx_net_t* net, int32_t list_index, bsx_stream_t stream);
 
 /* ---- small utilities ---------------------------------------------------- */
 int bsx_fill_f32(float* dst, int64_t n, float value, bsx_stream_t stream);

@@ -298,9 +298,12 @@ class EINetOracle:
     def __init__(self, n_exc, n_inh, idx_e, w_e, idx_i, w_i, *, coba=False,
                  dt=0.1, tau_m=20., tau_e=5., tau_i=10., V_rest=-49., V_th=-50.,
                  V_reset=-60., tau_ref=5., R=1., I_ext=0., E_e=0., E_i=-80.,
-                 V0=None, indptr_e=None, indptr_i=None):
+                 V0=None, indptr_e=None, indptr_i=None, n_local=None):
+        # n_local: number of neurons whose state this instance holds (a postsynaptic
+        # shard); the index arrays then hold local column ids.  Default: the whole network.
         self.n_exc, self.n_inh = n_exc, n_inh
-        self.n = n_exc + n_inh
+        self.n_global = n_exc + n_inh
+        self.n = self.n_global if n_local is None else n_local
         self.idx_e, self.w_e, self.idx_i, self.w_i = idx_e, w_e, idx_i, w_i
         self.indptr_e, self.indptr_i = indptr_e, indptr_i
         self.coba = coba
@@ -319,8 +322,11 @@ class EINetOracle:
         self.ref = np.zeros(self.n, np.int32)       # remaining refractory steps
         self.spk = np.zeros(self.n, bool)
 
-    def step(self):
-        s = self.spk
+    def step(self, s_global=None):
+        """One step.  ``s_global``: spikes of the previous step of the WHOLE network
+        (needed by a shard); by default the instance's own previous spikes."""
+        s = self.spk if s_global is None else np.asarray(s_global, bool)
+        assert s.shape == (self.n_global,)
         dg_e = event_vecmat(s[:self.n_exc], self.idx_e, self.w_e, self.n, self.indptr_e)
         dg_i = event_vecmat(s[self.n_exc:], self.idx_i, self.w_i, self.n, self.indptr_i)
         self.g_e = (self.g_e * self.decay_e).astype(F32) + dg_e

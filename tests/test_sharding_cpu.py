@@ -1,0 +1,98 @@
+"""CPU: host-side logic of the postsynaptic sharding — block bounds, the shard's
+CSR block drawn from the one seeded stream, and the per-step exchange of packed
+spike words, run as two gloo ranks whose arithmetic is the CPU oracle."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import event_oracle as eo
+
+
+@pytest.mark.parametrize('n,world', [(4000, 1), (4000, 2), (4000, 8), (1000000, 8), (96, 4), (33, 2), (31, 3)])
+def test_shard_bounds_partition_whole_words(n, world):
+    from brainstate_b200.sim import shard_bounds, words_per_rank
+    wpr = words_per_rank(n, world)
+    assert wpr * world * 32 >= n
+    prev = 0
+    for r in range(world):
+        a, b = shard_bounds(n, world, r)
+        assert a == prev and a <= b <= n and a % 32 == 0 or a == n
+        assert b - a <= 32 * wpr
+        prev = b
+    assert prev == n
+
+
+def test_sharded_block_is_the_column_filter_of_the_full_matrix(bsx):
+    from brainstate_b200.sim import sharded_block, shard_bounds
+    seed, n_pre, n_post, K = 300, 257, 1000, 23
+    full = np.random.RandomState(seed).randint(0, n_post, size=(n_pre, K)).astype(np.int32)
+    total = 0
+    for world in (2, 3):
+        for r in range(world):
+            c0, c1 = shard_bounds(n_post, world, r)
+            idx, indptr = sharded_block(seed, n_pre, n_post, K, c0, c1)
+            keep = (full >= c0) & (full < c1)
+            assert np.array_equal(np.diff(indptr), keep.sum(axis=1))
+            assert np.array_equal(idx, full[keep] - c0)            # row-major order is preserved
+            total += idx.size
+    assert total == 2 * full.size
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(('127.0.0.1', 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _rank_main(rank, world, port, steps, out_dir):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        from brainstate_b200.sim import shard_bounds, sharded_block, words_per_rank
+        n_exc, n_inh, K = 320, 96, 12
+        n = n_exc + n_inh
+        first, last = shard_bounds(n, world, rank)
+        ie, pe = sharded_block(100, n_exc, n, K, first, last)
+        ii, pi = sharded_block(101, n_inh, n, K, first, last)
+        V0 = np.random.RandomState(102).uniform(-60, -50, n).astype(np.float32)
+        net = eo.EINetOracle(n_exc, n_inh, ie, np.float32(1.62), ii, np.float32(-9.0), V0=V0[first:last],
+                             indptr_e=pe, indptr_i=pi, n_local=last - first)
+        wpr = words_per_rank(n, world)
+        words = (n + 31) // 32
+        bits = torch.zeros(wpr * world, dtype=torch.int32)
+        s_global = np.zeros(n, bool)
+        raster = np.zeros((steps, n), bool)
+        for t in range(steps):
+            spk_local, _, _ = net.step(s_global)
+            mine = np.zeros(wpr, np.uint32)
+            packed = eo.pack_bits(spk_local)
+            mine[:packed.size] = packed
+            dist.all_gather_into_tensor(bits, torch.from_numpy(mine.view(np.int32)))
+            s_global = eo.unpack_bits(bits.numpy().view(np.uint32)[:words], n)
+            raster[t] = s_global
+        if rank == 0:
+            np.save(os.path.join(out_dir, 'raster.npy'), raster)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_reproduce_the_unsharded_raster(tmp_path, bsx):
+    steps = 150
+    world = 2
+    mp.spawn(_rank_main, args=(world, _free_port(), steps, str(tmp_path)), nprocs=world, join=True)
+    got = np.load(tmp_path / 'raster.npy')
+    n_exc, n_inh, K = 320, 96, 12
+    n = n_exc + n_inh
+    V0 = np.random.RandomState(102).uniform(-60, -50, n).astype(np.float32)
+    ref = eo.EINetOracle(n_exc, n_inh, eo.fixed_num_indices(100, n_exc, n, K), np.float32(1.62),
+                         eo.fixed_num_indices(101, n_inh, n, K), np.float32(-9.0), V0=V0).run(steps)
+    assert ref.sum() > 20
+    assert np.array_equal(got, ref)
