@@ -216,8 +216,11 @@ class DevicePass:
         self.bits = torch.empty((vectors, self.words), dtype=torch.int32, device=dev)
         self.ws_bytes = self.lib.bsx_event_vecmat_workspace_bytes(vectors, n)
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=dev)
-        self.launches_per_pass = 2 + 1 + vectors     # compact + scatter, pack, T gathers
-        self.ev0 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        self.mv_ws_bytes = self.lib.bsx_event_matvec_workspace_bytes(vectors, n)
+        self.mv_ws = torch.empty(self.mv_ws_bytes, dtype=torch.uint8, device=dev)
+        self.passes = (vectors + 15) // 16
+        # compact + scatter; transpose-pack + one gather pass per 16 vectors
+        self.launches_per_pass = 2 + 1 + self.passes
 
     def vecmat(self, spk_dev, stream):
         self._lib.check(self.lib.bsx_event_vecmat(C.byref(self.st), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
@@ -225,14 +228,9 @@ class DevicePass:
                                                   self.ws_bytes, stream))
 
     def matvec(self, spk_dev, stream):
-        lib, _lib = self.lib, self._lib
-        _lib.check(lib.bsx_pack_spikes(spk_dev.data_ptr(), _lib.SPK_BOOL8, self.T, self.n,
-                                       self.bits.data_ptr(), stream))
-        row_bytes = self.words * 4
-        for t in range(self.T):
-            _lib.check(lib.bsx_event_matvec(C.byref(self.st), self.bits.data_ptr() + t * row_bytes,
-                                            _lib.SPK_BITS32, 1, self.y_matvec.data_ptr() + t * self.n * 4,
-                                            None, 0, stream))
+        self._lib.check(self.lib.bsx_event_matvec(C.byref(self.st), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
+                                                  self.T, self.y_matvec.data_ptr(), self.mv_ws.data_ptr(),
+                                                  self.mv_ws_bytes, stream))
 
     def run(self, spk_dev, stream):
         self.vecmat(spk_dev, stream)
@@ -270,8 +268,13 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- device-resident timing -------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
+    # at least 3 warm-up steps, and enough of them for the SM clock to leave idle
+    t_w, n_w = time.perf_counter(), 0
+    while n_w < (args.warmup if args.profile else max(args.warmup, 3)) or (not args.profile and time.perf_counter() - t_w < 0.5):
         dp.run(spk_dev, stream)
+        n_w += 1
+        if n_w % 8 == 0:
+            torch.cuda.synchronize()
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -341,21 +344,38 @@ def run_ours(args):
             dist.destroy_process_group()
         return 0
 
-    # ---- roofline of the dominant kernel (the gather event matvec) ----------------
+    # ---- roofline of the two kernels of a step; the dominant one is reported first --
     peak, peak_kind = measured_hbm_peak()
     nnz = n * K
-    mean_events = float(spk.sum()) * K / T
-    bytes_per_launch = nnz * 4 + mean_events * 4 + n / 8 + 4 * n
-    avg_launch_s = (ms_matvec * 1e-3) / (args.steps * T)      # includes the per-pass pack launch (<1 %)
-    achieved = bytes_per_launch / avg_launch_s / 1e9
-    roofline = {'bound': 'hbm', 'kernel': 'event_matvec_kernel<hetero, smem mask>', 'achieved': achieved,
-                'peak': peak, 'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': achieved / peak,
-                'bytes_per_launch': bytes_per_launch, 'avg_launch_us': avg_launch_s * 1e6,
-                'share_of_step': ms_matvec / ms_total, 'traffic': None}
-    prof = os.path.join(ROOT, 'profiles', 'event_matvec_traffic.json')
+    events_vec = float(spk.sum()) * K                      # events of one product over the batch
+    # gather: one launch = one pass over the indices for 16 vectors
+    g_bytes = nnz * 4 + (events_vec / dp.passes) * 4 + n * 2 + min(T, 16) * 4 * n
+    g_launch_s = (ms_matvec * 1e-3) / (args.steps * dp.passes)   # includes the transpose-pack launch (~2 %)
+    # scatter: one launch = all T vectors
+    ms_vecmat = ms_total - ms_matvec
+    s_bytes = events_vec * 8 + T * (n + 4 * n)
+    s_launch_s = (ms_vecmat * 1e-3) / args.steps
+
+    def roof(kernel, nbytes, sec, share, note):
+        a = nbytes / sec / 1e9
+        return {'bound': 'hbm', 'kernel': kernel, 'achieved': a, 'peak': peak, 'peak_kind': peak_kind,
+                'unit': 'GB/s', 'frac': a / peak, 'bytes_per_launch': nbytes, 'avg_launch_us': sec * 1e6,
+                'share_of_step': share, 'traffic': None, 'note': note}
+
+    r_g = roof('event_matvec_b16_kernel<hetero>', g_bytes, g_launch_s, ms_matvec / ms_total,
+               'W@spike, 16 vectors per pass over the indices; limited by shared-memory bit tests and '
+               'instruction issue, see DESIGN.md')
+    r_s = roof('scatter_queue_kernel<hetero> (+compact)', s_bytes, s_launch_s, ms_vecmat / ms_total,
+               'spike@W; limited by the L2 rate of red.global.add.f32, not by HBM')
+    roofline, roofline_2 = (r_g, r_s) if ms_matvec >= ms_vecmat else (r_s, r_g)
+    prof = os.path.join(ROOT, 'profiles', 'traffic.json')
     if os.path.exists(prof):
         try:
-            roofline['traffic'] = float(json.load(open(prof))['dram_bytes_per_launch'])
+            tr = json.load(open(prof))
+            for r in (roofline, roofline_2):
+                key = r['kernel'].split('<')[0].split(' ')[0]
+                if key in tr:
+                    r['traffic'] = float(tr[key])
         except Exception:
             pass
 
@@ -372,6 +392,7 @@ def run_ours(args):
                 'd2h_bytes_per_step': int(2 * T * n * 4), 'steps': e2e_steps},
         'gpu_launches': int(dp.launches_per_pass * args.steps),
         'roofline': roofline,
+        'roofline_other_kernel': roofline_2,
         'cpu_baseline': cpu,
         'events_per_step': events_all,
     }
@@ -410,8 +431,15 @@ def run_cases(torch, dev, dp, idx, w, peak):
                     _lib.check(lib.bsx_event_matvec(C.byref(st), dp.bits.data_ptr() + t * dp.words * 4, _lib.SPK_BITS32,
                                                     1, dp.y_matvec.data_ptr() + t * n * 4, None, 0, stream))
 
+            def matvec_b16():
+                _lib.check(lib.bsx_event_matvec(C.byref(st), sd.data_ptr(), _lib.SPK_BOOL8, T, dp.y_matvec.data_ptr(),
+                                                dp.mv_ws.data_ptr(), dp.mv_ws_bytes, stream))
+
             for prod, fn, alg in (('spike@W scatter', vecmat, events * (4 + 4 * h) + T * (n + 4 * n)),
-                                  ('W@spike gather', matvec, T * (n * K * 4 + n / 8 + 4 * n) + events * 4 * h)):
+                                  ('W@spike gather, one vector per pass', matvec,
+                                   T * (n * K * 4 + n / 8 + 4 * n) + events * 4 * h),
+                                  ('W@spike gather, 16 vectors per pass', matvec_b16,
+                                   dp.passes * (n * K * 4 + 2 * n) + T * 4 * n + events * 4 * h)):
                 for _ in range(3):
                     fn()
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -90,6 +90,8 @@ SIGNATURES = {
     'bsx_event_matvec_tuned': (_i32, [_connp, _vp, _i32, _i64, _vp, _vp, _sz, _i32, _i32, _i32, _vp]),
     'bsx_float_matvec': (_i32, [_connp, _vp, _i64, _vp, _vp]),
     'bsx_vecmat_vjp': (_i32, [_connp, _vp, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
+    'bsx_vecmat_vjp_batched_workspace_bytes': (_sz, [_i64, _i64]),
+    'bsx_vecmat_vjp_batched': (_i32, [_connp, _vp, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     'bsx_dense_event_vecmat': (_i32, [_vp, _i32, _vp, _i64, _i64, _i64, _vp, _vp]),
     'bsx_net_run': (_i32, [_netp, _lifp, _i32, _i32, _vp, _vp, _i32, _vp]),
     'bsx_net_update': (_i32, [_netp, _lifp, _vp, _vp]),

@@ -282,10 +282,16 @@ using namespace bsx;
 
 extern "C" {
 
-size_t bsx_event_matvec_workspace_bytes(int64_t batch, int64_t n_post) {
-  if (batch < 0 || n_post < 0) return 0;
+static size_t packed_words_bytes(int64_t batch, int64_t n_post) {
   size_t b = sizeof(uint32_t) * (size_t)batch * (size_t)((n_post + 31) / 32);
   return (b + 255) & ~size_t(255);
+}
+
+size_t bsx_event_matvec_workspace_bytes(int64_t batch, int64_t n_post) {
+  if (batch < 0 || n_post < 0) return 0;
+  const size_t a = packed_words_bytes(batch, n_post);
+  const size_t b = (batch >= 2 && b16_fits(n_post)) ? b16_mask_bytes(batch, n_post) : 0;
+  return a > b ? a : b;
 }
 
 int bsx_event_matvec_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
@@ -300,14 +306,22 @@ int bsx_event_matvec_tuned(const bsx_conn_t* conn, const void* spikes, int spike
   const bool empty = !conn->indptr && conn->conn_num == 0;
   if (empty || conn->n_post == 0) return launch_zero(out, batch * conn->n_pre, st);
   if (!spikes) return fail(BSX_ERR_INVALID_ARG, "spikes is NULL");
+  if (spike_format != BSX_SPK_BITS32 && spike_format != BSX_SPK_BOOL8 && spike_format != BSX_SPK_F32)
+    return fail(BSX_ERR_INVALID_ARG, "event matvec takes BOOL8, F32 or BITS32 spikes");
+  // two or more vectors: one pass over the indices serves 16 vectors (mask_mode 4 opts out)
+  if (batch >= 2 && mask_mode != 4 && b16_fits(conn->n_post) && workspace &&
+      (reinterpret_cast<uintptr_t>(workspace) & 15) == 0 &&
+      workspace_bytes >= b16_mask_bytes(batch, conn->n_post))
+    return launch_event_matvec_b16(conn, spikes, spike_format, batch, out, workspace,
+                                   mask_mode == 5 ? 1 : (mask_mode == 6 ? 2 : 0), st);
   const int64_t words = (conn->n_post + 31) / 32;
   const uint32_t* bits;
   if (spike_format == BSX_SPK_BITS32) {
     bits = static_cast<const uint32_t*>(spikes);
   } else if (spike_format == BSX_SPK_BOOL8 || spike_format == BSX_SPK_F32) {
-    if (!workspace || workspace_bytes < bsx_event_matvec_workspace_bytes(batch, conn->n_post))
+    if (!workspace || workspace_bytes < packed_words_bytes(batch, conn->n_post))
       return fail(BSX_ERR_WORKSPACE, "event matvec needs %zu workspace bytes for the packed spikes",
-                  bsx_event_matvec_workspace_bytes(batch, conn->n_post));
+                  packed_words_bytes(batch, conn->n_post));
     rc = launch_pack(spikes, spike_format, batch, conn->n_post, static_cast<uint32_t*>(workspace), st);
     if (rc) return rc;
     bits = static_cast<const uint32_t*>(workspace);

@@ -20,4 +20,10 @@ int vecmat_common(const bsx_conn_t* conn, const void* in, int format, const floa
                   float* out, int accumulate, void* ws, size_t ws_bytes, int chunk, int blocks_per_sm,
                   cudaStream_t st);
 
+// Batched event matvec, 16 spike vectors per pass over the indices (gather_batched.cu).
+size_t b16_mask_bytes(int64_t batch, int64_t n_post);
+bool b16_fits(int64_t n_post);
+int launch_event_matvec_b16(const bsx_conn_t* conn, const void* spikes, int format, int64_t batch, float* out,
+                            void* workspace, int weight_mode, cudaStream_t st);
+
 }  // namespace bsx

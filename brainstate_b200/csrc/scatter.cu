@@ -23,6 +23,12 @@ scatter_queue_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   const int64_t count = *count_ptr;
+  // Few active rows: small chunks spread each row over many warps (latency).  Many:
+  // eight times larger chunks, fewer and longer streams per warp (throughput).
+  if (chunks_per_row > 1 && count * chunks_per_row > 4 * nwarps) {
+    chunk *= 8;
+    chunks_per_row = (chunks_per_row + 7) >> 3;
+  }
   const int64_t items = count * chunks_per_row;
   const float w0 = HETERO ? 1.0f : __ldg(w);
   for (int64_t it = warp; it < items; it += nwarps) {

@@ -1,0 +1,208 @@
+// Reverse mode of y = x @ W for a batch of inputs (the training step of the batched
+// event matmul): one pass over the indices produces
+//   dx[b, i] = sum_k w[i,k] ct[b, idx[i,k]]                 (dense, every b)
+//   dw[i, k] = sum_b a[b,i] ct[b, idx[i,k]]                 (heterogeneous)
+//   dw       = sum_b sum_i a[b,i] sum_k ct[b, idx[i,k]]     (homogeneous)
+// with a = x or the event indicator [x != 0].
+//
+// The cotangent is first transposed to batch-minor order (n_post, Bp) so that one
+// index fetches the values of 64 batch lanes as two coalesced 128-byte loads.  A
+// warp owns a row; lane l holds batch lanes l and l + 32.  Indices and weights are
+// loaded 32 at a time (coalesced) and broadcast by shuffles.  The weight cotangent
+// only touches the batch lanes where the row was active (a handful at the firing
+// rates of interest), found by ballot.  No atomics; fixed summation order.
+#include "common.cuh"
+#include "internal.cuh"
+
+namespace bsx {
+
+// (B, n) row-major -> (n, Bp) row-major, zero padded to Bp columns.
+__global__ void __launch_bounds__(256)
+transpose_pad_kernel(const float* __restrict__ src, int64_t B, int64_t n, int64_t Bp, float* __restrict__ dst) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int64_t n0 = (int64_t)blockIdx.x * 32, b0 = (int64_t)blockIdx.y * 32;
+  for (int r = ty; r < 32; r += 8) {
+    const int64_t b = b0 + r, j = n0 + tx;
+    tile[r][tx] = (b < B && j < n) ? src[b * n + j] : 0.f;
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const int64_t j = n0 + r, b = b0 + tx;
+    if (j < n && b < Bp) dst[j * Bp + b] = tile[tx][r];
+  }
+}
+
+template <int XFORMAT>
+__device__ __forceinline__ float act_at(const void* x, int64_t pos, bool event) {
+  float a = (XFORMAT == BSX_SPK_BOOL8) ? (float)(static_cast<const uint8_t*>(x)[pos] != 0)
+                                       : static_cast<const float*>(x)[pos];
+  if (event) a = (a != 0.f) ? 1.f : 0.f;
+  return a;
+}
+
+// One chunk of up to 64 batch lanes starting at b0.  first_chunk: dw is written,
+// later chunks add to it.
+template <bool HETERO, int XFORMAT>
+__global__ void __launch_bounds__(256)
+vjp_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
+                   const void* __restrict__ x, bool event, const float* __restrict__ ctT, int64_t Bp,
+                   int64_t B, int64_t b0, int64_t n_pre, float* __restrict__ dx, float* __restrict__ dw,
+                   bool first_chunk) {
+  __shared__ float block_part[8];
+  const int lane = threadIdx.x & 31;
+  const float w0 = HETERO ? 0.f : __ldg(w);
+  const int64_t blo = b0 + lane, bhi = b0 + 32 + lane;
+  const bool has_lo = blo < B, has_hi = bhi < B;
+  float homo_acc = 0.f;
+  const int64_t wstep = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < n_pre; row += wstep) {
+    float a_lo = 0.f, a_hi = 0.f;
+    if (dw) {
+      if (has_lo) a_lo = act_at<XFORMAT>(x, blo * n_pre + row, event);
+      if (has_hi) a_hi = act_at<XFORMAT>(x, bhi * n_pre + row, event);
+    }
+    const uint32_t act_lo = __ballot_sync(0xffffffffu, a_lo != 0.f);
+    const uint32_t act_hi = __ballot_sync(0xffffffffu, a_hi != 0.f);
+    const bool any_act = (act_lo | act_hi) != 0;
+    if (!dx && !any_act) {
+      if (dw && HETERO && first_chunk) {  // this row contributes nothing: clear its slice
+        int64_t s, e;
+        rm.range(row, s, e);
+        for (int64_t p = s + lane; p < e; p += 32) dw[p] = 0.f;
+      }
+      continue;
+    }
+    int64_t s, e;
+    rm.range(row, s, e);
+    float dx_lo = 0.f, dx_hi = 0.f;
+    for (int64_t pb = s; pb < e; pb += 32) {
+      const int64_t p = pb + lane;
+      int32_t j_l = 0;
+      float w_l = 0.f;
+      if (p < e) {
+        j_l = __ldg(idx + p);
+        w_l = HETERO ? __ldg(w + p) : 1.f;
+      }
+      const int cnt = (int)((e - pb) < 32 ? (e - pb) : 32);
+      float dw_l = 0.f;
+      for (int t = 0; t < cnt; ++t) {
+        const int32_t j = __shfl_sync(0xffffffffu, j_l, t);
+        const float ww = __shfl_sync(0xffffffffu, w_l, t);
+        const float* __restrict__ crow = ctT + (int64_t)j * Bp + b0;
+        const float c_lo = __ldg(crow + lane);          // padded columns are zero
+        const float c_hi = (b0 + 32 < Bp) ? __ldg(crow + 32 + lane) : 0.f;
+        dx_lo = fmaf(ww, c_lo, dx_lo);
+        dx_hi = fmaf(ww, c_hi, dx_hi);
+        if (any_act) {
+          float sacc = 0.f;  // sum over the active batch lanes, ascending b
+          uint32_t m = act_lo;
+          while (m) {
+            const int src = __ffs(m) - 1;
+            m &= m - 1;
+            sacc = fmaf(__shfl_sync(0xffffffffu, a_lo, src), __shfl_sync(0xffffffffu, c_lo, src), sacc);
+          }
+          m = act_hi;
+          while (m) {
+            const int src = __ffs(m) - 1;
+            m &= m - 1;
+            sacc = fmaf(__shfl_sync(0xffffffffu, a_hi, src), __shfl_sync(0xffffffffu, c_hi, src), sacc);
+          }
+          if (lane == t) dw_l = sacc;
+        }
+      }
+      if (dw && HETERO && p < e) {
+        if (first_chunk) dw[p] = dw_l; else dw[p] += dw_l;
+      }
+      if (dw && !HETERO && p < e) homo_acc += dw_l;
+    }
+    if (dx) {
+      if (!HETERO) { dx_lo *= w0; dx_hi *= w0; }
+      if (has_lo) dx[blo * n_pre + row] = dx_lo;
+      if (has_hi) dx[bhi * n_pre + row] = dx_hi;
+    }
+  }
+  if (dw && !HETERO) {
+    homo_acc = warp_sum(homo_acc);
+    if (lane == 0) block_part[threadIdx.x >> 5] = homo_acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int k = 0; k < (int)(blockDim.x >> 5); ++k) t += block_part[k];
+      if (t != 0.f) red_add(dw, t);
+    }
+  }
+}
+
+static size_t ctT_bytes(int64_t batch, int64_t n_post) {
+  const int64_t Bp = (batch + 31) & ~int64_t(31);
+  return ((size_t)n_post * (size_t)Bp * sizeof(float) + 255) & ~size_t(255);
+}
+
+}  // namespace bsx
+
+using namespace bsx;
+
+extern "C" {
+
+size_t bsx_vecmat_vjp_batched_workspace_bytes(int64_t batch, int64_t n_post) {
+  if (batch < 0 || n_post < 0) return 0;
+  return ctT_bytes(batch, n_post);
+}
+
+int bsx_vecmat_vjp_batched(const bsx_conn_t* conn, const void* x, int x_format, int event, const float* ct,
+                           int64_t batch, float* dx, float* dw, void* workspace, size_t workspace_bytes,
+                           bsx_stream_t stream) {
+  int rc = check_conn(conn);
+  if (rc) return rc;
+  if (batch < 0) return fail(BSX_ERR_INVALID_ARG, "negative batch");
+  if (x_format != BSX_SPK_BOOL8 && x_format != BSX_SPK_F32)
+    return fail(BSX_ERR_INVALID_ARG, "vjp takes the primal input as BOOL8 or F32");
+  cudaStream_t st = as_stream(stream);
+  const bool empty = conn->n_pre == 0 || (!conn->indptr && conn->conn_num == 0) || conn->n_post == 0;
+  if (dw && !conn->hetero) {
+    rc = launch_zero(dw, 1, st);
+    if (rc) return rc;
+  }
+  if (batch == 0 || empty) {
+    if (dx && batch > 0 && conn->n_pre > 0) return launch_zero(dx, batch * conn->n_pre, st);
+    if (dw && conn->hetero && conn->nnz > 0) return launch_zero(dw, conn->nnz, st);
+    return BSX_OK;
+  }
+  if (!ct) return fail(BSX_ERR_INVALID_ARG, "ct is NULL");
+  if (dw && !x) return fail(BSX_ERR_INVALID_ARG, "the weight cotangent needs the primal input x");
+  if (!dx && !dw) return BSX_OK;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) || workspace_bytes < ctT_bytes(batch, conn->n_post))
+    return fail(BSX_ERR_WORKSPACE, "batched vjp needs %zu workspace bytes", ctT_bytes(batch, conn->n_post));
+  int sms = sm_count();
+  if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  const int64_t Bp = (batch + 31) & ~int64_t(31);
+  if (Bp / 32 > 65535) return fail(BSX_ERR_UNSUPPORTED, "batch too large");
+  float* ctT = static_cast<float*>(workspace);
+  {
+    dim3 grid((unsigned)((conn->n_post + 31) / 32), (unsigned)(Bp / 32), 1);
+    transpose_pad_kernel<<<grid, 256, 0, st>>>(ct, batch, conn->n_post, Bp, ctT);
+    BSX_LAUNCH_CHECK("transpose_pad_kernel");
+  }
+  int64_t blocks = (conn->n_pre + 7) / 8;
+  if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
+  if (blocks < 1) blocks = 1;
+  const RowMap rm = make_rowmap(conn);
+  const bool ev = event != 0;
+  for (int64_t b0 = 0; b0 < batch; b0 += 64) {
+    const bool first = b0 == 0;
+#define BSX_VJPB(H, F)                                                                                    \
+  vjp_batched_kernel<H, F><<<(unsigned)blocks, 256, 0, st>>>(rm, conn->indices, conn->weights, x, ev, ctT, Bp, \
+                                                             batch, b0, conn->n_pre, dx, dw, first)
+    if (conn->hetero) {
+      if (x_format == BSX_SPK_BOOL8) BSX_VJPB(true, BSX_SPK_BOOL8); else BSX_VJPB(true, BSX_SPK_F32);
+    } else {
+      if (x_format == BSX_SPK_BOOL8) BSX_VJPB(false, BSX_SPK_BOOL8); else BSX_VJPB(false, BSX_SPK_F32);
+    }
+#undef BSX_VJPB
+    BSX_LAUNCH_CHECK("vjp_batched_kernel");
+  }
+  return BSX_OK;
+}
+
+}  // extern "C"

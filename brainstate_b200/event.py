@@ -355,8 +355,14 @@ def _raw_vjp(conn: _SparseConn, x: torch.Tensor, weights: torch.Tensor, ct: torc
     if need_dw:
         dw = torch.empty(conn.indices.shape if conn.hetero else (1,), dtype=torch.float32, device=ct.device)
     st = conn._struct(weights)
-    check(lib().bsx_vecmat_vjp(C.byref(st), ptr(xb), spike_format_of(xb), int(event), ptr(ctb), batch,
-                               ptr(dx), ptr(dw), _lib.current_stream()))
+    if batch >= 4:      # batch-minor cotangent: one index fetch serves 64 batch lanes
+        ws_bytes = lib().bsx_vecmat_vjp_batched_workspace_bytes(batch, n_post)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=ct.device)
+        check(lib().bsx_vecmat_vjp_batched(C.byref(st), ptr(xb), spike_format_of(xb), int(event), ptr(ctb), batch,
+                                           ptr(dx), ptr(dw), ptr(ws), ws_bytes, _lib.current_stream()))
+    else:
+        check(lib().bsx_vecmat_vjp(C.byref(st), ptr(xb), spike_format_of(xb), int(event), ptr(ctb), batch,
+                                   ptr(dx), ptr(dw), _lib.current_stream()))
     if dx is not None:
         dx = dx.reshape(lead + (n_pre,))
     if dw is not None and not conn.hetero:

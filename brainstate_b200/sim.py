@@ -147,6 +147,8 @@ class EINet:
         self.lists = [torch.zeros(self.n + 1, dtype=torch.int32, device=dev) for _ in range(2)]
         self.cur = 0
         self.step_count = 0
+        self._graphs = {}
+        self._warmed = False
         self._pstruct = self.params.struct()
         self._net = self._make_struct()
 
@@ -177,29 +179,83 @@ class EINet:
         self.step_count += steps
         return raster, counts
 
-    def _run_sharded(self, steps: int, record: bool):
+    def _sharded_step(self, t: int, counts, raster_rows):
+        """Enqueues one step on the current stream: scatter the previous step's spikes
+        (all ranks' spikes, this rank's targets), update the local neurons, all-gather
+        the packed spike words, rebuild the spike list."""
         import torch.distributed as dist
-        dev = self.dev
         l = lib()
         stream = _lib.current_stream()
+        net, ps = C.byref(self._net), C.byref(self._pstruct)
+        nxt = self.cur ^ 1
+        check(l.bsx_net_scatter(net, self.cur, stream))
+        check(l.bsx_net_update(net, ps, counts[t:t + 1].data_ptr(), stream))
+        dist.all_gather_into_tensor(self.bits, self._mine, group=self.group)
+        check(l.bsx_net_list_from_bits(net, nxt, stream))
+        if raster_rows is not None:
+            raster_rows[t].copy_(self.bits[:self.words])
+        self.cur = nxt
+
+    def _run_sharded(self, steps: int, record: bool, graph_steps: int = 0):
+        """Multi-rank run.  With ``graph_steps`` > 0, whole chunks of that many (even)
+        steps are replayed from a captured CUDA graph, which removes the per-launch
+        host cost; the rest, and everything by default, runs eagerly."""
+        import torch.distributed as dist
+        dev = self.dev
+        self._mine = self.bits[self.rank * self.wpr:(self.rank + 1) * self.wpr]
         raster = torch.empty((steps, self.words), dtype=torch.int32, device=dev) if record else None
         counts = torch.zeros(steps, dtype=torch.int32, device=dev)
-        wpr = self.wpr
-        mine = self.bits[self.rank * wpr:(self.rank + 1) * wpr]
-        net, ps = C.byref(self._net), C.byref(self._pstruct)
-        for t in range(steps):
-            nxt = self.cur ^ 1
-            # scatter the spikes of the previous step (all ranks' spikes, this rank's targets)
-            check(l.bsx_net_scatter(net, self.cur, stream))
-            check(l.bsx_net_update(net, ps, counts[t:t + 1].data_ptr(), stream))
-            dist.all_gather_into_tensor(self.bits, mine, group=self.group)
-            check(l.bsx_net_list_from_bits(net, nxt, stream))
+        t = 0
+        S = graph_steps - (graph_steps & 1)
+        if S >= 2 and steps >= 2 * S:
+            if not self._warmed:       # NCCL and lazy module loading must have run before a capture
+                c0 = torch.zeros(2, dtype=torch.int32, device=dev)
+                r0 = torch.empty((2, self.words), dtype=torch.int32, device=dev) if record else None
+                for k in range(2):
+                    self._sharded_step(k, c0, r0)
+                counts[0:2].copy_(c0)
+                if record:
+                    raster[0:2].copy_(r0)
+                t = 2
+                self._warmed = True
+                torch.cuda.synchronize()
+            key = (S, record, self.cur)
+            if key not in self._graphs:
+                gc = torch.zeros(S, dtype=torch.int32, device=dev)
+                gr = torch.empty((S, self.words), dtype=torch.int32, device=dev) if record else None
+                snap = {k: v.clone() for k, v in self._full_state().items()}
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    gc.zero_()
+                    for k in range(S):
+                        self._sharded_step(k, gc, gr)
+                # capture does not execute: the state is untouched, but restore defensively
+                for k, v in self._full_state().items():
+                    v.copy_(snap[k])
+                self._graphs[key] = (g, gc, gr)
+            g, gc, gr = self._graphs[key]
+            while steps - t >= S:
+                g.replay()
+                counts[t:t + S].copy_(gc)
+                if record:
+                    raster[t:t + S].copy_(gr)
+                t += S
+        if t < steps:
+            rest = steps - t
+            c1 = torch.zeros(rest, dtype=torch.int32, device=dev)
+            r1 = torch.empty((rest, self.words), dtype=torch.int32, device=dev) if record else None
+            for k in range(rest):
+                self._sharded_step(k, c1, r1)
+            counts[t:].copy_(c1)
             if record:
-                raster[t].copy_(self.bits[:self.words])
-            self.cur = nxt
+                raster[t:].copy_(r1)
         self.step_count += steps
         dist.all_reduce(counts, group=self.group)
         return raster, counts
+
+    def _full_state(self):
+        return {'V': self.V, 'g_e': self.g_e, 'g_i': self.g_i, 'ref': self.ref, 'delta_e': self.delta_e,
+                'delta_i': self.delta_i, 'bits': self.bits, 'l0': self.lists[0], 'l1': self.lists[1]}
 
     # ------------------------------------------------------------------
     def spikes(self) -> torch.Tensor:

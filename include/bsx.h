@@ -181,15 +181,18 @@ int bsx_float_vecmat(const bsx_conn_t* conn, const float* x, int64_t batch, floa
  * y = conn @ EventArray(s): y[b,i] = sum_k w[i,k] * [s[b, idx[i,k]] != 0]
  * (the "W @ spike" product; deterministic gather, one warp per row, spike
  * bitmask staged in shared memory).  spikes: (batch, n_post); out: (batch, n_pre).
- * Workspace holds the packed spike words when the input is not BITS32 already.
+ * With batch >= 2 and a workspace of bsx_event_matvec_workspace_bytes, one pass
+ * over the indices serves 16 spike vectors at a time; otherwise each vector is a
+ * pass of its own (the workspace then only holds packed spike words, and may be
+ * NULL for BITS32 input).
  */
 size_t bsx_event_matvec_workspace_bytes(int64_t batch, int64_t n_post);
 int bsx_event_matvec(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                      float* out, void* workspace, size_t workspace_bytes, bsx_stream_t stream);
 /* Same, with explicit launch geometry for tuning (0 = default).  mask_mode: 1 spike
  * words staged in shared memory by a bulk-async (TMA) copy, 2 staged by ordinary
- * loads, 3 read from global memory.  unroll: 128-bit index loads in flight per lane
- * (1, 2, 4 or 6). */
+ * loads, 3 read from global memory, 4 one pass per vector even when batched.
+ * unroll: 128-bit index loads in flight per lane (1, 2, 4 or 6). */
 int bsx_event_matvec_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                            float* out, void* workspace, size_t workspace_bytes, int blocks_per_sm,
                            int mask_mode, int unroll, bsx_stream_t stream);
@@ -222,6 +225,17 @@ int bsx_dense_event_vecmat(const void* spikes, int spike_format, const float* we
  */
 int bsx_vecmat_vjp(const bsx_conn_t* conn, const void* x, int x_format, int event,
                    const float* ct, int64_t batch, float* dx, float* dw, bsx_stream_t stream);
+
+/*
+ * The same cotangents for a batch (the training step of the batched event matmul):
+ * ct is transposed once into the workspace so that each index serves 64 batch lanes
+ * with two coalesced loads; dw only visits the batch lanes where the row fired.
+ * Deterministic (no atomics) for heterogeneous weights.
+ */
+size_t bsx_vecmat_vjp_batched_workspace_bytes(int64_t batch, int64_t n_post);
+int bsx_vecmat_vjp_batched(const bsx_conn_t* conn, const void* x, int x_format, int event, const float* ct,
+                           int64_t batch, float* dx, float* dw, void* workspace, size_t workspace_bytes,
+                           bsx_stream_t stream);
 
 /* ---- fused E/I network step ------------------------------------------------ */
 /*

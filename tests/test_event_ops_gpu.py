@@ -236,7 +236,7 @@ def test_jvp_like_the_reference_test(homo_w, cuda):
 
 
 @pytest.mark.parametrize('hetero', [False, True])
-@pytest.mark.parametrize('batch', [1, 4])
+@pytest.mark.parametrize('batch', [1, 3, 4, 37, 70])
 def test_raw_vjp_entry_point(hetero, batch, bsx, cuda, c_oracle):
     from brainstate_b200.event import _raw_vjp
     n_pre, n_post, K = 150, 220, 21
@@ -253,6 +253,28 @@ def test_raw_vjp_entry_point(hetero, batch, bsx, cuda, c_oracle):
                 if need_dx:
                     close(dx, dx_ref, scale=30)
                 close(dw.reshape(np.shape(dw_ref)), dw_ref, scale=30 * (1 if hetero else 50))
+
+
+def test_batched_training_step_at_microbenchmark_size(microbench, c_oracle, cuda):
+    """The batched event matmul with gradient: 64 x 65 536 spikes at 2 %, dense N(0,1)
+    cotangent; forward, input cotangent and weight cotangent against the C oracle."""
+    from brainstate_b200 import FixedPostNumConn
+    from brainstate_b200.event import _raw_vjp
+    n, K, idx, w, ti, tw = microbench
+    B = 64
+    spk = np.random.RandomState(220).random_sample((B, n)) < 0.02
+    ct = np.random.RandomState(221).standard_normal((B, n)).astype(np.float32)
+    het = FixedPostNumConn((tw, ti), shape=(n, n))
+    ts, tct = torch.from_numpy(spk).to(cuda), torch.from_numpy(ct).to(cuda)
+    y = het._vecmat(ts, event=True)
+    close(y, c_oracle.event_vecmat_u8(spk, idx, w, n))
+    yg = het._vecmat(ts, event=True, method='gather')
+    close(yg, c_oracle.event_vecmat_u8(spk, idx, w, n))
+    dx, dw = _raw_vjp(het, ts, tw, tct, True, True, True)
+    close(dx, c_oracle.float_matvec(ct, idx, w, n), scale=30)
+    close(dw, c_oracle.vecmat_dw(spk.astype(np.float32), ct, idx, n, n, event=True), scale=30)
+    dx2, dw2 = _raw_vjp(het, ts, tw, tct, True, True, True)
+    assert torch.equal(dx, dx2) and torch.equal(dw, dw2)         # no atomics: reproducible
 
 
 def test_transposed_copy_is_canonical(cuda):
