@@ -48,7 +48,8 @@ class BsxLifParams(C.Structure):
     """Mirror of ``bsx_lif_params_t``."""
     _fields_ = [(n, C.c_float) for n in ('dt', 'decay_e', 'decay_i', 'inv_tau_m', 'cuba_gain', 'V_rest', 'V_th',
                                          'V_reset', 'R', 'I_ext', 'E_e', 'E_i')] + \
-               [('ref_steps', C.c_int32), ('coba', C.c_int32)]
+               [('ref_steps', C.c_int32), ('coba', C.c_int32), ('ext_threshold', C.c_uint32),
+                ('ext_seed', C.c_uint32), ('ext_weight', C.c_float)]
 
 
 class BsxNet(C.Structure):
@@ -58,7 +59,7 @@ class BsxNet(C.Structure):
         ('exc', BsxConn), ('inh', BsxConn),
         ('V', C.c_void_p), ('g_e', C.c_void_p), ('g_i', C.c_void_p), ('ref', C.c_void_p),
         ('delta_e', C.c_void_p), ('delta_i', C.c_void_p), ('bits', C.c_void_p),
-        ('list', C.c_void_p * 2),
+        ('lists', C.c_void_p), ('ring', C.c_int32), ('delay_e', C.c_int32), ('delay_i', C.c_int32),
     ]
 
 
@@ -93,10 +94,11 @@ SIGNATURES = {
     'bsx_vecmat_vjp_batched_workspace_bytes': (_sz, [_i64, _i64]),
     'bsx_vecmat_vjp_batched': (_i32, [_connp, _vp, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     'bsx_dense_event_vecmat': (_i32, [_vp, _i32, _vp, _i64, _i64, _i64, _vp, _vp]),
-    'bsx_net_run': (_i32, [_netp, _lifp, _i32, _i32, _vp, _vp, _i32, _vp]),
-    'bsx_net_update': (_i32, [_netp, _lifp, _vp, _vp]),
-    'bsx_net_list_from_bits': (_i32, [_netp, _i32, _vp]),
-    'bsx_net_scatter': (_i32, [_netp, _i32, _vp]),
+    'bsx_net_run': (_i32, [_netp, _lifp, _i32, _i64, _vp, _vp, _i32, _vp]),
+    'bsx_net_update': (_i32, [_netp, _lifp, _i64, _vp, _vp]),
+    'bsx_net_list_from_bits': (_i32, [_netp, _i64, _vp]),
+    'bsx_net_scatter': (_i32, [_netp, _i64, _vp]),
+    'bsx_drive_hash': (C.c_uint32, [C.c_uint32, C.c_uint32, C.c_uint32]),
     'bsx_fill_f32': (_i32, [_vp, _i64, _f32, _vp]),
 }
 

@@ -47,9 +47,12 @@ struct NetDev {
   float *V, *g_e, *g_i, *delta_e, *delta_i;
   int32_t* ref;
   uint32_t* bits;
-  int32_t* list0;
-  int32_t* list1;
+  int32_t* lists;      // ring of spike lists, stride n_global + 1
+  int ring, delay_e, delay_i;
   bsx_lif_params_t p;
+  __device__ __forceinline__ int32_t* slot(int64_t step) const {
+    return lists + (step % ring) * (n_global + 1);
+  }
 };
 
 __device__ __forceinline__ void scatter_one(const ProjDev& pr, int64_t row, int c, int chunk, int lane,
@@ -63,9 +66,10 @@ __device__ __forceinline__ void scatter_one(const ProjDev& pr, int64_t row, int 
   else scatter_span<false>(pr.idx, pr.w, s, e, lane, __ldg(pr.w), out, pr.vec_ok);
 }
 
-// Phase A: list = [count, global ids...] of the neurons that spiked last step.
-__device__ __forceinline__ void phase_scatter(const NetDev& a, const int32_t* __restrict__ list, int64_t warp,
-                                              int64_t nwarps, int lane) {
+// Phase A for one list = [count, global ids...]; do_exc / do_inh select which
+// population's rows are taken from it (the two projections may have different delays).
+__device__ __forceinline__ void scatter_list(const NetDev& a, const int32_t* __restrict__ list, bool do_exc,
+                                             bool do_inh, int64_t warp, int64_t nwarps, int lane) {
   const int64_t count = list[0];
   const int cpr = a.exc.cpr > a.inh.cpr ? a.exc.cpr : a.inh.cpr;
   const int64_t items = count * cpr;
@@ -74,11 +78,39 @@ __device__ __forceinline__ void phase_scatter(const NetDev& a, const int32_t* __
     const int c = (int)(it - q * cpr);
     const int64_t id = list[1 + q];
     if (id < a.n_exc) {
-      if (c < a.exc.cpr) scatter_one(a.exc, id, c, a.chunk, lane, a.delta_e);
+      if (do_exc && c < a.exc.cpr) scatter_one(a.exc, id, c, a.chunk, lane, a.delta_e);
     } else {
-      if (c < a.inh.cpr) scatter_one(a.inh, id - a.n_exc, c, a.chunk, lane, a.delta_i);
+      if (do_inh && c < a.inh.cpr) scatter_one(a.inh, id - a.n_exc, c, a.chunk, lane, a.delta_i);
     }
   }
+}
+
+// Phase A of step `step`: excitatory spikes of step - 1 - delay_e, inhibitory spikes
+// of step - 1 - delay_i (steps before 0 produced nothing).
+__device__ __forceinline__ void phase_scatter(const NetDev& a, int64_t step, int64_t warp, int64_t nwarps,
+                                              int lane) {
+  const int64_t te = step - 1 - a.delay_e, ti = step - 1 - a.delay_i;
+  if (te == ti) {
+    if (te >= 0) scatter_list(a, a.slot(te), true, true, warp, nwarps, lane);
+  } else {
+    if (te >= 0) scatter_list(a, a.slot(te), true, false, warp, nwarps, lane);
+    if (ti >= 0) scatter_list(a, a.slot(ti), false, true, warp, nwarps, lane);
+  }
+}
+
+// Counter-based background drive: neuron `gid` receives one external excitatory
+// event at step `step` when a 32-bit hash of (seed, gid, step) falls below the
+// threshold.  Integer arithmetic only, so a host restatement matches bit for bit.
+__host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7feb352du;
+  x ^= x >> 15;
+  x *= 0x846ca68bu;
+  x ^= x >> 16;
+  return x;
+}
+__host__ __device__ __forceinline__ uint32_t drive_hash(uint32_t seed, uint32_t gid, uint32_t step) {
+  return mix32(mix32(gid + seed * 0x9e3779b9u) ^ (step * 0x85ebca6bu + 0xc2b2ae35u));
 }
 
 __device__ __forceinline__ float exprel_once(float z) {
@@ -88,7 +120,8 @@ __device__ __forceinline__ float exprel_once(float z) {
 }
 
 // Phase B for the 32 neurons of local word `word`; returns the spike word.
-__device__ __forceinline__ uint32_t update_word(const NetDev& a, int64_t word, int lane, bool* spiked) {
+__device__ __forceinline__ uint32_t update_word(const NetDev& a, int64_t word, int lane, int64_t step,
+                                                bool* spiked) {
   const bsx_lif_params_t& p = a.p;
   const int64_t i = word * 32 + lane;
   bool spk = false;
@@ -101,8 +134,11 @@ __device__ __forceinline__ uint32_t update_word(const NetDev& a, int64_t word, i
     float* __restrict__ pgi = a.g_i;
     float* __restrict__ pV = a.V;
     int32_t* __restrict__ pref = a.ref;
-    const float de = pde[i], di = pdi[i], ge0 = pge[i], gi0 = pgi[i], V = pV[i];
+    const float de_in = pde[i], di = pdi[i], ge0 = pge[i], gi0 = pgi[i], V = pV[i];
     const int32_t r = pref[i];
+    float de = de_in;
+    if (p.ext_threshold && drive_hash(p.ext_seed, (uint32_t)(a.first + i), (uint32_t)step) < p.ext_threshold)
+      de = __fadd_rn(de, p.ext_weight);
     const float ge = __fadd_rn(__fmul_rn(ge0, p.decay_e), de);
     const float gi = __fadd_rn(__fmul_rn(gi0, p.decay_i), di);
     float cur;
@@ -123,7 +159,7 @@ __device__ __forceinline__ uint32_t update_word(const NetDev& a, int64_t word, i
     const bool refractory = r > 0;
     if (refractory) Vn = V;
     spk = (Vn >= p.V_th) && !refractory;
-    if (de != 0.0f) pde[i] = 0.0f;
+    if (de_in != 0.0f) pde[i] = 0.0f;
     if (di != 0.0f) pdi[i] = 0.0f;
     pge[i] = ge;
     pgi[i] = gi;
@@ -146,21 +182,22 @@ __device__ __forceinline__ void append_spikes(uint32_t m, bool spk, int lane, in
 
 // ---- one cooperative launch for many steps (single GPU) ------------------------
 __global__ void __launch_bounds__(256)
-net_run_kernel(NetDev a, int steps, int cur, uint32_t* __restrict__ raster, int32_t* __restrict__ spike_counts) {
+net_run_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict__ raster,
+               int32_t* __restrict__ spike_counts) {
   cg::grid_group grid = cg::this_grid();
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   const int64_t words = (a.n_local + 31) >> 5;
   for (int t = 0; t < steps; ++t) {
-    int32_t* lcur = cur ? a.list1 : a.list0;
-    int32_t* lnext = cur ? a.list0 : a.list1;
+    const int64_t step = step0 + t;
+    int32_t* lnext = a.slot(step);   // not among the slots read this step: ring >= max delay + 2
     if (warp == 0 && lane == 0) lnext[0] = 0;
-    phase_scatter(a, lcur, warp, nwarps, lane);
+    phase_scatter(a, step, warp, nwarps, lane);
     grid.sync();
     for (int64_t wd = warp; wd < words; wd += nwarps) {
       bool spk;
-      const uint32_t m = update_word(a, wd, lane, &spk);
+      const uint32_t m = update_word(a, wd, lane, step, &spk);
       if (lane == 0) {
         a.bits[wd] = m;
         if (raster) raster[(int64_t)t * words + wd] = m;
@@ -169,19 +206,19 @@ net_run_kernel(NetDev a, int steps, int cur, uint32_t* __restrict__ raster, int3
     }
     grid.sync();
     if (spike_counts && warp == 0 && lane == 0) spike_counts[t] = lnext[0];
-    cur ^= 1;
   }
 }
 
 // ---- split phases (multi-GPU driver) ----------------------------------------------
-__global__ void __launch_bounds__(256) net_scatter_kernel(NetDev a, int which) {
+__global__ void __launch_bounds__(256) net_scatter_kernel(NetDev a, int64_t step) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  phase_scatter(a, which ? a.list1 : a.list0, warp, nwarps, lane);
+  phase_scatter(a, step, warp, nwarps, lane);
 }
 
-__global__ void __launch_bounds__(256) net_update_kernel(NetDev a, int32_t* __restrict__ local_count) {
+__global__ void __launch_bounds__(256)
+net_update_kernel(NetDev a, int64_t step, int32_t* __restrict__ local_count) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -190,7 +227,7 @@ __global__ void __launch_bounds__(256) net_update_kernel(NetDev a, int32_t* __re
   int mine = 0;
   for (int64_t wd = warp; wd < words; wd += nwarps) {
     bool spk;
-    const uint32_t m = update_word(a, wd, lane, &spk);
+    const uint32_t m = update_word(a, wd, lane, step, &spk);
     if (lane == 0) a.bits[word0 + wd] = m;
     mine += __popc(m);
   }
@@ -256,8 +293,14 @@ static int make_net(const bsx_net_t* net, const bsx_lif_params_t* p, NetDev* a) 
       net->exc.n_post != net->n_local || net->inh.n_post != net->n_local)
     return fail(BSX_ERR_INVALID_ARG, "projection shapes do not match the network (rows: population, columns: local neurons)");
   if (!net->V || !net->g_e || !net->g_i || !net->ref || !net->delta_e || !net->delta_i || !net->bits ||
-      !net->list[0] || !net->list[1])
+      !net->lists)
     return fail(BSX_ERR_INVALID_ARG, "a state buffer of the network is NULL");
+  if (net->delay_e < 0 || net->delay_i < 0) return fail(BSX_ERR_INVALID_ARG, "negative synaptic delay");
+  {
+    const int dmax = net->delay_e > net->delay_i ? net->delay_e : net->delay_i;
+    if (net->ring < dmax + 2)
+      return fail(BSX_ERR_INVALID_ARG, "the spike-list ring needs at least max(delay) + 2 = %d lists", dmax + 2);
+  }
   a->chunk = 128;
   // keep chunks-per-row small for very long rows
   int64_t kmax = net->exc.conn_num > net->inh.conn_num ? net->exc.conn_num : net->inh.conn_num;
@@ -273,9 +316,11 @@ static int make_net(const bsx_net_t* net, const bsx_lif_params_t* p, NetDev* a) 
   a->V = net->V; a->g_e = net->g_e; a->g_i = net->g_i; a->ref = net->ref;
   a->delta_e = net->delta_e; a->delta_i = net->delta_i;
   a->bits = net->bits;
-  a->list0 = net->list[0];
-  a->list1 = net->list[1];
-  if (p) a->p = *p;
+  a->lists = net->lists;
+  a->ring = net->ring;
+  a->delay_e = net->delay_e;
+  a->delay_i = net->delay_i;
+  if (p) a->p = *p; else a->p = bsx_lif_params_t{};
   return BSX_OK;
 }
 
@@ -285,10 +330,10 @@ using namespace bsx;
 
 extern "C" {
 
-int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t steps, int32_t cur_list,
+int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t steps, int64_t step0,
                 uint32_t* raster, int32_t* spike_counts, int32_t blocks, bsx_stream_t stream) {
   if (!params) return fail(BSX_ERR_INVALID_ARG, "params is NULL");
-  if (steps < 0 || (cur_list != 0 && cur_list != 1)) return fail(BSX_ERR_INVALID_ARG, "bad steps or list index");
+  if (steps < 0 || step0 < 0) return fail(BSX_ERR_INVALID_ARG, "bad step range");
   NetDev a;
   int rc = make_net(net, params, &a);
   if (rc) return rc;
@@ -304,28 +349,30 @@ int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t st
   int64_t want = blocks > 0 ? blocks : (net->n_local + 255) / 256;
   if (want < 1) want = 1;
   if (want > max_blocks) want = max_blocks;
-  int steps_i = steps, cur_i = cur_list;
-  void* args[] = {&a, &steps_i, &cur_i, &raster, &spike_counts};
+  int steps_i = steps;
+  int64_t step0_i = step0;
+  void* args[] = {&a, &steps_i, &step0_i, &raster, &spike_counts};
   BSX_CUDA(cudaLaunchCooperativeKernel((const void*)net_run_kernel, dim3((unsigned)want), dim3(256), args, 0,
                                        as_stream(stream)));
   return BSX_OK;
 }
 
-int bsx_net_scatter(const bsx_net_t* net, int32_t list_index, bsx_stream_t stream) {
-  if (list_index != 0 && list_index != 1) return fail(BSX_ERR_INVALID_ARG, "bad list index");
+int bsx_net_scatter(const bsx_net_t* net, int64_t step, bsx_stream_t stream) {
+  if (step < 0) return fail(BSX_ERR_INVALID_ARG, "negative step");
   NetDev a;
   int rc = make_net(net, nullptr, &a);
   if (rc) return rc;
   int sms = sm_count();
   if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
-  net_scatter_kernel<<<(unsigned)(sms * 4), 256, 0, as_stream(stream)>>>(a, list_index);
+  net_scatter_kernel<<<(unsigned)(sms * 4), 256, 0, as_stream(stream)>>>(a, step);
   BSX_LAUNCH_CHECK("net_scatter_kernel");
   return BSX_OK;
 }
 
-int bsx_net_update(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t* local_count,
+int bsx_net_update(const bsx_net_t* net, const bsx_lif_params_t* params, int64_t step, int32_t* local_count,
                    bsx_stream_t stream) {
   if (!params) return fail(BSX_ERR_INVALID_ARG, "params is NULL");
+  if (step < 0) return fail(BSX_ERR_INVALID_ARG, "negative step");
   NetDev a;
   int rc = make_net(net, params, &a);
   if (rc) return rc;
@@ -334,19 +381,19 @@ int bsx_net_update(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t
   if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
   int64_t blocks = (net->n_local + 255) / 256;
   if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
-  net_update_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(a, local_count);
+  net_update_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(a, step, local_count);
   BSX_LAUNCH_CHECK("net_update_kernel");
   return BSX_OK;
 }
 
-int bsx_net_list_from_bits(const bsx_net_t* net, int32_t list_index, bsx_stream_t stream) {
-  if (list_index != 0 && list_index != 1) return fail(BSX_ERR_INVALID_ARG, "bad list index");
+int bsx_net_list_from_bits(const bsx_net_t* net, int64_t step, bsx_stream_t stream) {
+  if (step < 0) return fail(BSX_ERR_INVALID_ARG, "negative step");
   NetDev a;
   int rc = make_net(net, nullptr, &a);
   if (rc) return rc;
   int sms = sm_count();
   if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
-  int32_t* list = list_index ? a.list1 : a.list0;
+  int32_t* list = net->lists + (step % net->ring) * (net->n_global + 1);
   BSX_CUDA(cudaMemsetAsync(list, 0, sizeof(int32_t), as_stream(stream)));
   const int64_t words = (a.n_global + 31) >> 5;
   int64_t blocks = (words + 255) / 256;
@@ -356,5 +403,8 @@ int bsx_net_list_from_bits(const bsx_net_t* net, int32_t list_index, bsx_stream_
   BSX_LAUNCH_CHECK("net_list_kernel");
   return BSX_OK;
 }
+
+// Host restatement of the device hash, for bindings that want to predict the drive.
+uint32_t bsx_drive_hash(uint32_t seed, uint32_t neuron, uint32_t step) { return drive_hash(seed, neuron, step); }
 
 }  // extern "C"

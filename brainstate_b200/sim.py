@@ -48,6 +48,15 @@ class LIFParams:
     E_e: float = 0.
     E_i: float = -80.
     coba: bool = False
+    ext_rate_hz: float = 0.      # background drive: external events per second per neuron
+    ext_weight: float = 0.       # size of one external event (added to the excitatory synapse)
+    ext_seed: int = 0
+
+    @property
+    def ext_threshold(self) -> int:
+        """32-bit threshold of the per-step event probability ``rate * dt`` (dt in ms)."""
+        p = max(0.0, min(1.0, self.ext_rate_hz * self.dt * 1e-3))
+        return min(0xffffffff, int(round(p * 4294967296.0)))
 
     def struct(self) -> BsxLifParams:
         p = BsxLifParams()
@@ -62,6 +71,9 @@ class LIFParams:
         p.E_e, p.E_i = f32(self.E_e), f32(self.E_i)
         p.ref_steps = int(round(self.tau_ref / self.dt))
         p.coba = int(self.coba)
+        p.ext_threshold = self.ext_threshold
+        p.ext_seed = int(self.ext_seed) & 0xffffffff
+        p.ext_weight = f32(self.ext_weight)
         return p
 
 
@@ -104,12 +116,19 @@ class EINet:
     w_e, w_i : homogeneous synaptic weights of the two projections.
     seed_e, seed_i : connectivity seeds (``EventFixedProb(..., seed=...)``).
     V0 : initial membrane potentials, ``(n_exc + n_inh,)``.
+    delay_e, delay_i : synaptic delays in steps beyond the next step (0: a spike of
+        step t acts at step t+1).  The spikes wait in a ring of bit-packed-by-index
+        lists, the counterpart of the reference's delay ring buffer
+        (``brainstate/nn/_delay.py:768-958``) for spike vectors.
     group : optional ``torch.distributed`` process group; with more than one rank
         the postsynaptic neurons are sharded.
     """
 
     def __init__(self, n_exc: int, n_inh: int, conn_num, w_e: float, w_i: float, *, seed_e: int, seed_i: int,
-                 V0, params: Optional[LIFParams] = None, device=None, group=None):
+                 V0, params: Optional[LIFParams] = None, device=None, group=None, delay_e: int = 0,
+                 delay_i: int = 0):
+        self.delay_e, self.delay_i = int(delay_e), int(delay_i)
+        self.ring = max(self.delay_e, self.delay_i) + 2
         self.n_exc, self.n_inh = int(n_exc), int(n_inh)
         self.n = self.n_exc + self.n_inh
         self.params = params or LIFParams()
@@ -144,8 +163,7 @@ class EINet:
         self.words = (self.n + 31) // 32
         self.wpr = words_per_rank(self.n, self.world)
         self.bits = torch.zeros(self.wpr * self.world, dtype=torch.int32, device=dev)
-        self.lists = [torch.zeros(self.n + 1, dtype=torch.int32, device=dev) for _ in range(2)]
-        self.cur = 0
+        self.lists = torch.zeros((self.ring, self.n + 1), dtype=torch.int32, device=dev)
         self.step_count = 0
         self._graphs = {}
         self._warmed = False
@@ -160,7 +178,8 @@ class EINet:
         s.V, s.g_e, s.g_i, s.ref = self.V.data_ptr(), self.g_e.data_ptr(), self.g_i.data_ptr(), self.ref.data_ptr()
         s.delta_e, s.delta_i = self.delta_e.data_ptr(), self.delta_i.data_ptr()
         s.bits = self.bits.data_ptr()
-        s.list[0], s.list[1] = self.lists[0].data_ptr(), self.lists[1].data_ptr()
+        s.lists = self.lists.data_ptr()
+        s.ring, s.delay_e, s.delay_i = self.ring, self.delay_e, self.delay_i
         return s
 
     # ------------------------------------------------------------------
@@ -173,9 +192,8 @@ class EINet:
         dev = self.dev
         raster = torch.empty((steps, self.words), dtype=torch.int32, device=dev) if record else None
         counts = torch.empty(steps, dtype=torch.int32, device=dev)
-        check(lib().bsx_net_run(C.byref(self._net), C.byref(self._pstruct), steps, self.cur,
+        check(lib().bsx_net_run(C.byref(self._net), C.byref(self._pstruct), steps, self.step_count,
                                 _lib.ptr(raster), counts.data_ptr(), blocks, _lib.current_stream()))
-        self.cur = (self.cur + steps) & 1
         self.step_count += steps
         return raster, counts
 
@@ -187,14 +205,14 @@ class EINet:
         l = lib()
         stream = _lib.current_stream()
         net, ps = C.byref(self._net), C.byref(self._pstruct)
-        nxt = self.cur ^ 1
-        check(l.bsx_net_scatter(net, self.cur, stream))
-        check(l.bsx_net_update(net, ps, counts[t:t + 1].data_ptr(), stream))
+        step = self.step_count
+        check(l.bsx_net_scatter(net, step, stream))
+        check(l.bsx_net_update(net, ps, step, counts[t:t + 1].data_ptr(), stream))
         dist.all_gather_into_tensor(self.bits, self._mine, group=self.group)
-        check(l.bsx_net_list_from_bits(net, nxt, stream))
+        check(l.bsx_net_list_from_bits(net, step, stream))
         if raster_rows is not None:
             raster_rows[t].copy_(self.bits[:self.words])
-        self.cur = nxt
+        self.step_count += 1
 
     def _run_sharded(self, steps: int, record: bool, graph_steps: int = 0):
         """Multi-rank run.  With ``graph_steps`` > 0, whole chunks of that many (even)
@@ -206,8 +224,8 @@ class EINet:
         raster = torch.empty((steps, self.words), dtype=torch.int32, device=dev) if record else None
         counts = torch.zeros(steps, dtype=torch.int32, device=dev)
         t = 0
-        S = graph_steps - (graph_steps & 1)
-        if S >= 2 and steps >= 2 * S:
+        S = graph_steps - (graph_steps % self.ring)      # a whole number of turns of the list ring
+        if S >= self.ring and steps >= 2 * S:
             if not self._warmed:       # NCCL and lazy module loading must have run before a capture
                 c0 = torch.zeros(2, dtype=torch.int32, device=dev)
                 r0 = torch.empty((2, self.words), dtype=torch.int32, device=dev) if record else None
@@ -219,23 +237,22 @@ class EINet:
                 t = 2
                 self._warmed = True
                 torch.cuda.synchronize()
-            key = (S, record, self.cur)
+            key = (S, record, self.step_count % self.ring)
             if key not in self._graphs:
                 gc = torch.zeros(S, dtype=torch.int32, device=dev)
                 gr = torch.empty((S, self.words), dtype=torch.int32, device=dev) if record else None
-                snap = {k: v.clone() for k, v in self._full_state().items()}
+                step_before = self.step_count
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     gc.zero_()
                     for k in range(S):
                         self._sharded_step(k, gc, gr)
-                # capture does not execute: the state is untouched, but restore defensively
-                for k, v in self._full_state().items():
-                    v.copy_(snap[k])
+                self.step_count = step_before          # capture enqueues nothing: no step was taken
                 self._graphs[key] = (g, gc, gr)
             g, gc, gr = self._graphs[key]
             while steps - t >= S:
                 g.replay()
+                self.step_count += S
                 counts[t:t + S].copy_(gc)
                 if record:
                     raster[t:t + S].copy_(gr)
@@ -249,13 +266,9 @@ class EINet:
             counts[t:].copy_(c1)
             if record:
                 raster[t:].copy_(r1)
-        self.step_count += steps
         dist.all_reduce(counts, group=self.group)
         return raster, counts
 
-    def _full_state(self):
-        return {'V': self.V, 'g_e': self.g_e, 'g_i': self.g_i, 'ref': self.ref, 'delta_e': self.delta_e,
-                'delta_i': self.delta_i, 'bits': self.bits, 'l0': self.lists[0], 'l1': self.lists[1]}
 
     # ------------------------------------------------------------------
     def spikes(self) -> torch.Tensor:
@@ -264,10 +277,27 @@ class EINet:
         b = np.unpackbits(w.view(np.uint8), bitorder='little')[:self.n].astype(bool)
         return torch.from_numpy(b)
 
-    def state(self):
-        """Local state tensors (for checkpoints): V, g_e, g_i, ref, bits, current list."""
-        return {'V': self.V, 'g_e': self.g_e, 'g_i': self.g_i, 'ref': self.ref, 'bits': self.bits,
-                'list': self.lists[self.cur], 'step': self.step_count}
+    # -- checkpoint / resume --------------------------------------------------
+    def state_dict(self) -> dict:
+        """Everything a resumed run needs that cannot be regenerated: the rank's neuron
+        state, the pending spike lists and the step counter.  The connectivity is not
+        stored; like the reference (whose index arrays are plain attributes, not
+        states, ``brainstate/nn/_event_fixedprob.py:181``) it is rebuilt from the seeds."""
+        return {'V': self.V.clone(), 'g_e': self.g_e.clone(), 'g_i': self.g_i.clone(), 'ref': self.ref.clone(),
+                'delta_e': self.delta_e.clone(), 'delta_i': self.delta_i.clone(), 'bits': self.bits.clone(),
+                'lists': self.lists.clone(), 'step': self.step_count,
+                'meta': {'n_exc': self.n_exc, 'n_inh': self.n_inh, 'conn_num': self.conn_num, 'ring': self.ring,
+                         'first': self.first, 'n_local': self.n_local}}
+
+    def load_state_dict(self, sd: dict):
+        m = sd['meta']
+        mine = {'n_exc': self.n_exc, 'n_inh': self.n_inh, 'conn_num': self.conn_num, 'ring': self.ring,
+                'first': self.first, 'n_local': self.n_local}
+        if m != mine:
+            raise ValueError(f'checkpoint of a different network or shard: {m} vs {mine}')
+        for k in ('V', 'g_e', 'g_i', 'ref', 'delta_e', 'delta_i', 'bits', 'lists'):
+            getattr(self, k).copy_(sd[k])
+        self.step_count = int(sd['step'])
 
 
 def unpack_raster(raster: torch.Tensor, n: int) -> np.ndarray:

@@ -191,7 +191,9 @@ int bsx_event_matvec(const bsx_conn_t* conn, const void* spikes, int spike_forma
                      float* out, void* workspace, size_t workspace_bytes, bsx_stream_t stream);
 /* Same, with explicit launch geometry for tuning (0 = default).  mask_mode: 1 spike
  * words staged in shared memory by a bulk-async (TMA) copy, 2 staged by ordinary
- * loads, 3 read from global memory, 4 one pass per vector even when batched.
+ * loads, 3 read from global memory, 4 one pass per vector even when batched;
+ * batched passes only: 5 stream heterogeneous weights with the indices, 6 fetch
+ * them per hit (default: chosen on the device from the spike density).
  * unroll: 128-bit index loads in flight per lane (1, 2, 4 or 6). */
 int bsx_event_matvec_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                            float* out, void* workspace, size_t workspace_bytes, int blocks_per_sm,
@@ -254,6 +256,12 @@ typedef struct bsx_lif_params {
   float E_e, E_i;    /* reversal potentials (conductance-based only) */
   int32_t ref_steps; /* refractory period in steps */
   int32_t coba;      /* 0: current-based (CUBA), 1: conductance-based (COBA) */
+  /* Background drive: at every step each neuron receives one external excitatory
+   * event of size ext_weight when bsx_drive_hash(ext_seed, neuron, step) <
+   * ext_threshold (probability ext_threshold / 2^32 per step; 0 switches it off). */
+  uint32_t ext_threshold;
+  uint32_t ext_seed;
+  float ext_weight;
 } bsx_lif_params_t;
 
 /*
@@ -273,28 +281,36 @@ typedef struct bsx_net {
   float* delta_e;      /* (n_local) scatter target, zero between steps */
   float* delta_i;      /* (n_local) */
   uint32_t* bits;      /* (ceil(n_global/32)) packed spikes of the latest step, whole network */
-  int32_t* list[2];    /* two spike lists, each [count, global ids...] with room for n_global ids */
+  int32_t* lists;      /* ring of `ring` spike lists of n_global + 1 ints each: [count, global ids...];
+                          the spikes of step t live in list t % ring; zero the counts before step 0 */
+  int32_t ring;        /* >= max(delay_e, delay_i) + 2 */
+  int32_t delay_e;     /* steps an excitatory spike waits beyond the next step (synaptic delay) */
+  int32_t delay_i;     /* same for inhibitory spikes */
 } bsx_net_t;
 
 /*
- * Runs `steps` steps of a whole network on one GPU in ONE cooperative launch.
- * This fuses what the reference's examples run as separate operators per step
- * (examples/400_CUBA_2005_bpu.py:60-66: two EventFixedProb products, two Expon
- * updates, CUBA/COBA output, LIFRef update).  list[cur_list] holds the spikes of
- * the step before the first one (count 0 at the start of a run); after the call
- * the latest spikes are in list[(cur_list + steps) & 1] and in `bits`.
+ * Runs steps [step0, step0 + steps) of a whole network on one GPU in ONE cooperative
+ * launch.  This fuses what the reference's examples run as separate operators per
+ * step (examples/400_CUBA_2005_bpu.py:60-66: two EventFixedProb products, two Expon
+ * updates, CUBA/COBA output, LIFRef update).  Step t consumes the excitatory spikes
+ * of step t-1-delay_e and the inhibitory spikes of step t-1-delay_i (the bit-packed
+ * counterpart of the reference's delay ring buffer, brainstate/nn/_delay.py:768-958)
+ * and leaves its own spikes in list t % ring and in `bits`.
  * raster (may be NULL): (steps, ceil(n/32)) packed spike words; spike_counts (may
  * be NULL): spikes per step.  blocks: grid size, 0 = chosen from the network size.
  */
-int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t steps, int32_t cur_list,
+int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t steps, int64_t step0,
                 uint32_t* raster, int32_t* spike_counts, int32_t blocks, bsx_stream_t stream);
-/* The pieces of one step, for the multi-GPU driver (update -> exchange of the
- * spike words -> list -> scatter).  bsx_net_update writes the rank's words of
- * `bits` and adds its spike count to *local_count (may be NULL). */
-int bsx_net_update(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t* local_count,
+/* The pieces of step `step`, for the multi-GPU driver: scatter (the delayed spikes
+ * of all ranks onto this rank's neurons) -> update (writes the rank's words of
+ * `bits`, adds its spike count to *local_count, which may be NULL) -> exchange of
+ * the spike words by the caller -> list (fills list step % ring from `bits`). */
+int bsx_net_scatter(const bsx_net_t* net, int64_t step, bsx_stream_t stream);
+int bsx_net_update(const bsx_net_t* net, const bsx_lif_params_t* params, int64_t step, int32_t* local_count,
                    bsx_stream_t stream);
-int bsx_net_list_from_bits(const bsx_net_t* net, int32_t list_index, bsx_stream_t stream);
-int bsx_net_scatter(const bsx_net_t* net, int32_t list_index, bsx_stream_t stream);
+int bsx_net_list_from_bits(const bsx_net_t* net, int64_t step, bsx_stream_t stream);
+/* The hash behind the background drive, on the host (same integer arithmetic). */
+uint32_t bsx_drive_hash(uint32_t seed, uint32_t neuron, uint32_t step);
 
 /* ---- small utilities ---------------------------------------------------- */
 int bsx_fill_f32(float* dst, int64_t n, float value, bsx_stream_t stream);

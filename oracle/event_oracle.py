@@ -298,7 +298,8 @@ class EINetOracle:
     def __init__(self, n_exc, n_inh, idx_e, w_e, idx_i, w_i, *, coba=False,
                  dt=0.1, tau_m=20., tau_e=5., tau_i=10., V_rest=-49., V_th=-50.,
                  V_reset=-60., tau_ref=5., R=1., I_ext=0., E_e=0., E_i=-80.,
-                 V0=None, indptr_e=None, indptr_i=None, n_local=None):
+                 V0=None, indptr_e=None, indptr_i=None, n_local=None, first=0, delay_e=0, delay_i=0,
+                 ext_threshold=0, ext_seed=0, ext_weight=0.):
         # n_local: number of neurons whose state this instance holds (a postsynaptic
         # shard); the index arrays then hold local column ids.  Default: the whole network.
         self.n_exc, self.n_inh = n_exc, n_inh
@@ -321,14 +322,52 @@ class EINetOracle:
         self.g_i = np.zeros(self.n, F32)
         self.ref = np.zeros(self.n, np.int32)       # remaining refractory steps
         self.spk = np.zeros(self.n, bool)
+        # synaptic delays: a spike of step t acts at step t + 1 + delay; background drive:
+        # one external excitatory event per neuron and step where the hash of
+        # (seed, global id, step) is below the threshold
+        self.first = first
+        self.delay_e, self.delay_i = int(delay_e), int(delay_i)
+        self.history = []                      # global spike vectors of past steps, oldest first
+        self.t = 0
+        self.ext_threshold, self.ext_seed, self.ext_weight = int(ext_threshold), int(ext_seed), F32(ext_weight)
+
+    @staticmethod
+    def mix32(x):
+        x = x.astype(np.uint32)
+        x ^= x >> np.uint32(16); x *= np.uint32(0x7feb352d)
+        x ^= x >> np.uint32(15); x *= np.uint32(0x846ca68b)
+        x ^= x >> np.uint32(16)
+        return x
+
+    @classmethod
+    def drive_hash(cls, seed, gid, step):
+        """Restates the integer hash of the device's background drive."""
+        with np.errstate(over='ignore'):
+            gid = np.asarray(gid, np.uint32)
+            a = cls.mix32(gid + np.uint32(seed) * np.uint32(0x9e3779b9))
+            b = np.uint32(step) * np.uint32(0x85ebca6b) + np.uint32(0xc2b2ae35)
+            return cls.mix32(a ^ b)
+
+    def _delayed(self, delay):
+        k = len(self.history) - 1 - delay
+        return self.history[k] if k >= 0 else np.zeros(self.n_global, bool)
 
     def step(self, s_global=None):
         """One step.  ``s_global``: spikes of the previous step of the WHOLE network
         (needed by a shard); by default the instance's own previous spikes."""
         s = self.spk if s_global is None else np.asarray(s_global, bool)
         assert s.shape == (self.n_global,)
-        dg_e = event_vecmat(s[:self.n_exc], self.idx_e, self.w_e, self.n, self.indptr_e)
-        dg_i = event_vecmat(s[self.n_exc:], self.idx_i, self.w_i, self.n, self.indptr_i)
+        if self.t > 0:
+            self.history.append(s.copy())
+        s_e, s_i = self._delayed(self.delay_e), self._delayed(self.delay_i)
+        self.history = self.history[-(max(self.delay_e, self.delay_i) + 1):]
+        dg_e = event_vecmat(s_e[:self.n_exc], self.idx_e, self.w_e, self.n, self.indptr_e)
+        dg_i = event_vecmat(s_i[self.n_exc:], self.idx_i, self.w_i, self.n, self.indptr_i)
+        if self.ext_threshold:
+            gid = np.arange(self.first, self.first + self.n, dtype=np.uint32)
+            fire = self.drive_hash(self.ext_seed, gid, self.t) < np.uint32(min(self.ext_threshold, 0xffffffff))
+            dg_e = np.where(fire, (dg_e + self.ext_weight).astype(F32), dg_e).astype(F32)
+        self.t += 1
         self.g_e = (self.g_e * self.decay_e).astype(F32) + dg_e
         self.g_i = (self.g_i * self.decay_i).astype(F32) + dg_i
         V = self.V

@@ -15,16 +15,21 @@ from oracle import event_oracle as eo
 pytestmark = pytest.mark.gpu
 
 
-def build(n_exc, n_inh, K, coba, cuda, w_e, w_i, I_ext=0.0, R=None):
+def build(n_exc, n_inh, K, coba, cuda, w_e, w_i, I_ext=0.0, R=None, delay_e=0, delay_i=0, ext=None):
     from brainstate_b200.sim import EINet, LIFParams
     n = n_exc + n_inh
     V0 = np.random.RandomState(102).uniform(-60, -50, n).astype(np.float32)
     R = (0.1 if coba else 1.0) if R is None else R      # COBA: R = 1/g_leak with g_leak = 10 nS
     params = LIFParams(coba=coba, I_ext=I_ext, R=R)
-    net = EINet(n_exc, n_inh, K, w_e, w_i, seed_e=100, seed_i=101, V0=V0, params=params, device=cuda)
+    if ext is not None:
+        params.ext_rate_hz, params.ext_weight, params.ext_seed = ext
+    net = EINet(n_exc, n_inh, K, w_e, w_i, seed_e=100, seed_i=101, V0=V0, params=params, device=cuda,
+                delay_e=delay_e, delay_i=delay_i)
     idx_e = eo.fixed_num_indices(100, n_exc, n, K)
     idx_i = eo.fixed_num_indices(101, n_inh, n, K)
-    orc = eo.EINetOracle(n_exc, n_inh, idx_e, np.float32(w_e), idx_i, np.float32(w_i), coba=coba, V0=V0, I_ext=I_ext, R=R)
+    orc = eo.EINetOracle(n_exc, n_inh, idx_e, np.float32(w_e), idx_i, np.float32(w_i), coba=coba, V0=V0, I_ext=I_ext, R=R,
+                         delay_e=delay_e, delay_i=delay_i, ext_threshold=params.ext_threshold,
+                         ext_seed=params.ext_seed, ext_weight=params.ext_weight)
     return net, orc
 
 
@@ -91,9 +96,62 @@ def test_split_phase_entry_points_equal_fused_run(bsx, cuda):
     rows = []
     net, ps = C.byref(b._net), C.byref(b._pstruct)
     for t in range(steps):
-        _lib.check(bsx.bsx_net_scatter(net, b.cur, stream))
-        _lib.check(bsx.bsx_net_update(net, ps, None, stream))
-        _lib.check(bsx.bsx_net_list_from_bits(net, b.cur ^ 1, stream))
+        _lib.check(bsx.bsx_net_scatter(net, t, stream))
+        _lib.check(bsx.bsx_net_update(net, ps, t, None, stream))
+        _lib.check(bsx.bsx_net_list_from_bits(net, t, stream))
         rows.append(b.bits[:b.words].clone())
-        b.cur ^= 1
     assert torch.equal(r1, torch.stack(rows))
+
+
+@pytest.mark.parametrize('delays', [(1, 0), (3, 7), (12, 12)])
+def test_synaptic_delays_match_oracle(delays, cuda):
+    """A spike of step t acts at step t + 1 + delay; the two projections may differ."""
+    from brainstate_b200.sim import unpack_raster
+    de, di = delays
+    net, orc = build(640, 160, 16, False, cuda, 1.62, -9.0, delay_e=de, delay_i=di)
+    assert net.ring == max(de, di) + 2
+    steps = 260
+    r = torch.cat([net.run(k)[0] for k in (33, 100, 127)])        # pieces: the ring position carries over
+    ref = orc.run(steps)
+    assert ref.sum() > 50
+    assert np.array_equal(unpack_raster(r, 800), ref)
+
+
+def test_background_drive_matches_oracle(cuda):
+    """The hashed per-neuron drive (the stand-in for a Poisson input) is integer
+    arithmetic and reproduces bit for bit; V_rest below threshold so that only the
+    drive makes the network fire."""
+    from brainstate_b200.sim import EINet, LIFParams, unpack_raster
+    n_exc, n_inh, K = 640, 160, 16
+    n = n_exc + n_inh
+    V0 = np.random.RandomState(102).uniform(-60, -52, n).astype(np.float32)
+    params = LIFParams(V_rest=-55., ext_rate_hz=2000., ext_weight=1.5, ext_seed=403)
+    net = EINet(n_exc, n_inh, K, 1.62, -9.0, seed_e=100, seed_i=101, V0=V0, params=params, device=cuda)
+    orc = eo.EINetOracle(n_exc, n_inh, eo.fixed_num_indices(100, n_exc, n, K), np.float32(1.62),
+                         eo.fixed_num_indices(101, n_inh, n, K), np.float32(-9.0), V0=V0, V_rest=-55.,
+                         ext_threshold=params.ext_threshold, ext_seed=403, ext_weight=1.5)
+    steps = 300
+    r, counts = net.run(steps)
+    ref = orc.run(steps)
+    assert ref.sum() > 50
+    assert np.array_equal(unpack_raster(r, n), ref)
+    quiet = EINet(n_exc, n_inh, K, 1.62, -9.0, seed_e=100, seed_i=101, V0=V0, params=LIFParams(V_rest=-55.), device=cuda)
+    assert int(quiet.run(steps)[1].sum()) == 0
+
+
+def test_checkpoint_and_resume(cuda, tmp_path):
+    """Stop after 90 steps, save, rebuild the network from its seeds, load, continue:
+    the continuation equals the uninterrupted run (pending delayed spikes included)."""
+    a, _ = build(640, 160, 16, True, cuda, 0.6, 6.7, delay_e=2, delay_i=5)
+    full, _ = a.run(200)
+    b, _ = build(640, 160, 16, True, cuda, 0.6, 6.7, delay_e=2, delay_i=5)
+    first, _ = b.run(90)
+    torch.save(b.state_dict(), tmp_path / 'ckpt.pt')
+    c, _ = build(640, 160, 16, True, cuda, 0.6, 6.7, delay_e=2, delay_i=5)
+    c.load_state_dict(torch.load(tmp_path / 'ckpt.pt'))
+    assert c.step_count == 90
+    rest, _ = c.run(110)
+    assert torch.equal(torch.cat([first, rest]), full)
+    other, _ = build(320, 96, 12, True, cuda, 0.6, 6.7, delay_e=2, delay_i=5)
+    with pytest.raises(ValueError):
+        other.load_state_dict(torch.load(tmp_path / 'ckpt.pt'))
