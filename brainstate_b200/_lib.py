@@ -63,6 +63,13 @@ class BsxNet(C.Structure):
     ]
 
 
+class BsxNetPeers(C.Structure):
+    """Mirror of ``bsx_net_peers_t``."""
+    _fields_ = [('world', C.c_int32), ('rank', C.c_int32), ('words_per_rank', C.c_int64),
+                ('spin_limit', C.c_int64), ('bits', C.c_void_p * 16), ('flags', C.c_void_p * 16),
+                ('status', C.c_void_p)]
+
+
 _i64, _i32, _vp, _sz, _f32 = C.c_int64, C.c_int, C.c_void_p, C.c_size_t, C.c_float
 _connp = C.POINTER(BsxConn)
 _netp = C.POINTER(BsxNet)
@@ -98,6 +105,11 @@ SIGNATURES = {
     'bsx_net_update': (_i32, [_netp, _lifp, _i64, _vp, _vp]),
     'bsx_net_list_from_bits': (_i32, [_netp, _i64, _vp]),
     'bsx_net_scatter': (_i32, [_netp, _i64, _vp]),
+    'bsx_net_run_p2p': (_i32, [_netp, _lifp, C.POINTER(BsxNetPeers), _i32, _i64, _vp, _vp, _i32, _vp]),
+    'bsx_ipc_alloc': (_i32, [_sz, C.POINTER(C.c_void_p), _vp]),
+    'bsx_ipc_open': (_i32, [_vp, C.POINTER(C.c_void_p)]),
+    'bsx_ipc_close': (_i32, [_vp]),
+    'bsx_ipc_free': (_i32, [_vp]),
     'bsx_drive_hash': (C.c_uint32, [C.c_uint32, C.c_uint32, C.c_uint32]),
     'bsx_fill_f32': (_i32, [_vp, _i64, _f32, _vp]),
 }

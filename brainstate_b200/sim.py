@@ -126,7 +126,11 @@ class EINet:
 
     def __init__(self, n_exc: int, n_inh: int, conn_num, w_e: float, w_i: float, *, seed_e: int, seed_i: int,
                  V0, params: Optional[LIFParams] = None, device=None, group=None, delay_e: int = 0,
-                 delay_i: int = 0):
+                 delay_i: int = 0, exchange: str = 'nccl'):
+        if exchange not in ('nccl', 'p2p'):
+            raise ValueError("exchange must be 'nccl' or 'p2p'")
+        self.exchange = exchange
+        self._p2p = None
         self.delay_e, self.delay_i = int(delay_e), int(delay_i)
         self.ring = max(self.delay_e, self.delay_i) + 2
         self.n_exc, self.n_inh = int(n_exc), int(n_inh)
@@ -187,6 +191,8 @@ class EINet:
         """Advances ``steps`` steps.  Returns ``(raster, counts)``: the packed spike
         words ``(steps, ceil(n/32))`` int32 (``None`` without ``record``) and the
         number of spikes of every step ``(steps,)`` int32."""
+        if self.world > 1 and self.exchange == 'p2p':
+            return self._run_p2p(steps, record, blocks)
         if self.world > 1:
             return self._run_sharded(steps, record)
         dev = self.dev
@@ -276,6 +282,77 @@ class EINet:
         w = self.bits[:self.words].cpu().numpy().view(np.uint32)
         b = np.unpackbits(w.view(np.uint8), bitorder='little')[:self.n].astype(bool)
         return torch.from_numpy(b)
+
+    # -- exchange inside the kernel (peer stores over NVLink) ---------------------
+    def _setup_p2p(self):
+        """Allocates this rank's exchange buffer and progress counters, exports them to
+        the other ranks of the node and maps theirs (CUDA IPC; one-time)."""
+        import torch.distributed as dist
+        from ._lib import BsxNetPeers
+        l = lib()
+        words = self.wpr * self.world
+        bits_bytes = 2 * words * 4
+        flags_off = (bits_bytes + 255) // 256 * 256
+        total = flags_off + 256 + 256                     # counters (world x int64), status word
+        base = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        check(l.bsx_ipc_alloc(total, C.byref(base), handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=self.group)
+        ptrs, opened = [], []
+        for r in range(self.world):
+            if r == self.rank:
+                ptrs.append(base.value)
+            else:
+                q = C.c_void_p()
+                check(l.bsx_ipc_open(C.create_string_buffer(handles[r], 64), C.byref(q)))
+                ptrs.append(q.value)
+                opened.append(q.value)
+        peers = BsxNetPeers()
+        peers.world, peers.rank, peers.words_per_rank, peers.spin_limit = self.world, self.rank, self.wpr, 0
+        for r in range(self.world):
+            peers.bits[r] = ptrs[r]
+            peers.flags[r] = ptrs[r] + flags_off
+        peers.status = base.value + flags_off + 256
+        self._p2p = {'peers': peers, 'base': base.value, 'opened': opened, 'status_ptr': base.value + flags_off + 256}
+        dist.barrier(group=self.group)                    # every rank has mapped every buffer
+
+    def _run_p2p(self, steps: int, record: bool, blocks: int = 0):
+        """All steps of all ranks in one cooperative launch per GPU; the spike words
+        travel by peer stores inside the kernel."""
+        if self._p2p is None:
+            self._setup_p2p()
+        dev = self.dev
+        raster = torch.empty((steps, self.words), dtype=torch.int32, device=dev) if record else None
+        counts = torch.empty(steps, dtype=torch.int32, device=dev)
+        check(lib().bsx_net_run_p2p(C.byref(self._net), C.byref(self._pstruct), C.byref(self._p2p['peers']), steps,
+                                    self.step_count, _lib.ptr(raster), counts.data_ptr(), blocks,
+                                    _lib.current_stream()))
+        host = C.c_int32(0)
+        check(lib().bsx_read_status(self._p2p['status_ptr'], C.byref(host), _lib.current_stream()))
+        if host.value != 0:
+            raise RuntimeError('the multi-GPU step kernel gave up waiting for a peer '
+                               f'({lib().bsx_status_name(host.value).decode()}); the run stopped early')
+        self.step_count += steps
+        return raster, counts
+
+    def close(self):
+        """Drops the captured CUDA graphs and the peer mappings.  Call it before the
+        process group is destroyed: a live graph that holds captured collectives keeps
+        the communicator busy and the teardown waits for it."""
+        if self._p2p is not None:
+            import torch.distributed as dist
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)                # nobody still writes into a buffer about to go
+            for q in self._p2p['opened']:
+                lib().bsx_ipc_close(q)
+            dist.barrier(group=self.group)
+            lib().bsx_ipc_free(self._p2p['base'])
+            self._p2p = None
+        self._graphs.clear()
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
 
     # -- checkpoint / resume --------------------------------------------------
     def state_dict(self) -> dict:

@@ -309,6 +309,42 @@ int bsx_net_scatter(const bsx_net_t* net, int64_t step, bsx_stream_t stream);
 int bsx_net_update(const bsx_net_t* net, const bsx_lif_params_t* params, int64_t step, int32_t* local_count,
                    bsx_stream_t stream);
 int bsx_net_list_from_bits(const bsx_net_t* net, int64_t step, bsx_stream_t stream);
+/*
+ * Many steps on many GPUs with the exchange inside the kernel: each rank (one
+ * process per GPU) launches this cooperative kernel on its part of the network.
+ * After the neuron update a rank stores its packed spike words into every peer's
+ * exchange buffer with plain stores over NVLink, fences at system scope and raises
+ * its progress counter on every peer; it then waits (bounded) for all counters and
+ * compacts the complete words into the spike list.  No collective library call and
+ * no host round trip per step.  There is no counterpart in the reference, which
+ * runs on one device.
+ *   bits[r]   rank r's exchange buffer: 2 * world * words_per_rank uint32 (two
+ *             step parities), zero before the first step
+ *   flags[r]  rank r's progress counters: `world` int64, zero before the first step
+ *   status    local int32, zero on entry; BSX_ERR_TIMEOUT after a wait of more than
+ *             spin_limit polls (0 = default, about a second), in which case the
+ *             kernel has stopped early at a step boundary
+ * Rank r owns neurons [32*r*words_per_rank, ...) as in bsx_net_t.  All ranks must
+ * call with the same steps and step0.
+ */
+typedef struct bsx_net_peers {
+  int32_t world, rank;
+  int64_t words_per_rank;
+  int64_t spin_limit;
+  uint32_t* bits[16];
+  int64_t* flags[16];
+  int32_t* status;
+} bsx_net_peers_t;
+int bsx_net_run_p2p(const bsx_net_t* net, const bsx_lif_params_t* params, const bsx_net_peers_t* peers,
+                    int32_t steps, int64_t step0, uint32_t* raster, int32_t* spike_counts, int32_t blocks,
+                    bsx_stream_t stream);
+/* Set-up helpers for the buffers above (the only allocating entry points; never on
+ * the hot path): allocate zeroed device memory with a 64-byte handle another process
+ * on the node can open; open / close a peer's handle; free. */
+int bsx_ipc_alloc(size_t bytes, void** ptr, void* handle64);
+int bsx_ipc_open(const void* handle64, void** ptr);
+int bsx_ipc_close(void* ptr);
+int bsx_ipc_free(void* ptr);
 /* The hash behind the background drive, on the host (same integer arithmetic). */
 uint32_t bsx_drive_hash(uint32_t seed, uint32_t neuron, uint32_t step);
 

@@ -18,7 +18,7 @@ def _free_port():
     return port
 
 
-def _rank_main(rank, world, port, steps, coba, out_dir):
+def _rank_main(rank, world, port, steps, coba, exchange, out_dir):
     import torch.distributed as dist
     os.environ['MASTER_ADDR'] = '127.0.0.1'
     os.environ['MASTER_PORT'] = str(port)
@@ -33,32 +33,37 @@ def _rank_main(rank, world, port, steps, coba, out_dir):
         V0 = np.random.RandomState(102).uniform(-60, -50, n).astype(np.float32)
         w_e, w_i, R = (0.6, 6.7, 0.1) if coba else (1.62, -9.0, 1.0)
         net = EINet(n_exc, n_inh, K, w_e, w_i, seed_e=100, seed_i=101, V0=V0,
-                    params=LIFParams(coba=coba, R=R), device=dev, group=dist.group.WORLD)
-        raster, counts = net.run(steps)
+                    params=LIFParams(coba=coba, R=R), device=dev, group=dist.group.WORLD, exchange=exchange,
+                    delay_e=1, delay_i=0)
+        r1, c1 = net.run(steps // 2)
+        r2, c2 = net.run(steps - steps // 2)
+        raster, counts = torch.cat([r1, r2]), torch.cat([c1, c2])
         torch.cuda.synchronize()
         if rank == 0:
             torch.save({'raster': raster.cpu(), 'counts': counts.cpu()}, os.path.join(out_dir, 'sharded.pt'))
         dist.barrier()
+        net.close()
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize('exchange', ['nccl', 'p2p'])
 @pytest.mark.parametrize('coba', [False, True])
-def test_sharded_network_equals_single_gpu(coba, tmp_path):
+def test_sharded_network_equals_single_gpu(coba, exchange, tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip('needs at least two GPUs')
     import torch.multiprocessing as mp
     from brainstate_b200.sim import EINet, LIFParams
     world = 2 if torch.cuda.device_count() < 4 else 4
     steps = 200
-    mp.spawn(_rank_main, args=(world, _free_port(), steps, coba, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_rank_main, args=(world, _free_port(), steps, coba, exchange, str(tmp_path)), nprocs=world, join=True)
     got = torch.load(tmp_path / 'sharded.pt')
     n_exc, n_inh, K = 3200, 800, 80
     n = n_exc + n_inh
     V0 = np.random.RandomState(102).uniform(-60, -50, n).astype(np.float32)
     w_e, w_i, R = (0.6, 6.7, 0.1) if coba else (1.62, -9.0, 1.0)
     net = EINet(n_exc, n_inh, K, w_e, w_i, seed_e=100, seed_i=101, V0=V0, params=LIFParams(coba=coba, R=R),
-                device='cuda:0')
+                device='cuda:0', delay_e=1, delay_i=0)
     raster, counts = net.run(steps)
     assert int(counts.sum()) > 50
     assert torch.equal(raster.cpu(), got['raster'])

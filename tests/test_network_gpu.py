@@ -155,3 +155,55 @@ def test_checkpoint_and_resume(cuda, tmp_path):
     other, _ = build(320, 96, 12, True, cuda, 0.6, 6.7, delay_e=2, delay_i=5)
     with pytest.raises(ValueError):
         other.load_state_dict(torch.load(tmp_path / 'ckpt.pt'))
+
+
+def _local_peers(net, world, cuda, spin_limit=0):
+    """Peer description whose buffers all live on this GPU (world = 1, or a second
+    'rank' that never runs)."""
+    from brainstate_b200._lib import BsxNetPeers
+    wpr = net.words
+    bits = [torch.zeros(2 * world * wpr, dtype=torch.int32, device=cuda) for _ in range(world)]
+    flags = [torch.zeros(world, dtype=torch.int64, device=cuda) for _ in range(world)]
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    p = BsxNetPeers()
+    p.world, p.rank, p.words_per_rank, p.spin_limit = world, 0, wpr, spin_limit
+    for r in range(world):
+        p.bits[r], p.flags[r] = bits[r].data_ptr(), flags[r].data_ptr()
+    p.status = status.data_ptr()
+    return p, (bits, flags, status)
+
+
+def test_exchange_in_kernel_variant_on_one_rank(bsx, cuda):
+    """The multi-GPU step kernel with a world of one: same raster as the plain kernel."""
+    import ctypes as C
+    from brainstate_b200 import _lib
+    a, _ = build(640, 160, 16, True, cuda, 0.6, 6.7, delay_e=2, delay_i=0)
+    b, _ = build(640, 160, 16, True, cuda, 0.6, 6.7, delay_e=2, delay_i=0)
+    steps = 150
+    r1, c1 = a.run(steps)
+    peers, keep = _local_peers(b, 1, cuda)
+    raster = torch.empty((steps, b.words), dtype=torch.int32, device=cuda)
+    counts = torch.empty(steps, dtype=torch.int32, device=cuda)
+    for (s0, k) in ((0, 70), (70, 80)):
+        _lib.check(bsx.bsx_net_run_p2p(C.byref(b._net), C.byref(b._pstruct), C.byref(peers), k, s0,
+                                       raster[s0:].data_ptr(), counts[s0:].data_ptr(), 0, _lib.current_stream()))
+    torch.cuda.synchronize()
+    assert int(keep[2].item()) == 0
+    assert torch.equal(r1, raster) and torch.equal(c1, counts)
+
+
+def test_wait_for_a_silent_peer_runs_out_and_reports(bsx, cuda):
+    """A second rank that never raises its counter: the kernel gives up after the
+    bounded wait, reports BSX_ERR_TIMEOUT in the status word and the context stays usable."""
+    import ctypes as C
+    from brainstate_b200 import _lib
+    b, _ = build(320, 96, 12, False, cuda, 1.62, -9.0)
+    peers, keep = _local_peers(b, 2, cuda, spin_limit=2000)
+    counts = torch.full((10,), -1, dtype=torch.int32, device=cuda)
+    _lib.check(bsx.bsx_net_run_p2p(C.byref(b._net), C.byref(b._pstruct), C.byref(peers), 10, 0, None,
+                                   counts.data_ptr(), 0, _lib.current_stream()))
+    torch.cuda.synchronize()
+    assert int(keep[2].item()) == _lib.BSX_ERR_TIMEOUT
+    assert int(counts[0].item()) == -1                      # stopped at the first step boundary
+    x = torch.ones(8, device=cuda)                          # the context is still healthy
+    assert float((x + 1).sum()) == 16.0
