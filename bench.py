@@ -339,6 +339,10 @@ def run_ours(args):
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
     e2e_value = events_all * e2e_steps / float(t_e2e.item())
 
+    network = None
+    if not args.no_network:
+        network = run_network(torch, dist, dev, world, rank)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -395,6 +399,7 @@ def run_ours(args):
         'roofline_other_kernel': roofline_2,
         'cpu_baseline': cpu,
         'events_per_step': events_all,
+        'network': network,
     }
     if args.cases:
         line['cases'] = run_cases(torch, dev, dp, idx, w, peak)
@@ -402,6 +407,39 @@ def run_ours(args):
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def run_network(torch, dist, dev, world, rank, steps=1000, warm=200):
+    """The scaled COBA E/I network (1 000 000 neurons, 100 targets per neuron, dt 0.1 ms),
+    postsynaptic-sharded over the ranks, all steps in one cooperative launch per GPU with
+    the spike exchange inside the kernel.  Reported beside the headline, not part of it."""
+    from brainstate_b200.sim import EINet, LIFParams
+    n_exc, n_inh, K = 800000, 200000, 100
+    n = n_exc + n_inh
+    V0 = np.random.RandomState(302).uniform(-60, -50, n).astype(np.float32)
+    params = LIFParams(coba=True, R=0.1, E_e=0., E_i=-80., tau_e=5., tau_i=10.)
+    net = EINet(n_exc, n_inh, K, 0.6, 6.7, seed_e=300, seed_i=301, V0=V0, params=params, device=dev,
+                group=dist.group.WORLD if world > 1 else None, exchange='p2p')
+    net.run(warm, record=False)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    _, counts = net.run(steps, record=False)
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    spikes = int(counts.sum().item())
+    net.close()
+    return {'workload': 'COBA E/I LIF network, 1e6 neurons (800k E / 200k I), 100 targets per neuron, '
+                        'g_exc 0.6, g_inh 6.7, E_exc 0 mV, E_inh -80 mV, dt 0.1 ms; postsynaptic neurons sharded',
+            'steps': steps, 'us_per_step': ms * 1e3 / steps, 'spikes': spikes,
+            'mean_rate_hz': spikes / n / (steps * 1e-4), 'synaptic_events_per_s': spikes * K / (ms * 1e-3),
+            'launches': 1, 'exchange': 'peer stores inside the step kernel' if world > 1 else 'none (one GPU)'}
 
 
 def run_cases(torch, dev, dp, idx, w, peak):
@@ -465,6 +503,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--vectors', type=int, default=64, help='spike vectors per step (per GPU)')
     ap.add_argument('--cases', action='store_true', help='also time the full rate x weight x product grid')
+    ap.add_argument('--no-network', action='store_true', help='skip the sharded network run reported beside the headline')
     ap.add_argument('--profile', action='store_true',
                     help='run only the device-resident loop (for ncu); prints no bench line')
     args = ap.parse_args()
