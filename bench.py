@@ -317,16 +317,20 @@ def run_ours(args):
     host_y1 = torch.empty((T, n), dtype=torch.float32).pin_memory()
     host_y2 = torch.empty((T, n), dtype=torch.float32).pin_memory()
 
+    from brainstate_b200.host import HostEventProducts
+    pipe = HostEventProducts(layer.conn, chunk=16)     # public host-buffer API: upload, products, download overlap
+
     def e2e_pass():
-        s = host_spk.to(dev, non_blocking=True)
-        y1 = layer(s)                                  # spike @ W  (public layer call)
-        y2 = layer.conn @ EventArray(s)                # W @ spike  (public operator)
-        host_y1.copy_(y1, non_blocking=True)
-        host_y2.copy_(y2, non_blocking=True)
+        pipe(host_spk, host_y1, host_y2)               # spike @ W and W @ spike, host memory in and out
         torch.cuda.current_stream().synchronize()
 
     for _ in range(2):
         e2e_pass()
+    if rank == 0:      # the host-buffer path returns what the device-resident path computes
+        dp.run(spk_dev, stream)
+        torch.cuda.synchronize()
+        assert torch.allclose(host_y1.to(dev), dp.y_vecmat, rtol=1e-5, atol=1e-6)
+        assert torch.equal(host_y2.to(dev), dp.y_matvec)
     barrier()
     e2e_steps = max(3, min(args.steps, 10))
     t0 = time.perf_counter()

@@ -9,7 +9,8 @@ all the arithmetic (``include/bsx.h``).  There is no CPU fallback.
 from . import _lib
 from . import event
 from . import nn
+from . import host
 from .event import EventArray, FixedPostNumConn, CSR
 
 __version__ = '0.1.0'
-__all__ = ['event', 'nn', 'EventArray', 'FixedPostNumConn', 'CSR']
+__all__ = ['event', 'nn', 'host', 'EventArray', 'FixedPostNumConn', 'CSR']

@@ -100,6 +100,99 @@ __device__ __forceinline__ void stage_bytes(void* __restrict__ smem, const void*
   }
 }
 
+// Body of the kernel for one way of reading the weights (EAGER: streamed with the
+// indices; otherwise fetched per hit).  All loop arithmetic inside a row is 32-bit and
+// relative to the row start.
+template <bool HETERO, bool EAGER>
+__device__ __forceinline__ void b16_rows(const RowMap& rm, const int32_t* __restrict__ idx,
+                                         const float* __restrict__ w, const uint16_t* __restrict__ smask,
+                                         uint2* __restrict__ list, int64_t n_rows, float* __restrict__ out,
+                                         int nb, bool vec_ok, float w0) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const uint32_t lt = (1u << lane) - 1u;
+  const int b = lane & 15, half = lane >> 4;
+  const uint4* __restrict__ pairs = reinterpret_cast<const uint4*>(list);
+  const int64_t wstep = (int64_t)gridDim.x * (kB16Threads >> 5);
+  for (int64_t row = (int64_t)blockIdx.x * (kB16Threads >> 5) + wid; row < n_rows; row += wstep) {
+    int64_t s, e;
+    rm.range(row, s, e);
+    const int len = (int)(e - s);
+    const int32_t* __restrict__ ri = idx + s;
+    const float* __restrict__ rw = w + s;
+    int head = len, nvec = 0;                        // unaligned arrays: everything is "head"
+    if (vec_ok) {
+      head = (int)((4 - (s & 3)) & 3);
+      if (head > len) head = len;
+      nvec = (len - head) >> 2;
+    }
+    const int tail0 = head + (nvec << 2);            // first entry after the 128-bit body
+    const int4* __restrict__ r4 = reinterpret_cast<const int4*>(ri + head);
+    const float4* __restrict__ rw4 = reinterpret_cast<const float4*>(rw + head);
+    int n_list = 0;
+    float acc = 0.f;
+
+#define BSX_B16_PUSH(VALID, J, PAYLOAD)                                      \
+  do {                                                                       \
+    const uint32_t m_ = (VALID) ? (uint32_t)smask[(J)] : 0u;                 \
+    const uint32_t bal_ = __ballot_sync(0xffffffffu, m_ != 0);               \
+    if (m_) list[n_list + __popc(bal_ & lt)] = make_uint2(m_, (PAYLOAD));    \
+    n_list += __popc(bal_);                                                  \
+  } while (0)
+#define BSX_B16_FLUSH()                                                                        \
+  do {                                                                                         \
+    __syncwarp();                                                                              \
+    if (HETERO && !EAGER) {                                                                    \
+      for (int h = lane; h < n_list; h += 32) list[h].y = __float_as_uint(__ldg(rw + list[h].y)); \
+      __syncwarp();                                                                            \
+    }                                                                                          \
+    if (lane == 0 && (n_list & 1)) list[n_list] = make_uint2(0u, 0u);                          \
+    __syncwarp();                                                                              \
+    const int n_pairs_ = (n_list + 1) >> 1;                                                    \
+    for (int h = half; h < n_pairs_; h += 2) {                                                 \
+      const uint4 en = pairs[h];                                                               \
+      if ((en.x >> b) & 1u) acc += HETERO ? __uint_as_float(en.y) : 1.0f;                      \
+      if ((en.z >> b) & 1u) acc += HETERO ? __uint_as_float(en.w) : 1.0f;                      \
+    }                                                                                          \
+    n_list = 0;                                                                                \
+    __syncwarp();                                                                              \
+  } while (0)
+
+    // 128-bit body: every lane takes 4 consecutive entries per step
+    for (int v0 = 0; v0 < nvec; v0 += 32) {
+      const int v = v0 + lane;
+      const bool ok = v < nvec;
+      int4 j = make_int4(0, 0, 0, 0);
+      float4 wv = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (ok) {
+        j = __ldg(r4 + v);
+        if (HETERO && EAGER) wv = __ldg(rw4 + v);
+      }
+      const uint32_t off = (uint32_t)(head + (v << 2));
+      BSX_B16_PUSH(ok, j.x, (HETERO && EAGER) ? __float_as_uint(wv.x) : off);
+      BSX_B16_PUSH(ok, j.y, (HETERO && EAGER) ? __float_as_uint(wv.y) : off + 1);
+      BSX_B16_PUSH(ok, j.z, (HETERO && EAGER) ? __float_as_uint(wv.z) : off + 2);
+      BSX_B16_PUSH(ok, j.w, (HETERO && EAGER) ? __float_as_uint(wv.w) : off + 3);
+      if (n_list > kB16List - 130) BSX_B16_FLUSH();
+    }
+    // scalar entries: the head [0, head) and the tail [tail0, len), 32 per step
+    const int n_scalar = head + (len - tail0);
+    for (int t0 = 0; t0 < n_scalar; t0 += 32) {
+      const int t = t0 + lane;
+      const bool ok = t < n_scalar;
+      const int rel = t < head ? t : tail0 + (t - head);
+      const int32_t j = ok ? __ldg(ri + rel) : 0;
+      const uint32_t pay = (HETERO && EAGER && ok) ? __float_as_uint(__ldg(rw + rel)) : (uint32_t)rel;
+      BSX_B16_PUSH(ok, j, pay);
+      if (n_list > kB16List - 130) BSX_B16_FLUSH();
+    }
+    BSX_B16_FLUSH();
+    const float total = acc + __shfl_down_sync(0xffffffffu, acc, 16);
+    if (lane < nb) out[(int64_t)lane * n_rows + row] = HETERO ? total : __fmul_rn(total, w0);
+#undef BSX_B16_PUSH
+#undef BSX_B16_FLUSH
+  }
+}
+
 // Per warp: phase 1 scans the row and compacts the hits (mask word != 0) into a
 // list in shared memory with __ballot_sync/__popc; phase 2 walks the list with
 // lane = (half, vector): the lanes of half h take the entry pairs {4k+2h, 4k+2h+1}
@@ -122,9 +215,6 @@ event_matvec_b16_kernel(RowMap rm, const int32_t* __restrict__ idx, const float*
   // [warps][kB16List] hit lists, then the mask words
   uint2* lists = reinterpret_cast<uint2*>(smem_raw);
   uint16_t* smask = reinterpret_cast<uint16_t*>(smem_raw + sizeof(uint2) * kB16List * (kB16Threads / 32));
-  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-  const uint32_t lt = (1u << lane) - 1u;
-  const int b = lane & 15, half = lane >> 4;
   stage_bytes(smask, masks, (uint32_t)(n_cols_pad * 2), use_tma, &bar);
   const float w0 = HETERO ? 0.f : __ldg(w);
   // weight_mode: 0 decide from the density, 1 always stream, 2 always fetch on hit
@@ -133,94 +223,9 @@ event_matvec_b16_kernel(RowMap rm, const int32_t* __restrict__ idx, const float*
     if (weight_mode == 1) eager = true;
     else if (weight_mode == 0) eager = (int64_t)__ldg(nonzero_words) * 16 > n_cols;
   }
-  const int4* __restrict__ idx4 = reinterpret_cast<const int4*>(idx);
-  const float4* __restrict__ w4 = reinterpret_cast<const float4*>(w);
-  uint2* __restrict__ list = lists + wid * kB16List;
-  int n_list = 0;
-  float acc = 0.f;
-
-  // Called by all 32 lanes together (the ballot needs the whole warp); lanes without
-  // a valid entry pass VALID = false.  PAYLOAD: weight bits (streamed weights) or the
-  // offset of the synapse in its row (weights fetched later).
-#define BSX_B16_PUSH(VALID, J, PAYLOAD)                                      \
-  do {                                                                       \
-    const uint32_t m_ = (VALID) ? (uint32_t)smask[(J)] : 0u;                 \
-    const uint32_t bal_ = __ballot_sync(0xffffffffu, m_ != 0);               \
-    if (m_) list[n_list + __popc(bal_ & lt)] = make_uint2(m_, (PAYLOAD));    \
-    n_list += __popc(bal_);                                                  \
-  } while (0)
-
-  const int64_t wstep = (int64_t)gridDim.x * (kB16Threads >> 5);
-  for (int64_t row = (int64_t)blockIdx.x * (kB16Threads >> 5) + wid; row < n_rows; row += wstep) {
-    int64_t s, e;
-    rm.range(row, s, e);
-    int64_t a0 = e, a1 = e;
-    if (vec_ok) {
-      a0 = (s + 3) & ~int64_t(3);
-      if (a0 > e) a0 = e;
-      a1 = e & ~int64_t(3);
-      if (a1 < a0) a1 = a0;
-    }
-    acc = 0.f;
-    n_list = 0;
-    auto flush = [&]() {
-      __syncwarp();
-      if (HETERO && !eager) {  // turn row offsets into weights, 32 loads in flight per round
-        for (int h = lane; h < n_list; h += 32) list[h].y = __float_as_uint(__ldg(w + s + list[h].y));
-        __syncwarp();
-      }
-      if (lane == 0 && (n_list & 1)) list[n_list] = make_uint2(0u, 0u);   // pad to a whole pair
-      __syncwarp();
-      const uint4* __restrict__ pairs = reinterpret_cast<const uint4*>(list);
-      const int n_pairs = (n_list + 1) >> 1;
-      for (int h = half; h < n_pairs; h += 2) {
-        const uint4 en = pairs[h];
-        if ((en.x >> b) & 1u) acc += HETERO ? __uint_as_float(en.y) : 1.0f;
-        if ((en.z >> b) & 1u) acc += HETERO ? __uint_as_float(en.w) : 1.0f;
-      }
-      n_list = 0;
-      __syncwarp();
-    };
-    // 128-bit body: every lane takes 4 consecutive entries per step
-    const int64_t q1 = a1 >> 2;
-    for (int64_t qb = (a0 >> 2); qb < q1; qb += 32) {
-      const int64_t q = qb + lane;
-      const bool ok = q < q1;
-      int4 j = make_int4(0, 0, 0, 0);
-      float4 wv = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (ok) {
-        j = __ldg(idx4 + q);
-        if (eager) wv = __ldg(w4 + q);
-      }
-      const uint32_t off = (uint32_t)((q << 2) - s);
-      BSX_B16_PUSH(ok, j.x, eager ? __float_as_uint(wv.x) : off);
-      BSX_B16_PUSH(ok, j.y, eager ? __float_as_uint(wv.y) : off + 1);
-      BSX_B16_PUSH(ok, j.z, eager ? __float_as_uint(wv.z) : off + 2);
-      BSX_B16_PUSH(ok, j.w, eager ? __float_as_uint(wv.w) : off + 3);
-      if (n_list > kB16List - 130) flush();
-    }
-    // scalar head [s, a0) and tail [a1, e)
-    for (int64_t pb = s; pb < a0; pb += 32) {
-      const int64_t p = pb + lane;
-      const bool ok = p < a0;
-      const int32_t j = ok ? __ldg(idx + p) : 0;
-      const uint32_t pay = (eager && ok) ? __float_as_uint(__ldg(w + p)) : (uint32_t)(p - s);
-      BSX_B16_PUSH(ok, j, pay);
-      if (n_list > kB16List - 130) flush();
-    }
-    for (int64_t pb = a1; pb < e; pb += 32) {
-      const int64_t p = pb + lane;
-      const bool ok = p < e;
-      const int32_t j = ok ? __ldg(idx + p) : 0;
-      const uint32_t pay = (eager && ok) ? __float_as_uint(__ldg(w + p)) : (uint32_t)(p - s);
-      BSX_B16_PUSH(ok, j, pay);
-      if (n_list > kB16List - 130) flush();
-    }
-    flush();
-    const float total = acc + __shfl_down_sync(0xffffffffu, acc, 16);
-    if (lane < nb) out[(int64_t)lane * n_rows + row] = HETERO ? total : __fmul_rn(total, w0);
-  }
-#undef BSX_B16_PUSH
+  uint2* list = lists + (threadIdx.x >> 5) * kB16List;
+  if (HETERO && eager) b16_rows<HETERO, true>(rm, idx, w, smask, list, n_rows, out, nb, vec_ok, w0);
+  else b16_rows<HETERO, false>(rm, idx, w, smask, list, n_rows, out, nb, vec_ok, w0);
 }
 
 size_t b16_mask_bytes(int64_t batch, int64_t n_post) {

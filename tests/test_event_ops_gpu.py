@@ -277,6 +277,30 @@ def test_batched_training_step_at_microbenchmark_size(microbench, c_oracle, cuda
     assert torch.equal(dx, dx2) and torch.equal(dw, dw2)         # no atomics: reproducible
 
 
+def test_host_buffer_pipeline_equals_device_path(cuda):
+    """Pinned host spikes in, pinned host results out, chunks overlapped on three streams."""
+    from brainstate_b200 import EventArray
+    from brainstate_b200.host import HostEventProducts
+    n, K = 1000, 37
+    conn, idx, _, w = make(n, n, K, 31, True, cuda)
+    rs = np.random.RandomState(32)
+    for T in (5, 16, 50):
+        spk = rs.random_sample((T, n)) < 0.05
+        hs = torch.from_numpy(spk).pin_memory()
+        h1 = torch.empty((T, n), dtype=torch.float32).pin_memory()
+        h2 = torch.empty((T, n), dtype=torch.float32).pin_memory()
+        pipe = HostEventProducts(conn, chunk=16)
+        pipe(hs, h1, h2)
+        pipe(hs, h1, h2)                                   # reusable
+        torch.cuda.synchronize()
+        close(h1, eo.event_vecmat(spk, idx, w, n))
+        close(h2, eo.event_matvec(spk, idx, w, n))
+        d2 = conn @ EventArray(torch.from_numpy(spk).to(cuda))
+        assert torch.equal(h2.to(cuda), d2)
+    with pytest.raises(ValueError):
+        HostEventProducts(conn)(torch.from_numpy(spk), h1, h2)         # not pinned
+
+
 def test_transposed_copy_is_canonical(cuda):
     n_pre, n_post, K = 123, 77, 19
     for layout in (None, 0.5):
