@@ -133,6 +133,7 @@ def cpu_pass(co, idx, w, spk_sample):
 def cpu_baseline(idx, w, spk, budget_s=12.0, sample_vectors=8):
     from oracle import c_oracle as co
     co.build()
+    co.use_all_cores()
     K = idx.shape[1]
     sample = np.ascontiguousarray(spk[:sample_vectors]).astype(np.uint8)
     events = 2 * int(sample.sum()) * K
@@ -161,6 +162,7 @@ def run_reference_arm(args):
     n, K, idx, w, spk = build_workload(max(args.vectors, 8))
     from oracle import c_oracle as co
     co.build()
+    co.use_all_cores()
     sample = np.ascontiguousarray(spk[:8]).astype(np.uint8)
     events = 2 * int(sample.sum()) * K
     for _ in range(max(args.warmup, 1)):

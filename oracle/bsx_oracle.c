@@ -212,6 +212,16 @@ void orc_vecmat_dw(const float* x, const float* ct, int64_t batch, int64_t n_pre
     }
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; a caller that wants all the
+ * host cores sets the count explicitly. */
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -140,3 +140,14 @@ def vecmat_dw(x, ct, idx, n_pre, n_post, indptr=None, event=False):
 
 def num_threads():
     return int(lib().orc_num_threads())
+
+
+def use_all_cores():
+    """Sets the OpenMP thread count to the cores this process may run on (launchers
+    like torchrun export OMP_NUM_THREADS=1).  Returns the count."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().orc_set_threads(C.c_int(n))
+    return num_threads()
