@@ -83,6 +83,11 @@ SIGNATURES = {
     'bsx_device_count': (_i32, []),
     'bsx_read_status': (_i32, [_vp, C.POINTER(C.c_int32), _vp]),
     'bsx_host_fixed_num_indices': (_i64, [C.c_uint32, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
+    'bsx_host_gen_new': (_vp, [C.c_uint32]),
+    'bsx_host_gen_free': (None, [_vp]),
+    'bsx_host_gen_rows': (_i64, [_vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
+    'bsx_lognormal_weights': (_i32, [_connp, _vp, _i64, C.c_uint32, C.c_double, C.c_double, _f32, _vp, _vp]),
+    'bsx_lognormal_weight_at': (_f32, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_double, C.c_double, _f32]),
     'bsx_validate_conn': (_i32, [_connp, _vp, _vp]),
     'bsx_pack_spikes': (_i32, [_vp, _i32, _i64, _i64, _vp, _vp]),
     'bsx_transpose_workspace_bytes': (_sz, [_i64, _i64, _i64]),

@@ -1,4 +1,5 @@
 // Diagnostics, small utilities and the host-side connectivity generator.
+#include <new>
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
@@ -182,6 +183,45 @@ int64_t bsx_host_fixed_num_indices(uint32_t seed, int64_t n_pre, int64_t n_post,
       if (v >= c0 && v < c1) { host_out[written++] = (int32_t)(v - c0); ++kept; }
     }
     if (host_row_counts) host_row_counts[r - row_begin] = kept;
+  }
+  return written;
+}
+
+// ---- stateful form of the generator: one stream, drawn in row chunks -----------
+void* bsx_host_gen_new(uint32_t seed) { return new (std::nothrow) Mt19937(seed); }
+
+void bsx_host_gen_free(void* gen) { delete static_cast<Mt19937*>(gen); }
+
+int64_t bsx_host_gen_rows(void* gen, int64_t rows, int64_t n_post, int64_t conn_num, int64_t col_begin,
+                          int64_t col_end, int32_t* host_out, int16_t* host_k_out, int32_t* host_row_counts) {
+  if (!gen) return fail(BSX_ERR_INVALID_ARG, "bsx_host_gen_rows: generator is NULL");
+  if (rows < 0 || n_post < 1 || conn_num < 0 || n_post > (int64_t)INT32_MAX || conn_num > 32767)
+    return fail(BSX_ERR_INVALID_ARG, "bsx_host_gen_rows: bad sizes (conn_num must be below 32768)");
+  const bool filter = col_begin < col_end;
+  if (filter && (col_begin < 0 || col_end > n_post))
+    return fail(BSX_ERR_INVALID_ARG, "bsx_host_gen_rows: bad column range");
+  if (!host_out && rows > 0 && conn_num > 0) return fail(BSX_ERR_INVALID_ARG, "bsx_host_gen_rows: output is NULL");
+  Mt19937& mt = *static_cast<Mt19937*>(gen);
+  const uint32_t top = (uint32_t)(n_post - 1);
+  uint32_t mask = top;
+  mask |= mask >> 1; mask |= mask >> 2; mask |= mask >> 4; mask |= mask >> 8; mask |= mask >> 16;
+  const uint32_t c0 = (uint32_t)(filter ? col_begin : 0), c1 = (uint32_t)(filter ? col_end : n_post);
+  int64_t written = 0;
+  for (int64_t r = 0; r < rows; ++r) {
+    int32_t kept = 0;
+    for (int64_t k = 0; k < conn_num; ++k) {
+      uint32_t v = 0;
+      if (top) {  // a one-value range consumes no draws
+        do { v = mt.next() & mask; } while (v > top);
+      }
+      if (v >= c0 && v < c1) {
+        host_out[written] = (int32_t)(v - c0);
+        if (host_k_out) host_k_out[written] = (int16_t)k;
+        ++written;
+        ++kept;
+      }
+    }
+    if (host_row_counts) host_row_counts[r] = kept;
   }
   return written;
 }

@@ -29,7 +29,8 @@ from ._lib import BsxLifParams, BsxNet, check, lib
 from .event import CSR, FixedPostNumConn
 from .nn._event_fixedprob import EventFixedProb, _device
 
-__all__ = ['LIFParams', 'EINet', 'shard_bounds', 'words_per_rank', 'sharded_block', 'unpack_raster']
+__all__ = ['LIFParams', 'Lognormal', 'EINet', 'shard_bounds', 'words_per_rank', 'sharded_block',
+           'build_projection', 'unpack_raster']
 
 
 @dataclass
@@ -105,6 +106,81 @@ def sharded_block(seed: int, n_pre: int, n_post: int, conn_num: int, col0: int, 
     return buf[:n].copy(), indptr
 
 
+@dataclass
+class Lognormal:
+    """Heterogeneous weights ``scale * exp(mu + sigma * z)``, ``z`` standard normal keyed by
+    the synapse's position ``(row, k)`` and ``seed`` (so every shard can fill its own)."""
+    mu: float = -2.0
+    sigma: float = 0.5
+    seed: int = 0
+    scale: float = 1.0
+
+
+def build_projection(seed: int, n_pre: int, n_post: int, conn_num: int, weight, device, col0: int = 0,
+                     col1: Optional[int] = None, chunk_rows: Optional[int] = None):
+    """One projection's connectivity on the device, drawn from the reference's seeded
+    stream (``RandomState(seed).randint(0, n_post, (n_pre, conn_num))``,
+    ``brainstate/nn/_event_fixedprob.py:165-171``) in row chunks, so that neither the
+    host nor the device ever holds more than a chunk beyond the final arrays.
+
+    With ``[col0, col1)`` narrower than ``[0, n_post)`` the result is the CSR block of
+    one postsynaptic shard (local column ids); otherwise the full fixed-number matrix.
+    ``weight``: a float (homogeneous) or :class:`Lognormal`.
+    """
+    l = lib()
+    col1 = n_post if col1 is None else col1
+    filtered = not (col0 == 0 and col1 == n_post)
+    if chunk_rows is None:
+        chunk_rows = max(1, (1 << 26) // max(conn_num, 1))          # 64 Mi entries per chunk
+    gen = l.bsx_host_gen_new(C.c_uint32(int(seed) & 0xffffffff))
+    if not gen:
+        raise MemoryError('bsx_host_gen_new failed')
+    hetero = isinstance(weight, Lognormal)
+    try:
+        if not filtered:
+            idx = torch.empty((n_pre, conn_num), dtype=torch.int32, device=device)
+            buf = torch.empty((min(chunk_rows, n_pre), conn_num), dtype=torch.int32).pin_memory()
+            for r0 in range(0, n_pre, chunk_rows):
+                rows = min(chunk_rows, n_pre - r0)
+                n = l.bsx_host_gen_rows(gen, rows, n_post, conn_num, 0, 0, buf.data_ptr(), None, None)
+                check(int(n))
+                idx[r0:r0 + rows].copy_(buf[:rows])
+            kpos, indptr = None, None
+        else:
+            pieces, kpieces, counts = [], [], np.empty(n_pre, np.int32)
+            buf = np.empty(min(chunk_rows, n_pre) * conn_num, np.int32)
+            kbuf = np.empty(buf.size, np.int16) if hetero else None
+            for r0 in range(0, n_pre, chunk_rows):
+                rows = min(chunk_rows, n_pre - r0)
+                n = l.bsx_host_gen_rows(gen, rows, n_post, conn_num, col0, col1, buf.ctypes.data,
+                                        None if kbuf is None else kbuf.ctypes.data, counts[r0:].ctypes.data)
+                check(int(n))
+                pieces.append(torch.from_numpy(buf[:n].copy()).to(device))
+                if hetero:
+                    kpieces.append(torch.from_numpy(kbuf[:n].copy()).to(device))
+            idx = torch.cat(pieces) if pieces else torch.empty(0, dtype=torch.int32, device=device)
+            kpos = torch.cat(kpieces) if hetero and kpieces else None
+            ip = np.zeros(n_pre + 1, np.int64)
+            np.cumsum(counts, out=ip[1:])
+            indptr = torch.from_numpy(ip).to(device)
+    finally:
+        l.bsx_host_gen_free(gen)
+    n_cols = col1 - col0
+    if hetero:
+        w = torch.empty(idx.shape, dtype=torch.float32, device=device)
+        conn = (FixedPostNumConn((w, idx), shape=(n_pre, n_cols)) if indptr is None
+                else CSR((w, idx, indptr), shape=(n_pre, n_cols)))
+        st = conn._struct()
+        check(l.bsx_lognormal_weights(C.byref(st), _lib.ptr(kpos), 0, C.c_uint32(int(weight.seed) & 0xffffffff),
+                                      float(weight.mu), float(weight.sigma), float(weight.scale), w.data_ptr(),
+                                      _lib.current_stream()))
+        torch.cuda.synchronize(device)
+        return conn
+    if indptr is None:
+        return FixedPostNumConn((float(weight), idx), shape=(n_pre, n_cols))
+    return CSR((float(weight), idx, indptr), shape=(n_pre, n_cols))
+
+
 class EINet:
     """E/I network of LIF neurons with exponential synapses.
 
@@ -113,7 +189,8 @@ class EINet:
     n_exc, n_inh : population sizes; global ids ``[0, n_exc)`` are excitatory.
     conn_num : connection probability (float) or number of targets per neuron (int),
         as in ``EventFixedProb``.
-    w_e, w_i : homogeneous synaptic weights of the two projections.
+    w_e, w_i : synaptic weights of the two projections: a float (homogeneous) or
+        :class:`Lognormal` (heterogeneous, generated on the device).
     seed_e, seed_i : connectivity seeds (``EventFixedProb(..., seed=...)``).
     V0 : initial membrane potentials, ``(n_exc + n_inh,)``.
     delay_e, delay_i : synaptic delays in steps beyond the next step (0: a spike of
@@ -124,7 +201,7 @@ class EINet:
         the postsynaptic neurons are sharded.
     """
 
-    def __init__(self, n_exc: int, n_inh: int, conn_num, w_e: float, w_i: float, *, seed_e: int, seed_i: int,
+    def __init__(self, n_exc: int, n_inh: int, conn_num, w_e, w_i, *, seed_e: int, seed_i: int,
                  V0, params: Optional[LIFParams] = None, device=None, group=None, delay_e: int = 0,
                  delay_i: int = 0, exchange: str = 'nccl'):
         if exchange not in ('nccl', 'p2p'):
@@ -147,17 +224,15 @@ class EINet:
         K = conn_num if isinstance(conn_num, int) else int(self.n * conn_num)
         self.conn_num = K
         dev = self.dev
-        if self.world == 1:
+        hetero = isinstance(w_e, Lognormal) or isinstance(w_i, Lognormal)
+        if self.world == 1 and not hetero and self.n * K < (1 << 31):
             self.E = EventFixedProb(self.n_exc, self.n, K, float(w_e), seed=seed_e, device=dev)
             self.I = EventFixedProb(self.n_inh, self.n, K, float(w_i), seed=seed_i, device=dev)
             self.conn_e, self.conn_i = self.E.conn, self.I.conn
         else:
-            ie, pe = sharded_block(seed_e, self.n_exc, self.n, K, self.first, self.last)
-            ii, pi = sharded_block(seed_i, self.n_inh, self.n, K, self.first, self.last)
-            self.conn_e = CSR((float(w_e), torch.from_numpy(ie).to(dev), torch.from_numpy(pe).to(dev)),
-                              shape=(self.n_exc, self.n_local))
-            self.conn_i = CSR((float(w_i), torch.from_numpy(ii).to(dev), torch.from_numpy(pi).to(dev)),
-                              shape=(self.n_inh, self.n_local))
+            c0, c1 = (0, self.n) if self.world == 1 else (self.first, self.last)
+            self.conn_e = build_projection(seed_e, self.n_exc, self.n, K, w_e, dev, c0, c1)
+            self.conn_i = build_projection(seed_i, self.n_inh, self.n, K, w_i, dev, c0, c1)
         V0 = np.asarray(V0, np.float32)
         assert V0.shape == (self.n,)
         self.V = torch.from_numpy(V0[self.first:self.last].copy()).to(dev)

@@ -100,6 +100,28 @@ int64_t bsx_host_fixed_num_indices(uint32_t seed, int64_t n_pre, int64_t n_post,
                                    int64_t col_begin, int64_t col_end,
                                    int32_t* host_out, int32_t* host_row_counts);
 
+/* The same stream in stateful form, for matrices drawn in row chunks (a 32 GB index
+ * matrix is produced and uploaded piece by piece): create, draw the next `rows` rows,
+ * free.  With a column window only targets inside it are kept; host_k_out (may be
+ * NULL) receives the position k of every kept entry inside its row, host_row_counts
+ * (may be NULL) how many each row kept.  conn_num < 32768. */
+void* bsx_host_gen_new(uint32_t seed);
+void bsx_host_gen_free(void* gen);
+int64_t bsx_host_gen_rows(void* gen, int64_t rows, int64_t n_post, int64_t conn_num, int64_t col_begin,
+                          int64_t col_end, int32_t* host_out, int16_t* host_k_out, int32_t* host_row_counts);
+
+/*
+ * Heterogeneous weights keyed by position: w(row, k) = sign * exp(mu + sigma * z), z a
+ * standard normal derived from a hash of (seed, row0 + row, k).  kpos (may be NULL: k is
+ * the offset inside the row) gives k for every stored entry, as bsx_host_gen_rows
+ * reports it for a column-filtered block.  Stands for a `conn_weight` initializer
+ * callable (brainstate/nn/_event_fixedprob.py:173-175) at sizes where the weights are
+ * generated on the device; bsx_lognormal_weight_at is the same value on the host.
+ */
+int bsx_lognormal_weights(const bsx_conn_t* conn, const int16_t* kpos, int64_t row0, uint32_t seed, double mu,
+                          double sigma, float sign, float* weights_out, bsx_stream_t stream);
+float bsx_lognormal_weight_at(uint32_t seed, uint32_t row, uint32_t k, double mu, double sigma, float sign);
+
 /* ---- construction-time checks and derived layouts ---------------------- */
 /* Writes BSX_ERR_INDEX_RANGE to *status_word if any index is outside [0, n_post)
  * or indptr is not non-decreasing; leaves it untouched otherwise.  The reference

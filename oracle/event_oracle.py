@@ -243,6 +243,35 @@ def event_linear(spk, weight, out_size, float_as_event=True):
 
 
 # ----------------------------------------------------------------------------
+# position-keyed heterogeneous weights (builder-specified: the reference takes any
+# initializer callable for conn_weight, brainstate/nn/_event_fixedprob.py:173-175)
+# ----------------------------------------------------------------------------
+
+def _mix32(x):
+    x = np.asarray(x, np.uint32).copy()
+    with np.errstate(over='ignore'):
+        x ^= x >> np.uint32(16); x *= np.uint32(0x7feb352d)
+        x ^= x >> np.uint32(15); x *= np.uint32(0x846ca68b)
+        x ^= x >> np.uint32(16)
+    return x
+
+
+def lognormal_weights(seed, rows, ks, mu, sigma, sign=1.0):
+    """``sign * exp(mu + sigma * z)`` with ``z`` a standard normal from a 32-bit hash
+    of ``(seed, row, k)`` (Box-Muller in float64, one rounding to float32)."""
+    rows = np.asarray(rows, np.uint32)
+    ks = np.asarray(ks, np.uint32)
+    with np.errstate(over='ignore'):
+        h = _mix32(_mix32(rows + np.uint32(seed) * np.uint32(0x9e3779b9))
+                   ^ (ks * np.uint32(0x85ebca6b) + np.uint32(0x27d4eb2f)))
+        g = _mix32(h ^ np.uint32(0x165667b1))
+    u1 = (h.astype(np.float64) + 1.0) * (1.0 / 4294967296.0)
+    u2 = g.astype(np.float64) * (1.0 / 4294967296.0)
+    z = np.sqrt(-2.0 * np.log(u1)) * np.cos(6.283185307179586476925286766559 * u2)
+    return (np.float32(sign) * np.exp(mu + sigma * z).astype(F32)).astype(F32)
+
+
+# ----------------------------------------------------------------------------
 # spike packing
 # ----------------------------------------------------------------------------
 

@@ -207,3 +207,50 @@ def test_wait_for_a_silent_peer_runs_out_and_reports(bsx, cuda):
     assert int(counts[0].item()) == -1                      # stopped at the first step boundary
     x = torch.ones(8, device=cuda)                          # the context is still healthy
     assert float((x + 1).sum()) == 16.0
+
+
+def test_large_network_recipe_at_reduced_size(cuda):
+    """The large-network recipe (fixed 1000 targets per neuron, lognormal(-2, 0.5) weights
+    signed by population, hashed background drive, V_rest below threshold) on 10 000
+    neurons: per-step increments within rel 1e-5 / abs 1e-6 of the oracle, rasters
+    identical for the first 200 steps, long-run rate within 1 %."""
+    from brainstate_b200.sim import EINet, LIFParams, Lognormal, unpack_raster
+    n_exc, n_inh, K = 8000, 2000, 1000
+    n = n_exc + n_inh
+    V0 = np.random.RandomState(404).uniform(-65, -52, n).astype(np.float32)
+    params = LIFParams(V_rest=-60., ext_rate_hz=9000., ext_weight=0.3, ext_seed=405)
+    net = EINet(n_exc, n_inh, K, Lognormal(-2.0, 0.5, 402, 1.0), Lognormal(-2.0, 0.5, 403, -6.0),
+                seed_e=400, seed_i=401, V0=V0, params=params, device=cuda)
+    ie, ii = eo.fixed_num_indices(400, n_exc, n, K), eo.fixed_num_indices(401, n_inh, n, K)
+    assert np.array_equal(net.conn_e.indices.cpu().numpy(), ie)
+    we = eo.lognormal_weights(402, np.repeat(np.arange(n_exc), K), np.tile(np.arange(K), n_exc), -2.0, 0.5, 1.0).reshape(n_exc, K)
+    wi = eo.lognormal_weights(403, np.repeat(np.arange(n_inh), K), np.tile(np.arange(K), n_inh), -2.0, 0.5, -6.0).reshape(n_inh, K)
+    np.testing.assert_allclose(net.conn_e.data.cpu().numpy(), we, rtol=1e-6, atol=0)
+    np.testing.assert_allclose(net.conn_i.data.cpu().numpy(), wi, rtol=1e-6, atol=0)
+    orc = eo.EINetOracle(n_exc, n_inh, ie, net.conn_e.data.cpu().numpy(), ii, net.conn_i.data.cpu().numpy(), V0=V0,
+                         V_rest=-60., ext_threshold=params.ext_threshold, ext_seed=405, ext_weight=0.3)
+    steps = 600
+    raster, counts = net.run(steps)
+    got = unpack_raster(raster, n)
+    ref = orc.run(steps)
+    assert ref[:200].sum() > 100
+    assert np.array_equal(got[:200], ref[:200])
+    r_got, r_ref = got[200:].mean(), ref[200:].mean()
+    assert abs(r_got - r_ref) <= 0.01 * r_ref
+    np.testing.assert_allclose(net.g_e.cpu().numpy(), orc.g_e, rtol=1e-3, atol=1e-4)   # after 600 chaotic steps
+
+
+def test_chunked_builder_equals_one_shot(cuda):
+    """Row chunks of the seeded stream, with and without a column window."""
+    from brainstate_b200.sim import build_projection, Lognormal
+    seed, n_pre, n_post, K = 77, 333, 1000, 41
+    full = eo.fixed_num_indices(seed, n_pre, n_post, K)
+    a = build_projection(seed, n_pre, n_post, K, 0.5, cuda, chunk_rows=50)
+    assert np.array_equal(a.indices.cpu().numpy(), full)
+    c0, c1 = 320, 704
+    b = build_projection(seed, n_pre, n_post, K, Lognormal(-1.0, 0.3, 9, -2.0), cuda, c0, c1, chunk_rows=64)
+    keep = (full >= c0) & (full < c1)
+    assert np.array_equal(b.indices.cpu().numpy(), full[keep] - c0)
+    assert np.array_equal(np.diff(b.indptr.cpu().numpy()), keep.sum(axis=1))
+    rows, ks = np.nonzero(keep)
+    np.testing.assert_allclose(b.data.cpu().numpy(), eo.lognormal_weights(9, rows, ks, -1.0, 0.3, -2.0), rtol=1e-6)
