@@ -214,10 +214,10 @@ class DevicePass:
         self.st = self.conn._struct()
         self.y_vecmat = torch.empty((vectors, n), dtype=torch.float32, device=dev)
         self.y_matvec = torch.empty((vectors, n), dtype=torch.float32, device=dev)
-        self.words = (n + 31) // 32
-        self.bits = torch.empty((vectors, self.words), dtype=torch.int32, device=dev)
         self.ws_bytes = self.lib.bsx_event_vecmat_workspace_bytes(vectors, n)
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=dev)
+        self.words = (n + 31) // 32
+        self.bits = torch.empty((vectors, self.words), dtype=torch.int32, device=dev)   # used by --cases
         self.mv_ws_bytes = self.lib.bsx_event_matvec_workspace_bytes(vectors, n)
         self.mv_ws = torch.empty(self.mv_ws_bytes, dtype=torch.uint8, device=dev)
         self.passes = (vectors + 15) // 16
@@ -256,7 +256,6 @@ def run_ours(args):
 
     from brainstate_b200 import _lib
     from brainstate_b200.nn import EventFixedProb
-    from brainstate_b200 import EventArray
     T = args.vectors
     n, K, idx, w, spk = build_workload(T, rank)
     events_pass = 2 * int(spk.sum()) * K

@@ -10,13 +10,6 @@ namespace bsx {
 
 static thread_local char g_error[512] = "";
 
-void set_error(const char* fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_error, sizeof(g_error), fmt, ap);
-  va_end(ap);
-}
-
 int fail(int status, const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);

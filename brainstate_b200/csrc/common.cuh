@@ -13,7 +13,6 @@
 namespace bsx {
 
 // ---- host-side error plumbing (thread-local message, integer codes) --------
-void set_error(const char* fmt, ...);
 int fail(int status, const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 

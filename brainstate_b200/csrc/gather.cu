@@ -7,8 +7,6 @@
 //
 // HBM traffic: 4 B per stored synapse for the indices; weights are touched only
 // where a spike hits (event) or for every synapse (float / vjp).
-#include <cooperative_groups.h>
-
 #include "common.cuh"
 #include "internal.cuh"
 

@@ -87,17 +87,6 @@ def afferent_csr(seed: int, n_pre: int, n_post: int, conn_num: int, afferent_rat
 # helpers over the two layouts
 # ----------------------------------------------------------------------------
 
-def _rows(indices, indptr, n_pre):
-    """Yield ``(i, start, end)`` flat ranges for the fixed-number or CSR layout."""
-    if indptr is None:
-        K = indices.shape[-1] if indices.ndim == 2 else indices.size // max(n_pre, 1)
-        for i in range(n_pre):
-            yield i, i * K, (i + 1) * K
-    else:
-        for i in range(n_pre):
-            yield i, int(indptr[i]), int(indptr[i + 1])
-
-
 def _flat(indices, weights):
     idx = np.ascontiguousarray(indices).reshape(-1)
     w = np.asarray(weights, dtype=F32)
