@@ -113,62 +113,98 @@ __host__ __device__ __forceinline__ uint32_t drive_hash(uint32_t seed, uint32_t 
   return mix32(mix32(gid + seed * 0x9e3779b9u) ^ (step * 0x85ebca6bu + 0xc2b2ae35u));
 }
 
+// (exp(z) - 1) / z.  For |z| <= 0.25 (every realistic dt * df/dV) a degree-6 Taylor
+// polynomial in Horner form, each multiply and add rounded separately in float32 so
+// that a host restatement doing the same operations matches bit for bit (the
+// truncation error, z^7/5040, is below float32 resolution there); otherwise
+// evaluated in double and rounded once.
 __device__ __forceinline__ float exprel_once(float z) {
-  if (z == 0.0f) return 1.0f;
+  if (fabsf(z) <= 0.25f) {
+    float p = 0.0013888889f;                                  // 1/720
+    p = __fadd_rn(__fmul_rn(p, z), 0.008333334f);             // 1/120
+    p = __fadd_rn(__fmul_rn(p, z), 0.041666668f);             // 1/24
+    p = __fadd_rn(__fmul_rn(p, z), 0.16666667f);              // 1/6
+    p = __fadd_rn(__fmul_rn(p, z), 0.5f);
+    p = __fadd_rn(__fmul_rn(p, z), 1.0f);
+    return p;
+  }
   const double zd = (double)z;
   return (float)(expm1(zd) / zd);
 }
 
-// Phase B for the 32 neurons of local word `word`; returns the spike word.
-__device__ __forceinline__ uint32_t update_word(const NetDev& a, int64_t word, int lane, int64_t step,
-                                                bool* spiked) {
-  const bsx_lif_params_t& p = a.p;
-  const int64_t i = word * 32 + lane;
-  bool spk = false;
-  if (i < a.n_local) {
-    // all loads first: the six arrays never alias, and a store between two loads
-    // would otherwise serialise the memory round trips
-    float* __restrict__ pde = a.delta_e;
-    float* __restrict__ pdi = a.delta_i;
-    float* __restrict__ pge = a.g_e;
-    float* __restrict__ pgi = a.g_i;
-    float* __restrict__ pV = a.V;
-    int32_t* __restrict__ pref = a.ref;
-    const float de_in = pde[i], di = pdi[i], ge0 = pge[i], gi0 = pgi[i], V = pV[i];
-    const int32_t r = pref[i];
-    float de = de_in;
-    if (p.ext_threshold && drive_hash(p.ext_seed, (uint32_t)(a.first + i), (uint32_t)step) < p.ext_threshold)
-      de = __fadd_rn(de, p.ext_weight);
-    const float ge = __fadd_rn(__fmul_rn(ge0, p.decay_e), de);
-    const float gi = __fadd_rn(__fmul_rn(gi0, p.decay_i), di);
-    float cur;
-    if (p.coba) cur = __fadd_rn(__fmul_rn(ge, __fsub_rn(p.E_e, V)), __fmul_rn(gi, __fsub_rn(p.E_i, V)));
-    else cur = __fadd_rn(ge, gi);
-    const float drive = __fmul_rn(p.R, __fadd_rn(cur, p.I_ext));
-    const float num = __fadd_rn(__fsub_rn(p.V_rest, V), drive);
-    float Vn;
-    if (p.coba) {
-      const float f = __fmul_rn(num, p.inv_tau_m);
-      const float gsum = __fadd_rn(ge, gi);
-      const float J = __fmul_rn(-__fadd_rn(1.0f, __fmul_rn(p.R, gsum)), p.inv_tau_m);
-      const float gain = __fmul_rn(p.dt, exprel_once(__fmul_rn(p.dt, J)));
-      Vn = __fadd_rn(V, __fmul_rn(gain, f));
-    } else {
-      Vn = __fadd_rn(V, __fmul_rn(p.cuba_gain, num));
-    }
-    const bool refractory = r > 0;
-    if (refractory) Vn = V;
-    spk = (Vn >= p.V_th) && !refractory;
-    if (de_in != 0.0f) pde[i] = 0.0f;
-    if (di != 0.0f) pdi[i] = 0.0f;
-    pge[i] = ge;
-    pgi[i] = gi;
-    pV[i] = spk ? p.V_reset : Vn;
-    const int32_t rn = spk ? p.ref_steps : (r > 0 ? r - 1 : 0);
-    if (rn != r) pref[i] = rn;
+// Phase B is split in two so that a warp can have the loads of two words in flight
+// before it computes either: one L2 round trip per pair instead of per word.
+struct NeuronIn {
+  float de, di, ge0, gi0, V;
+  int32_t r;
+  bool valid;
+};
+
+__device__ __forceinline__ NeuronIn load_neuron(const NetDev& a, int64_t i) {
+  NeuronIn s;
+  s.valid = i >= 0 && i < a.n_local;
+  if (s.valid) {
+    s.de = a.delta_e[i];
+    s.di = a.delta_i[i];
+    s.ge0 = a.g_e[i];
+    s.gi0 = a.g_i[i];
+    s.V = a.V[i];
+    s.r = a.ref[i];
   }
-  *spiked = spk;
-  return __ballot_sync(0xffffffffu, spk);
+  return s;
+}
+
+// Synapse decay + increment, membrane update, threshold, reset, refractory count for
+// neuron i; stores the new state (unchanged values are not rewritten) and returns
+// whether it spiked.
+__device__ __forceinline__ bool step_neuron(const NetDev& a, int64_t i, int64_t step, const NeuronIn& s) {
+  if (!s.valid) return false;
+  const bsx_lif_params_t& p = a.p;
+  const float V = s.V;
+  float de = s.de;
+  if (p.ext_threshold && drive_hash(p.ext_seed, (uint32_t)(a.first + i), (uint32_t)step) < p.ext_threshold)
+    de = __fadd_rn(de, p.ext_weight);
+  const float ge = __fadd_rn(__fmul_rn(s.ge0, p.decay_e), de);
+  const float gi = __fadd_rn(__fmul_rn(s.gi0, p.decay_i), s.di);
+  float cur;
+  if (p.coba) cur = __fadd_rn(__fmul_rn(ge, __fsub_rn(p.E_e, V)), __fmul_rn(gi, __fsub_rn(p.E_i, V)));
+  else cur = __fadd_rn(ge, gi);
+  const float drive = __fmul_rn(p.R, __fadd_rn(cur, p.I_ext));
+  const float num = __fadd_rn(__fsub_rn(p.V_rest, V), drive);
+  float Vn;
+  if (p.coba) {
+    const float f = __fmul_rn(num, p.inv_tau_m);
+    const float gsum = __fadd_rn(ge, gi);
+    const float J = __fmul_rn(-__fadd_rn(1.0f, __fmul_rn(p.R, gsum)), p.inv_tau_m);
+    const float gain = __fmul_rn(p.dt, exprel_once(__fmul_rn(p.dt, J)));
+    Vn = __fadd_rn(V, __fmul_rn(gain, f));
+  } else {
+    Vn = __fadd_rn(V, __fmul_rn(p.cuba_gain, num));
+  }
+  const bool refractory = s.r > 0;
+  if (refractory) Vn = V;
+  const bool spk = (Vn >= p.V_th) && !refractory;
+  if (s.de != 0.0f) a.delta_e[i] = 0.0f;
+  if (s.di != 0.0f) a.delta_i[i] = 0.0f;
+  a.g_e[i] = ge;
+  a.g_i[i] = gi;
+  a.V[i] = spk ? p.V_reset : Vn;
+  const int32_t rn = spk ? p.ref_steps : (s.r > 0 ? s.r - 1 : 0);
+  if (rn != s.r) a.ref[i] = rn;
+  return spk;
+}
+
+// Phase B for local words wd0 and wd1 (wd1 < 0: none); returns their spike words.
+__device__ __forceinline__ void update_two_words(const NetDev& a, int64_t wd0, int64_t wd1, int lane,
+                                                 int64_t step, uint32_t* m0, uint32_t* m1, bool* spk0,
+                                                 bool* spk1) {
+  const int64_t i0 = wd0 * 32 + lane, i1 = wd1 >= 0 ? wd1 * 32 + lane : -1;
+  const NeuronIn s0 = load_neuron(a, i0);
+  const NeuronIn s1 = load_neuron(a, i1);
+  *spk0 = step_neuron(a, i0, step, s0);
+  *spk1 = step_neuron(a, i1, step, s1);
+  *m0 = __ballot_sync(0xffffffffu, *spk0);
+  *m1 = __ballot_sync(0xffffffffu, *spk1);
 }
 
 __device__ __forceinline__ void append_spikes(uint32_t m, bool spk, int lane, int64_t gid, int32_t* __restrict__ list) {
@@ -195,14 +231,21 @@ net_run_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict__ raster
     if (warp == 0 && lane == 0) lnext[0] = 0;
     phase_scatter(a, step, warp, nwarps, lane);
     grid.sync();
-    for (int64_t wd = warp; wd < words; wd += nwarps) {
-      bool spk;
-      const uint32_t m = update_word(a, wd, lane, step, &spk);
+    for (int64_t wd = warp; wd < words; wd += 2 * nwarps) {
+      const int64_t wd1 = wd + nwarps < words ? wd + nwarps : -1;
+      bool spk0, spk1;
+      uint32_t m0, m1;
+      update_two_words(a, wd, wd1, lane, step, &m0, &m1, &spk0, &spk1);
       if (lane == 0) {
-        a.bits[wd] = m;
-        if (raster) raster[(int64_t)t * words + wd] = m;
+        a.bits[wd] = m0;
+        if (raster) raster[(int64_t)t * words + wd] = m0;
+        if (wd1 >= 0) {
+          a.bits[wd1] = m1;
+          if (raster) raster[(int64_t)t * words + wd1] = m1;
+        }
       }
-      append_spikes(m, spk, lane, wd * 32 + lane, lnext);
+      append_spikes(m0, spk0, lane, wd * 32 + lane, lnext);
+      if (wd1 >= 0) append_spikes(m1, spk1, lane, wd1 * 32 + lane, lnext);
     }
     grid.sync();
     if (spike_counts && warp == 0 && lane == 0) spike_counts[t] = lnext[0];
@@ -225,11 +268,16 @@ net_update_kernel(NetDev a, int64_t step, int32_t* __restrict__ local_count) {
   const int64_t words = (a.n_local + 31) >> 5;
   const int64_t word0 = a.first >> 5;
   int mine = 0;
-  for (int64_t wd = warp; wd < words; wd += nwarps) {
-    bool spk;
-    const uint32_t m = update_word(a, wd, lane, step, &spk);
-    if (lane == 0) a.bits[word0 + wd] = m;
-    mine += __popc(m);
+  for (int64_t wd = warp; wd < words; wd += 2 * nwarps) {
+    const int64_t wd1 = wd + nwarps < words ? wd + nwarps : -1;
+    bool spk0, spk1;
+    uint32_t m0, m1;
+    update_two_words(a, wd, wd1, lane, step, &m0, &m1, &spk0, &spk1);
+    if (lane == 0) {
+      a.bits[word0 + wd] = m0;
+      if (wd1 >= 0) a.bits[word0 + wd1] = m1;
+    }
+    mine += __popc(m0) + __popc(m1);
   }
   if (local_count && lane == 0 && mine) atomicAdd(local_count, mine);
 }
@@ -293,10 +341,15 @@ net_run_p2p_kernel(NetDev a, PeerDev pr, int steps, int64_t step0, uint32_t* __r
     phase_scatter(a, step, warp, nwarps, lane);
     grid.sync();
     // neuron update; the spike words go to every rank's exchange buffer, mine included
-    for (int64_t wd = warp; wd < words_local; wd += nwarps) {
-      bool spk;
-      const uint32_t m = update_word(a, wd, lane, step, &spk);
-      if (lane < pr.world) pr.bits[lane][par * total_words + word0 + wd] = m;
+    for (int64_t wd = warp; wd < words_local; wd += 2 * nwarps) {
+      const int64_t wd1 = wd + nwarps < words_local ? wd + nwarps : -1;
+      bool spk0, spk1;
+      uint32_t m0, m1;
+      update_two_words(a, wd, wd1, lane, step, &m0, &m1, &spk0, &spk1);
+      if (lane < pr.world) {
+        pr.bits[lane][par * total_words + word0 + wd] = m0;
+        if (wd1 >= 0) pr.bits[lane][par * total_words + word0 + wd1] = m1;
+      }
     }
     __threadfence_system();
     grid.sync();

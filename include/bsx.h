@@ -10,7 +10,8 @@
  *
  * Conventions
  *  - Every pointer is a DEVICE pointer unless its name starts with `host_`.
- *    The caller owns every buffer, workspace included; nothing here allocates.
+ *    The caller owns every buffer, workspace included; nothing here allocates
+ *    (the bsx_ipc_* set-up helpers and the host generator handle excepted).
  *  - All work is enqueued on the caller's stream (a cudaStream_t passed as
  *    void*); functions return as soon as the work is enqueued.
  *  - Return value: BSX_OK or a negative bsx_status_t.  Nothing is thrown across
@@ -19,7 +20,8 @@
  *    through a caller-provided device status word, read with bsx_read_status().
  *  - There is no CPU implementation behind these symbols.  Without a CUDA
  *    device every compute entry point returns BSX_ERR_CUDA.
- *  - Re-entrant: no mutable global state except the thread-local error string.
+ *  - Re-entrant: the only mutable global state is the thread-local error string and
+ *    the built-in queue of bsx_event_vecmat_static (documented there).
  */
 #ifndef BSX_H_
 #define BSX_H_

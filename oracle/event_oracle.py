@@ -283,12 +283,19 @@ def unpack_bits(words, n) -> np.ndarray:
 # ----------------------------------------------------------------------------
 
 def exprel_f32(z):
-    """``(exp(z)-1)/z`` evaluated in float64 and rounded once to float32
-    (``z == 0`` gives 1), the form ``exp_euler_step`` uses
-    (``brainstate/nn/_exp_euler.py:246``)."""
-    z64 = np.asarray(z, dtype=np.float64)
+    """``(exp(z)-1)/z``, the factor ``exp_euler_step`` uses
+    (``brainstate/nn/_exp_euler.py:246``).  For ``|z| <= 0.25`` a degree-6 Taylor
+    polynomial in Horner form with every multiply and add rounded to float32 (its
+    truncation error is below float32 resolution there; a GPU doing the same
+    operations matches bit for bit); otherwise float64 and one rounding."""
+    z = np.asarray(z, dtype=F32)
+    p = np.full(z.shape, F32(0.0013888889), F32)
+    for c in (F32(0.008333334), F32(0.041666668), F32(0.16666667), F32(0.5), F32(1.0)):
+        p = ((p * z).astype(F32) + c).astype(F32)
+    z64 = z.astype(np.float64)
     safe = np.where(z64 == 0, 1.0, z64)
-    return np.where(z64 == 0, 1.0, np.expm1(safe) / safe).astype(F32)
+    big = (np.expm1(safe) / safe).astype(F32)
+    return np.where(np.abs(z) <= F32(0.25), p, big).astype(F32)
 
 
 class EINetOracle:
