@@ -20,6 +20,11 @@ int vecmat_common(const bsx_conn_t* conn, const void* in, int format, const floa
                   float* out, int accumulate, void* ws, size_t ws_bytes, int chunk, int blocks_per_sm,
                   cudaStream_t st);
 
+// Batched scatter with the output slice in shared memory (scatter_smem.cu).
+bool scatter_smem_applies(const bsx_conn_t* conn, int format, int64_t batch);
+int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, const float* x, int64_t batch,
+                        float* out, int accumulate, cudaStream_t st);
+
 // Batched event matvec, 16 spike vectors per pass over the indices (gather_batched.cu).
 size_t b16_mask_bytes(int64_t batch, int64_t n_post);
 bool b16_fits(int64_t n_post);

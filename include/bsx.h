@@ -168,7 +168,9 @@ int bsx_event_vecmat(const bsx_conn_t* conn, const void* spikes, int spike_forma
                      float* out, int accumulate, void* workspace, size_t workspace_bytes,
                      bsx_stream_t stream);
 /* Same, with explicit launch geometry for tuning (0 = default): entries per
- * work item of a fixed-number row, and resident blocks per SM. */
+ * work item of a fixed-number row, and resident blocks per SM.  blocks_per_sm = -1
+ * selects the variant that accumulates output slices in shared memory (batch >= 16,
+ * n_post <= 131072; faster only at firing rates of several percent). */
 int bsx_event_vecmat_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                            float* out, int accumulate, void* workspace, size_t workspace_bytes,
                            int chunk, int blocks_per_sm, bsx_stream_t stream);

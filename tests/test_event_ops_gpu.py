@@ -277,6 +277,43 @@ def test_batched_training_step_at_microbenchmark_size(microbench, c_oracle, cuda
     assert torch.equal(dx, dx2) and torch.equal(dw, dw2)         # no atomics: reproducible
 
 
+@pytest.mark.parametrize('n_post', [1000, 32768, 40001, 70003, 131072])
+@pytest.mark.parametrize('hetero', [False, True])
+def test_batched_scatter_with_output_in_shared_memory(n_post, hetero, bsx, cuda):
+    """The opt-in scatter that keeps output slices in shared memory (batches of 16 or
+    more over at most 131 072 columns; blocks_per_sm = -1 in the tuned entry point) must
+    agree with the oracle for every spike format, for CSR rows and when accumulating."""
+    from brainstate_b200 import _lib, EventArray
+    from brainstate_b200.event import pack_spikes
+    n_pre, K, B = 777, 29, 19
+    rs = np.random.RandomState(n_post % 97)
+    for layout in (None, 0.7):
+        conn, idx, indptr, w = make(n_pre, n_post, K, 41, hetero, cuda, layout)
+        spk = rs.random_sample((B, n_pre)) < 0.15
+        ref = eo.event_vecmat(spk, idx, w, n_post, indptr)
+        ts = torch.from_numpy(spk).to(cuda)
+        st = conn._struct()
+        ws_bytes = bsx.bsx_event_vecmat_workspace_bytes(B, n_pre)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=cuda)
+        stream = _lib.current_stream()
+
+        def smem_scatter(t, fmt, out, accumulate=0):
+            _lib.check(bsx.bsx_event_vecmat_tuned(C.byref(st), t.data_ptr(), fmt, B, out.data_ptr(), accumulate,
+                                                  ws.data_ptr(), ws_bytes, 0, -1, stream))
+            return out
+
+        y = smem_scatter(ts, _lib.SPK_BOOL8, torch.full((B, n_post), 9.0, device=cuda))
+        if hetero:
+            close(y, ref)
+        else:
+            assert np.array_equal(y.cpu().numpy(), ref)
+        xf = torch.from_numpy((spk * rs.uniform(0.5, 2, spk.shape)).astype(np.float32)).to(cuda)
+        close(smem_scatter(xf, _lib.SPK_F32, torch.empty_like(y)), ref)            # float spikes are events
+        bits = pack_spikes(ts)
+        close(smem_scatter(bits, _lib.SPK_BITS32, y.clone(), accumulate=1), 2 * ref)
+        close(EventArray(ts) @ conn, ref)                                          # the default kernel, same input
+
+
 def test_host_buffer_pipeline_equals_device_path(cuda):
     """Pinned host spikes in, pinned host results out, chunks overlapped on three streams."""
     from brainstate_b200 import EventArray
