@@ -395,8 +395,12 @@ class EINet:
     def _run_p2p(self, steps: int, record: bool, blocks: int = 0):
         """All steps of all ranks in one cooperative launch per GPU; the spike words
         travel by peer stores inside the kernel."""
+        import torch.distributed as dist
         if self._p2p is None:
             self._setup_p2p()
+        # the kernels of all ranks wait for one another with a bounded patience (about a
+        # second): line the hosts up first so that none of them launches much later
+        dist.barrier(group=self.group)
         dev = self.dev
         raster = torch.empty((steps, self.words), dtype=torch.int32, device=dev) if record else None
         counts = torch.empty(steps, dtype=torch.int32, device=dev)
