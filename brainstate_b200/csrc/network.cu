@@ -154,44 +154,56 @@ __device__ __forceinline__ NeuronIn load_neuron(const NetDev& a, int64_t i) {
   return s;
 }
 
-// Synapse decay + increment, membrane update, threshold, reset, refractory count for
-// neuron i; stores the new state (unchanged values are not rewritten) and returns
-// whether it spiked.
-__device__ __forceinline__ bool step_neuron(const NetDev& a, int64_t i, int64_t step, const NeuronIn& s) {
-  if (!s.valid) return false;
-  const bsx_lif_params_t& p = a.p;
-  const float V = s.V;
-  float de = s.de;
-  if (p.ext_threshold && drive_hash(p.ext_seed, (uint32_t)(a.first + i), (uint32_t)step) < p.ext_threshold)
+// The arithmetic of one neuron for one step: synapse decay + increment (+ background
+// drive), membrane update, threshold, reset, refractory count.  Pure: state in, state out.
+struct NeuronOut {
+  float ge, gi, V;
+  int32_t r;
+  bool spk;
+};
+
+__device__ __forceinline__ NeuronOut neuron_math(const bsx_lif_params_t& p, float de, float di, float ge0,
+                                                 float gi0, float V, int32_t r, uint32_t gid, int64_t step) {
+  if (p.ext_threshold && drive_hash(p.ext_seed, gid, (uint32_t)step) < p.ext_threshold)
     de = __fadd_rn(de, p.ext_weight);
-  const float ge = __fadd_rn(__fmul_rn(s.ge0, p.decay_e), de);
-  const float gi = __fadd_rn(__fmul_rn(s.gi0, p.decay_i), s.di);
+  NeuronOut o;
+  o.ge = __fadd_rn(__fmul_rn(ge0, p.decay_e), de);
+  o.gi = __fadd_rn(__fmul_rn(gi0, p.decay_i), di);
   float cur;
-  if (p.coba) cur = __fadd_rn(__fmul_rn(ge, __fsub_rn(p.E_e, V)), __fmul_rn(gi, __fsub_rn(p.E_i, V)));
-  else cur = __fadd_rn(ge, gi);
+  if (p.coba) cur = __fadd_rn(__fmul_rn(o.ge, __fsub_rn(p.E_e, V)), __fmul_rn(o.gi, __fsub_rn(p.E_i, V)));
+  else cur = __fadd_rn(o.ge, o.gi);
   const float drive = __fmul_rn(p.R, __fadd_rn(cur, p.I_ext));
   const float num = __fadd_rn(__fsub_rn(p.V_rest, V), drive);
   float Vn;
   if (p.coba) {
     const float f = __fmul_rn(num, p.inv_tau_m);
-    const float gsum = __fadd_rn(ge, gi);
+    const float gsum = __fadd_rn(o.ge, o.gi);
     const float J = __fmul_rn(-__fadd_rn(1.0f, __fmul_rn(p.R, gsum)), p.inv_tau_m);
     const float gain = __fmul_rn(p.dt, exprel_once(__fmul_rn(p.dt, J)));
     Vn = __fadd_rn(V, __fmul_rn(gain, f));
   } else {
     Vn = __fadd_rn(V, __fmul_rn(p.cuba_gain, num));
   }
-  const bool refractory = s.r > 0;
+  const bool refractory = r > 0;
   if (refractory) Vn = V;
-  const bool spk = (Vn >= p.V_th) && !refractory;
+  o.spk = (Vn >= p.V_th) && !refractory;
+  o.V = o.spk ? p.V_reset : Vn;
+  o.r = o.spk ? p.ref_steps : (r > 0 ? r - 1 : 0);
+  return o;
+}
+
+// Applies neuron_math to neuron i of the global-memory state; unchanged values are
+// not rewritten.  Returns whether it spiked.
+__device__ __forceinline__ bool step_neuron(const NetDev& a, int64_t i, int64_t step, const NeuronIn& s) {
+  if (!s.valid) return false;
+  const NeuronOut o = neuron_math(a.p, s.de, s.di, s.ge0, s.gi0, s.V, s.r, (uint32_t)(a.first + i), step);
   if (s.de != 0.0f) a.delta_e[i] = 0.0f;
   if (s.di != 0.0f) a.delta_i[i] = 0.0f;
-  a.g_e[i] = ge;
-  a.g_i[i] = gi;
-  a.V[i] = spk ? p.V_reset : Vn;
-  const int32_t rn = spk ? p.ref_steps : (s.r > 0 ? s.r - 1 : 0);
-  if (rn != s.r) a.ref[i] = rn;
-  return spk;
+  a.g_e[i] = o.ge;
+  a.g_i[i] = o.gi;
+  a.V[i] = o.V;
+  if (o.r != s.r) a.ref[i] = o.r;
+  return o.spk;
 }
 
 // Phase B for local words wd0 and wd1 (wd1 < 0: none); returns their spike words.
@@ -214,6 +226,135 @@ __device__ __forceinline__ void append_spikes(uint32_t m, bool spk, int lane, in
   if (lane == 0) base = atomicAdd(list, total);
   base = __shfl_sync(0xffffffffu, base, 0);
   if (spk) list[1 + base + __popc(m & ((1u << lane) - 1u))] = (int32_t)gid;
+}
+
+// ---- small networks: one thread block, state in shared memory ------------------------
+// A few thousand neurons fit one SM: V, g_e, g_i, delta_e, delta_i and the refractory
+// count live in shared memory for the whole run, the two phases of a step are
+// separated by __syncthreads instead of grid-wide barriers, and the scatter uses
+// shared-memory adds.  Same arithmetic, same spike lists and words in global memory.
+// One SM updates about 2 000 neurons per microsecond, a grid-wide barrier costs about
+// two: measured 3.5 us per step at 4 000 neurons against 4.1 for the cooperative
+// kernel, 5.5 against 4.4 at 8 000 — hence the limit.
+constexpr int kSmallMax = 4096;
+constexpr int kSmallThreads = 1024;
+
+__device__ __forceinline__ void smem_red(float* p, float v) {
+  asm volatile("red.shared.add.f32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "f"(v) : "memory");
+}
+
+__device__ __forceinline__ void small_scatter_row(const ProjDev& pr, int64_t row, int lane, float* __restrict__ acc) {
+  int64_t s, e;
+  pr.rm.range(row, s, e);
+  const float w0 = pr.hetero ? 1.0f : __ldg(pr.w);
+  for (int64_t p = s + lane; p < e; p += 32)
+    smem_red(acc + __ldg(pr.idx + p), pr.hetero ? __ldg(pr.w + p) : w0);
+}
+
+__device__ __forceinline__ void small_scatter_id(const NetDev& a, int64_t id, bool do_exc, bool do_inh, int lane,
+                                                 float* __restrict__ sde, float* __restrict__ sdi) {
+  if (id < a.n_exc) {
+    if (do_exc) small_scatter_row(a.exc, id, lane, sde);
+  } else if (do_inh) {
+    small_scatter_row(a.inh, id - a.n_exc, lane, sdi);
+  }
+}
+
+__global__ void __launch_bounds__(kSmallThreads, 1)
+net_run_small_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict__ raster,
+                     int32_t* __restrict__ spike_counts) {
+  extern __shared__ __align__(16) float sm_state[];
+  const int n = (int)a.n_local;
+  float* sV = sm_state;
+  float* sge = sV + n;
+  float* sgi = sge + n;
+  float* sde = sgi + n;
+  float* sdi = sde + n;
+  int16_t* sref = reinterpret_cast<int16_t*>(sdi + n);
+  // the spike lists of the last two steps also stay on chip (ids fit 16 bits here), so
+  // that an undelayed projection never waits for global memory to learn who spiked
+  uint16_t* slist0 = reinterpret_cast<uint16_t*>(sref + n);
+  uint16_t* slist1 = slist0 + n;
+  __shared__ int32_t s_count[2];
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int nwarps = kSmallThreads / 32;
+  const int words = (n + 31) >> 5;
+  for (int i = tid; i < n; i += kSmallThreads) {
+    sV[i] = a.V[i]; sge[i] = a.g_e[i]; sgi[i] = a.g_i[i];
+    sde[i] = a.delta_e[i]; sdi[i] = a.delta_i[i]; sref[i] = (int16_t)a.ref[i];
+  }
+  if (step0 > 0) {   // the list of the step before the first one, from global memory
+    const int32_t* lp = a.slot(step0 - 1);
+    const int cnt = lp[0];
+    uint16_t* dst = ((step0 - 1) & 1) ? slist1 : slist0;
+    for (int q = tid; q < cnt; q += kSmallThreads) dst[q] = (uint16_t)lp[1 + q];
+    if (tid == 0) s_count[(step0 - 1) & 1] = cnt;
+  } else if (tid == 0) {
+    s_count[0] = s_count[1] = 0;
+  }
+  __syncthreads();
+  for (int t = 0; t < steps; ++t) {
+    const int64_t step = step0 + t;
+    int32_t* lnext = a.slot(step);
+    uint16_t* snext = (step & 1) ? slist1 : slist0;
+    const uint16_t* sprev = (step & 1) ? slist0 : slist1;
+    const int prev_cnt = s_count[(step & 1) ^ 1];
+    __syncthreads();
+    if (tid == 0) s_count[step & 1] = 0;
+    // phase A: delayed spike lists -> shared-memory increments
+    const int64_t te = step - 1 - a.delay_e, ti = step - 1 - a.delay_i;
+    for (int pass = 0; pass < 2; ++pass) {
+      const int64_t ts = pass == 0 ? te : ti;
+      if (ts < 0 || (pass == 1 && ti == te)) continue;
+      const bool do_exc = pass == 0, do_inh = pass == 1 || ti == te;
+      if (ts == step - 1) {                       // previous step: on-chip list
+        for (int q = wid; q < prev_cnt; q += nwarps) small_scatter_id(a, sprev[q], do_exc, do_inh, lane, sde, sdi);
+      } else {                                    // older step: its list in global memory
+        const int32_t* lp = a.slot(ts);
+        const int cnt = lp[0];
+        for (int q = wid; q < cnt; q += nwarps) small_scatter_id(a, lp[1 + q], do_exc, do_inh, lane, sde, sdi);
+      }
+    }
+    __syncthreads();
+    // phase B
+    for (int wd = wid; wd < words; wd += nwarps) {
+      const int i = wd * 32 + lane;
+      bool spk = false;
+      if (i < n) {
+        const NeuronOut o = neuron_math(a.p, sde[i], sdi[i], sge[i], sgi[i], sV[i], sref[i], (uint32_t)i, step);
+        sde[i] = 0.0f; sdi[i] = 0.0f;
+        sge[i] = o.ge; sgi[i] = o.gi; sV[i] = o.V; sref[i] = (int16_t)o.r;
+        spk = o.spk;
+      }
+      const uint32_t m = __ballot_sync(0xffffffffu, spk);
+      if (lane == 0) {
+        a.bits[wd] = m;
+        if (raster) raster[(int64_t)t * words + wd] = m;
+      }
+      const int total = __popc(m);
+      if (total) {
+        int base = 0;
+        if (lane == 0) base = atomicAdd(&s_count[step & 1], total);
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (spk) {
+          const int pos = base + __popc(m & ((1u << lane) - 1u));
+          snext[pos] = (uint16_t)i;
+          lnext[1 + pos] = i;               // the copy that outlives the launch (and serves delays)
+        }
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const int c = s_count[step & 1];
+      lnext[0] = c;
+      if (spike_counts) spike_counts[t] = c;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < n; i += kSmallThreads) {
+    a.V[i] = sV[i]; a.g_e[i] = sge[i]; a.g_i[i] = sgi[i];
+    a.delta_e[i] = sde[i]; a.delta_i[i] = sdi[i]; a.ref[i] = sref[i];
+  }
 }
 
 // ---- one cooperative launch for many steps (single GPU) ------------------------
@@ -518,6 +659,14 @@ int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t st
   if (steps == 0) return BSX_OK;
   int sms = sm_count();
   if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  // the whole network fits one SM's shared memory (refractory counts are kept as int16 there)
+  if (blocks == 0 && net->n_global <= kSmallMax && params->ref_steps < 32768) {
+    const size_t smem = (size_t)net->n_global * (5 * sizeof(float) + 3 * sizeof(int16_t));
+    BSX_CUDA(cudaFuncSetAttribute(net_run_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    net_run_small_kernel<<<1, kSmallThreads, smem, as_stream(stream)>>>(a, steps, step0, raster, spike_counts);
+    BSX_LAUNCH_CHECK("net_run_small_kernel");
+    return BSX_OK;
+  }
   int per_sm = 0;
   BSX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, net_run_kernel, 256, 0));
   if (per_sm < 1) return fail(BSX_ERR_CUDA, "the network kernel does not fit on an SM");
