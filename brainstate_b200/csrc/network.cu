@@ -59,9 +59,11 @@ __device__ __forceinline__ void scatter_one(const ProjDev& pr, int64_t row, int 
                                             float* __restrict__ out) {
   int64_t s, e;
   pr.rm.range(row, s, e);
-  s += (int64_t)c * chunk;
-  if (s >= e) return;
-  if (s + chunk < e) e = s + chunk;
+  if (pr.cpr > 1) {   // fixed-number rows are cut into chunks; a CSR row is one item whatever its length
+    s += (int64_t)c * chunk;
+    if (s >= e) return;
+    if (s + chunk < e) e = s + chunk;
+  }
   if (pr.hetero) scatter_span<true>(pr.idx, pr.w, s, e, lane, 1.0f, out, pr.vec_ok);
   else scatter_span<false>(pr.idx, pr.w, s, e, lane, __ldg(pr.w), out, pr.vec_ok);
 }

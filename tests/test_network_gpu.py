@@ -254,3 +254,26 @@ def test_chunked_builder_equals_one_shot(cuda):
     assert np.array_equal(np.diff(b.indptr.cpu().numpy()), keep.sum(axis=1))
     rows, ks = np.nonzero(keep)
     np.testing.assert_allclose(b.data.cpu().numpy(), eo.lognormal_weights(9, rows, ks, -1.0, 0.3, -2.0), rtol=1e-6)
+
+
+def test_long_csr_rows_in_the_network_step(cuda):
+    """A shard's projections are CSR blocks whose rows can be far longer than the
+    chunk the fixed-number layout is cut into: the same network with its projections
+    re-expressed as CSR (300 entries per row) must give the same raster."""
+    from brainstate_b200 import CSR
+    a, orc = build(400, 112, 300, False, cuda, 0.3, -1.7)
+    b, _ = build(400, 112, 300, False, cuda, 0.3, -1.7)
+    for name in ('conn_e', 'conn_i'):
+        c = getattr(b, name)
+        n_pre, K = c.indices.shape
+        indptr = torch.arange(0, n_pre + 1, dtype=torch.int64, device=cuda) * K
+        setattr(b, name, CSR((c.data, c.indices.reshape(-1).contiguous(), indptr), shape=c.shape))
+    b._net = b._make_struct()
+    steps = 150
+    ra, _ = a.run(steps, blocks=4)          # cooperative kernel, fixed-number layout
+    rb, _ = b.run(steps, blocks=4)          # cooperative kernel, CSR layout
+    rc, _ = build(400, 112, 300, False, cuda, 0.3, -1.7)[0].run(steps)      # single-block kernel
+    assert int(ra.ne(0).sum()) > 0
+    assert torch.equal(ra, rb) and torch.equal(ra, rc)
+    from brainstate_b200.sim import unpack_raster
+    assert np.array_equal(unpack_raster(ra, 512), orc.run(steps))
