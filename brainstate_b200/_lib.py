@@ -86,6 +86,7 @@ SIGNATURES = {
     'bsx_host_gen_new': (_vp, [C.c_uint32]),
     'bsx_host_gen_free': (None, [_vp]),
     'bsx_host_gen_rows': (_i64, [_vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
+    'bsx_host_distinct_indices': (_i64, [C.c_uint32, _i64, _i64, _i64, _vp]),
     'bsx_lognormal_weights': (_i32, [_connp, _vp, _i64, C.c_uint32, C.c_double, C.c_double, _f32, _vp, _vp]),
     'bsx_lognormal_weight_at': (_f32, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_double, C.c_double, _f32]),
     'bsx_validate_conn': (_i32, [_connp, _vp, _vp]),

@@ -219,4 +219,43 @@ int64_t bsx_host_gen_rows(void* gen, int64_t rows, int64_t n_post, int64_t conn_
   return written;
 }
 
+// Rows of conn_num DISTINCT targets each (sampling without replacement), from the same
+// generator: bounded draws in stream order, a draw that repeats a target of the current
+// row is dropped.  Every ordered conn_num-subset is equally likely.  This is the
+// library's sampler for `allow_multi_conn=False`
+// (brainstate/nn/_event_fixedprob.py:39-62); it does not reproduce the reference's
+// numbers, which come from JAX's threefry generator.
+int64_t bsx_host_distinct_indices(uint32_t seed, int64_t n_pre, int64_t n_post, int64_t conn_num,
+                                  int32_t* host_out) {
+  if (n_pre < 0 || n_post < 1 || conn_num < 0 || n_post > (int64_t)INT32_MAX)
+    return fail(BSX_ERR_INVALID_ARG, "bsx_host_distinct_indices: bad sizes");
+  if (conn_num > n_post) return fail(BSX_ERR_INVALID_ARG, "cannot draw %lld distinct targets out of %lld",
+                                     (long long)conn_num, (long long)n_post);
+  if (!host_out && n_pre * conn_num > 0) return fail(BSX_ERR_INVALID_ARG, "bsx_host_distinct_indices: output is NULL");
+  const uint32_t top = (uint32_t)(n_post - 1);
+  uint32_t mask = top;
+  mask |= mask >> 1; mask |= mask >> 2; mask |= mask >> 4; mask |= mask >> 8; mask |= mask >> 16;
+  const size_t words = (size_t)((n_post + 63) / 64);
+  uint64_t* seen = new (std::nothrow) uint64_t[words]();
+  if (!seen) return fail(BSX_ERR_INVALID_ARG, "bsx_host_distinct_indices: out of host memory");
+  Mt19937 mt(seed);
+  for (int64_t r = 0; r < n_pre; ++r) {
+    int32_t* row = host_out + r * conn_num;
+    for (int64_t k = 0; k < conn_num;) {
+      uint32_t v = 0;
+      if (top) {
+        do { v = mt.next() & mask; } while (v > top);
+      }
+      uint64_t& w = seen[v >> 6];
+      const uint64_t bit = 1ull << (v & 63);
+      if (w & bit) continue;
+      w |= bit;
+      row[k++] = (int32_t)v;
+    }
+    for (int64_t k = 0; k < conn_num; ++k) seen[(uint32_t)row[k] >> 6] = 0;   // clear only what was set
+  }
+  delete[] seen;
+  return n_pre * conn_num;
+}
+
 }  // extern "C"

@@ -60,21 +60,20 @@ def init_indices_without_replace(conn_num: int, n_pre: int, n_post: int, seed: O
     The reference draws these from JAX's threefry generator, which is not
     available here, so this sampler is NOT bit-compatible with the reference: it
     honours the same contract (shape ``(n_pre, conn_num)``, values in
-    ``[0, n_post)``, distinct within a row, reproducible from ``seed``) using
-    NumPy's ``RandomState(seed)``.  ``method`` is validated as in the reference;
-    both methods give the same result.
+    ``[0, n_post)``, distinct within a row, reproducible from ``seed``) with the
+    library's host generator (MT19937 draws, repeats within a row dropped).
+    ``method`` is validated as in the reference; both methods give the same result.
     """
     if method not in ('vmap', 'for_loop'):
         raise ValueError(f"Unknown method: {method}")
     if conn_num > n_post:
         raise ValueError('cannot draw more distinct targets than there are postsynaptic neurons')
-    rng = np.random.RandomState(seed)
+    if seed is None:
+        seed = int(np.random.randint(0, 2 ** 31 - 1))
     out = np.empty((n_pre, conn_num), np.int32)
-    rows_per_chunk = max(1, (1 << 24) // max(n_post, 1))
-    for r0 in range(0, n_pre, rows_per_chunk):
-        r1 = min(n_pre, r0 + rows_per_chunk)
-        keys = rng.random_sample((r1 - r0, n_post))
-        out[r0:r1] = np.argsort(keys, axis=1, kind='stable')[:, :conn_num]
+    n = _lib.lib().bsx_host_distinct_indices(C.c_uint32(int(seed) & 0xffffffff), n_pre, n_post, conn_num,
+                                             out.ctypes.data)
+    _lib.check(int(n))
     return out
 
 

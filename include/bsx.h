@@ -112,6 +112,13 @@ void bsx_host_gen_free(void* gen);
 int64_t bsx_host_gen_rows(void* gen, int64_t rows, int64_t n_post, int64_t conn_num, int64_t col_begin,
                           int64_t col_end, int32_t* host_out, int16_t* host_k_out, int32_t* host_row_counts);
 
+/* Rows of conn_num distinct targets (sampling without replacement) from the same
+ * generator; the library's sampler for allow_multi_conn=False
+ * (brainstate/nn/_event_fixedprob.py:39-62).  Honours that function's contract but not
+ * its numbers, which the reference draws from JAX's threefry generator. */
+int64_t bsx_host_distinct_indices(uint32_t seed, int64_t n_pre, int64_t n_post, int64_t conn_num,
+                                  int32_t* host_out);
+
 /*
  * Heterogeneous weights keyed by position: w(row, k) = sign * exp(mu + sigma * z), z a
  * standard normal derived from a hash of (seed, row0 + row, k).  kpos (may be NULL: k is
