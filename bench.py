@@ -6,9 +6,13 @@ matrix with fixed-probability connectivity p = 0.01 (655 int32 targets per row,
 seed 200), heterogeneous float32 weights ~ N(0.1, 0.01) (seed 201), and T
 distinct Bernoulli(1 %) spike vectors (seed 211).  One step = one pass of the hot
 path over that batch: the forward product ``spike @ W`` of all T vectors (one
-batched scatter launch) and the event matvec ``W @ spike`` of each vector (T
-gather launches).  ``value`` = synaptic events per second = (events of both
-products over the batch) / time, with everything resident in HBM.  ``e2e`` is the
+batched scatter launch) and the event matvec ``W @ spike`` of all T vectors in
+the variant the firing rate selects — at 1 % the event-driven one, in which the
+active columns scatter along the transposed copy of the matrix (one launch);
+above 3 % it would be the deterministic gather (one pass per 16 vectors), which
+is timed beside the step for its own roofline.  ``value`` = synaptic events per
+second = (events of both products over the batch) / time, with everything
+resident in HBM.  ``e2e`` is the
 same pass through the public layer API starting from pinned host spikes and
 ending with the results back in host memory.  Data are synthetic, generated from
 the seeds above; the matrix (343 MB) is larger than the 126 MB L2.
@@ -221,8 +225,12 @@ class DevicePass:
         self.mv_ws_bytes = self.lib.bsx_event_matvec_workspace_bytes(vectors, n)
         self.mv_ws = torch.empty(self.mv_ws_bytes, dtype=torch.uint8, device=dev)
         self.passes = (vectors + 15) // 16
-        # compact + scatter; transpose-pack + one gather pass per 16 vectors
-        self.launches_per_pass = 2 + 1 + self.passes
+        # W@spike: below ~3 % firing the event-driven form (the active columns scatter along the
+        # transposed copy) beats the gather over all rows; above it the gather wins
+        self.matvec_method = 'scatter' if RATE <= 0.03 else 'gather'
+        self.st_t = self.conn._transposed_struct(self.tw) if self.matvec_method == 'scatter' else None
+        # per product: compact + scatter; for the gather: transpose-pack + one pass per 16 vectors
+        self.launches_per_pass = 2 + (2 if self.matvec_method == 'scatter' else 1 + self.passes)
 
     def vecmat(self, spk_dev, stream):
         self._lib.check(self.lib.bsx_event_vecmat(C.byref(self.st), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
@@ -230,6 +238,14 @@ class DevicePass:
                                                   self.ws_bytes, stream))
 
     def matvec(self, spk_dev, stream):
+        if self.matvec_method == 'scatter':
+            self._lib.check(self.lib.bsx_event_vecmat(C.byref(self.st_t), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
+                                                      self.T, self.y_matvec.data_ptr(), 0, self.ws.data_ptr(),
+                                                      self.ws_bytes, stream))
+        else:
+            self.matvec_gather(spk_dev, stream)
+
+    def matvec_gather(self, spk_dev, stream):
         self._lib.check(self.lib.bsx_event_matvec(C.byref(self.st), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
                                                   self.T, self.y_matvec.data_ptr(), self.mv_ws.data_ptr(),
                                                   self.mv_ws_bytes, stream))
@@ -291,9 +307,24 @@ def run_ours(args):
         mv[s][1].record()
     e_end.record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
     ms_total = e_start.elapsed_time(e_end)
     ms_matvec = sum(a.elapsed_time(b) for a, b in mv)
+    # the deterministic gather, timed on its own for the roofline of W@spike as an HBM stream
+    # (it is the step's W@spike only when the firing rate selects it)
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g_steps = 0 if args.profile else max(3, min(args.steps, 10))
+    g0.record()
+    for _ in range(g_steps):
+        dp.matvec_gather(spk_dev, stream)
+    g1.record()
+    torch.cuda.synchronize()
+    ms_gather = g0.elapsed_time(g1) / max(g_steps, 1)
+    clocks = sampler.stop() if rank == 0 else None
+    if dp.matvec_method == 'scatter' and rank == 0 and not args.profile:   # the two forms of W@spike agree
+        y_gather = dp.y_matvec.clone()
+        dp.matvec(spk_dev, stream)
+        torch.cuda.synchronize()
+        assert torch.allclose(dp.y_matvec, y_gather, rtol=1e-5, atol=1e-6)
     t_dev = torch.tensor([ms_total], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t_dev, op=dist.ReduceOp.MAX)
@@ -319,7 +350,8 @@ def run_ours(args):
     host_y2 = torch.empty((T, n), dtype=torch.float32).pin_memory()
 
     from brainstate_b200.host import HostEventProducts
-    pipe = HostEventProducts(layer.conn, chunk=16)     # public host-buffer API: upload, products, download overlap
+    # public host-buffer API: upload, products, download overlap
+    pipe = HostEventProducts(layer.conn, chunk=16, reverse_method=dp.matvec_method)
 
     def e2e_pass():
         pipe(host_spk, host_y1, host_y2)               # spike @ W and W @ spike, host memory in and out
@@ -331,7 +363,7 @@ def run_ours(args):
         dp.run(spk_dev, stream)
         torch.cuda.synchronize()
         assert torch.allclose(host_y1.to(dev), dp.y_vecmat, rtol=1e-5, atol=1e-6)
-        assert torch.equal(host_y2.to(dev), dp.y_matvec)
+        assert torch.allclose(host_y2.to(dev), dp.y_matvec, rtol=1e-5, atol=1e-6)
     barrier()
     e2e_steps = max(3, min(args.steps, 8))
     t0 = time.perf_counter()
@@ -359,11 +391,14 @@ def run_ours(args):
     events_vec = float(spk.sum()) * K                      # events of one product over the batch
     # gather: one launch = one pass over the indices for 16 vectors
     g_bytes = nnz * 4 + (events_vec / dp.passes) * 4 + n * 2 + min(T, 16) * 4 * n
-    g_launch_s = (ms_matvec * 1e-3) / (args.steps * dp.passes)   # includes the transpose-pack launch (~2 %)
-    # scatter: one launch = all T vectors
-    ms_vecmat = ms_total - ms_matvec
+    g_launch_s = (ms_gather * 1e-3) / dp.passes                  # includes the transpose-pack launch (~2 %)
+    # scatter: one launch = all T vectors of one product
     s_bytes = events_vec * 8 + T * (n + 4 * n)
-    s_launch_s = (ms_vecmat * 1e-3) / args.steps
+    if dp.matvec_method == 'scatter':
+        s_launches, ms_scatter = 2 * args.steps, ms_total
+    else:
+        s_launches, ms_scatter = args.steps, ms_total - ms_matvec
+    s_launch_s = (ms_scatter * 1e-3) / s_launches
 
     def roof(kernel, nbytes, sec, share, note):
         a = nbytes / sec / 1e9
@@ -371,12 +406,23 @@ def run_ours(args):
                 'unit': 'GB/s', 'frac': a / peak, 'bytes_per_launch': nbytes, 'avg_launch_us': sec * 1e6,
                 'share_of_step': share, 'traffic': None, 'note': note}
 
-    r_g = roof('event_matvec_b16_kernel<hetero>', g_bytes, g_launch_s, ms_matvec / ms_total,
-               'W@spike, 16 vectors per pass over the indices; limited by shared-memory bit tests and '
-               'instruction issue, see DESIGN.md')
-    r_s = roof('scatter_queue_kernel<hetero> (+compact)', s_bytes, s_launch_s, ms_vecmat / ms_total,
-               'spike@W; limited by the L2 rate of red.global.add.f32, not by HBM')
-    roofline, roofline_2 = (r_g, r_s) if ms_matvec >= ms_vecmat else (r_s, r_g)
+    r_s = roof('scatter_queue_kernel<hetero> (+compact)', s_bytes, s_launch_s, ms_scatter / ms_total,
+               'spike@W over the rows' + (' and W@spike over the transposed copy' if dp.matvec_method == 'scatter' else '')
+               + '; limited by the L2 rate of red.global.add.f32 (about 190 G adds/s in a stand-alone probe), '
+               'not by HBM')
+    r_s['atomic_adds_per_s'] = events_vec / s_launch_s
+    if dp.matvec_method == 'scatter':
+        r_g = roof('event_matvec_b16_kernel<hetero>', g_bytes, g_launch_s, 0.0,
+                   'the deterministic W@spike (16 vectors per pass over the indices), timed in its own loop after '
+                   'the steps: at this firing rate the step uses the event-driven form, which is '
+                   f'{ms_gather / (ms_matvec / args.steps):.2f}x faster; limited by shared-memory bit tests and '
+                   'instruction issue')
+        roofline, roofline_2 = r_s, r_g
+    else:
+        r_g = roof('event_matvec_b16_kernel<hetero>', g_bytes, g_launch_s, ms_matvec / ms_total,
+                   'W@spike, 16 vectors per pass over the indices; limited by shared-memory bit tests and '
+                   'instruction issue')
+        roofline, roofline_2 = (r_g, r_s) if ms_matvec >= ms_scatter else (r_s, r_g)
     prof = os.path.join(ROOT, 'profiles', 'traffic.json')
     if os.path.exists(prof):
         try:
@@ -402,6 +448,8 @@ def run_ours(args):
         'roofline_other_kernel': roofline_2,
         'cpu_baseline': cpu,
         'events_per_step': events_all,
+        'variants': {'spike@W': 'scatter', 'W@spike': dp.matvec_method + (' over the transposed copy' if dp.matvec_method == 'scatter' else ''),
+                     'chosen_for_rate': RATE},
         'network': network,
     }
     if args.cases:
@@ -476,11 +524,19 @@ def run_cases(torch, dev, dp, idx, w, peak):
                 _lib.check(lib.bsx_event_matvec(C.byref(st), sd.data_ptr(), _lib.SPK_BOOL8, T, dp.y_matvec.data_ptr(),
                                                 dp.mv_ws.data_ptr(), dp.mv_ws_bytes, stream))
 
+            st_t = conn._transposed_struct(conn.data)
+
+            def matvec_scatter():
+                _lib.check(lib.bsx_event_vecmat(C.byref(st_t), sd.data_ptr(), _lib.SPK_BOOL8, T, dp.y_matvec.data_ptr(),
+                                                0, dp.ws.data_ptr(), dp.ws_bytes, stream))
+
             for prod, fn, alg in (('spike@W scatter', vecmat, events * (4 + 4 * h) + T * (n + 4 * n)),
                                   ('W@spike gather, one vector per pass', matvec,
                                    T * (n * K * 4 + n / 8 + 4 * n) + events * 4 * h),
                                   ('W@spike gather, 16 vectors per pass', matvec_b16,
-                                   dp.passes * (n * K * 4 + 2 * n) + T * 4 * n + events * 4 * h)):
+                                   dp.passes * (n * K * 4 + 2 * n) + T * 4 * n + events * 4 * h),
+                                  ('W@spike scatter over the transposed copy', matvec_scatter,
+                                   events * (4 + 4 * h) + T * (n + 4 * n))):
                 for _ in range(3):
                     fn()
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -89,6 +89,7 @@ class _SparseConn:
                 raise ValueError('indptr must have n_pre + 1 entries')
             self.indptr = indptr.contiguous()
         self._transposed: Optional[_Transposed] = None
+        self.matvec_method = 'gather'    # what ``conn @ EventArray`` uses; see ``event_matvec``
         self._set_data(data)
 
     # -- data ---------------------------------------------------------------
@@ -107,6 +108,7 @@ class _SparseConn:
             raise ValueError(f'weights of shape {tuple(data.shape)} match neither a scalar nor the '
                              f'indices {tuple(self.indices.shape)}')
         self.data = data
+        self._t_weights = None          # permuted copy for the transposed layout, made on demand
 
     def with_data(self, data):
         """A view of the same connectivity with other weights
@@ -173,12 +175,20 @@ class _SparseConn:
         return self._transposed
 
     def _transposed_struct(self, weights: torch.Tensor):
-        """``bsx_conn_t`` of the transposed copy with the given (original-order) weights."""
+        """``bsx_conn_t`` of the transposed copy with the given (original-order) weights.
+        The permuted weights are kept until the weight tensor changes (new storage or an
+        in-place update), so repeated products pay the 4-byte-per-synapse gather once."""
         t = self.transposed()
         if self.hetero:
-            wt = torch.empty(self.nnz, dtype=torch.float32, device=weights.device)
             wsrc = weights.contiguous()
-            check(lib().bsx_permute_f32(ptr(wsrc), ptr(t.perm), self.nnz, ptr(wt), _lib.current_stream()))
+            key = (wsrc.data_ptr(), wsrc._version, wsrc.numel())
+            cached = getattr(self, '_t_weights', None)
+            if cached is not None and cached[0] == key:
+                wt = cached[1]
+            else:
+                wt = torch.empty(self.nnz, dtype=torch.float32, device=weights.device)
+                check(lib().bsx_permute_f32(ptr(wsrc), ptr(t.perm), self.nnz, ptr(wt), _lib.current_stream()))
+                self._t_weights = (key, wt, wsrc)      # wsrc held so that its address cannot be reused
         else:
             wt = weights.contiguous()
         s = BsxConn()
@@ -206,7 +216,7 @@ class _SparseConn:
 
     def __matmul__(self, v):
         if isinstance(v, EventArray):
-            return event_matvec(self, v.value)
+            return event_matvec(self, v.value, method=self.matvec_method)
         if isinstance(v, torch.Tensor):
             return float_matvec(self, v)
         return NotImplemented
@@ -298,10 +308,19 @@ def float_vecmat(conn: _SparseConn, x: torch.Tensor):
     return conn._vecmat(x, event=False)
 
 
-def event_matvec(conn: _SparseConn, spk: torch.Tensor, bits: bool = False):
+def event_matvec(conn: _SparseConn, spk: torch.Tensor, bits: bool = False, method: str = 'gather'):
     """``conn @ EventArray(spk)``: ``y[i] = sum_k w[i,k] [spk[idx[i,k]] != 0]``.
-    ``bits=True`` takes packed uint32/int32 words (``(…, ceil(n_post/32))``)."""
+    ``bits=True`` takes packed uint32/int32 words (``(…, ceil(n_post/32))``).
+
+    method : ``'gather'`` walks every row and tests its targets' spike bits — deterministic,
+        cost independent of the firing rate.  ``'scatter'`` is the event-driven form: the
+        active postsynaptic neurons scatter along the transposed copy (built once), cost
+        proportional to the events — about twice as fast at 1 % firing, slower above ≈ 3 %;
+        heterogeneous sums then depend on the order of the atomic adds (last-bit differences).
+    """
     _require_cuda(spk, 'spikes')
+    if method not in ('gather', 'scatter'):
+        raise ValueError(f"method must be 'gather' or 'scatter', got {method!r}")
     n_pre, n_post = conn.shape
     if bits:
         words = (n_post + 31) // 32
@@ -312,6 +331,13 @@ def event_matvec(conn: _SparseConn, spk: torch.Tensor, bits: bool = False):
         fmt = spike_format_of(xb)
     batch = xb.shape[0]
     out = torch.empty((batch, n_pre), dtype=torch.float32, device=spk.device)
+    if method == 'scatter':
+        st = conn._transposed_struct(conn.data)
+        ws_bytes = lib().bsx_event_vecmat_workspace_bytes(batch, n_post)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=spk.device)
+        check(lib().bsx_event_vecmat(C.byref(st), ptr(xb), fmt, batch, ptr(out), 0, ptr(ws), ws_bytes,
+                                     _lib.current_stream()))
+        return out.reshape(lead + (n_pre,))
     st = conn._struct()
     ws_bytes = lib().bsx_event_matvec_workspace_bytes(batch, n_post)
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=spk.device)

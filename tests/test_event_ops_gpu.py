@@ -473,3 +473,71 @@ def test_microbenchmark_size_against_c_oracle(rate_id, microbench, c_oracle, cud
         ct = np.random.RandomState(221).standard_normal((1, n)).astype(np.float32)
         dx = het @ torch.from_numpy(ct).to(cuda)
         close(dx, c_oracle.float_matvec(ct, idx, w, n), scale=30)
+
+
+@pytest.mark.parametrize('shape', [(20, 30, 3), (33, 1000, 17), (257, 513, 131), (1000, 96, 7)])
+@pytest.mark.parametrize('hetero', [False, True])
+@pytest.mark.parametrize('layout', ['fixed', 'csr'])
+def test_event_driven_matvec_over_the_transposed_copy(shape, hetero, layout, cuda):
+    """``W @ spikes`` with ``method='scatter'``: the active columns scatter along the transposed
+    copy.  Same sums as the gather within tolerance; reproducible for homogeneous weights."""
+    from brainstate_b200 import EventArray
+    from brainstate_b200.event import event_matvec, pack_spikes
+    n_pre, n_post, K = shape
+    conn, idx, indptr, w = make(n_pre, n_post, K, 41, hetero, cuda, 0.6 if layout == 'csr' else None)
+    rs = np.random.RandomState(42)
+    for rate in (0.0, 0.02, 0.3, 1.0):
+        for lead in ((), (5,), (2, 9)):
+            spk = rs.random_sample(lead + (n_post,)) < rate
+            ts = torch.from_numpy(spk).to(cuda)
+            ref = eo.event_matvec(spk.reshape(-1, n_post), idx, w, n_pre, indptr=indptr).reshape(lead + (n_pre,))
+            y = event_matvec(conn, ts, method='scatter')
+            assert y.shape == ref.shape
+            if hetero:
+                close(y, ref)
+            else:
+                assert torch.equal(y, event_matvec(conn, ts, method='scatter'))   # identical addends: any order, one sum
+                close(y, ref)
+            close(event_matvec(conn, pack_spikes(ts), bits=True, method='scatter'), ref)
+    conn.matvec_method = 'scatter'                                     # what ``conn @ EventArray`` uses
+    close(conn @ EventArray(ts), ref)
+    with pytest.raises(ValueError):
+        event_matvec(conn, ts, method='sorted')
+
+
+def test_transposed_weights_follow_the_weight_tensor(cuda):
+    """The permuted weight copy behind the event-driven matvec is kept between calls and
+    refreshed after an in-place update or ``with_data``."""
+    from brainstate_b200.event import event_matvec
+    n_pre, n_post, K = 300, 200, 11
+    conn, idx, _, w = make(n_pre, n_post, K, 43, True, cuda)
+    spk = np.random.RandomState(44).random_sample(n_post) < 0.2
+    ts = torch.from_numpy(spk).to(cuda)
+    close(event_matvec(conn, ts, method='scatter'), eo.event_matvec(spk, idx, w, n_pre))
+    kept = conn._t_weights[1]
+    event_matvec(conn, ts, method='scatter')
+    assert conn._t_weights[1] is kept                                   # no second permutation
+    conn.data.mul_(2.0)                                                 # optimiser-style in-place step
+    close(event_matvec(conn, ts, method='scatter'), eo.event_matvec(spk, idx, 2 * w, n_pre))
+    w3 = (3 * w).astype(np.float32)
+    c3 = conn.with_data(torch.from_numpy(w3).to(cuda))
+    close(event_matvec(c3, ts, method='scatter'), eo.event_matvec(spk, idx, w3, n_pre))
+    close(event_matvec(conn, ts, method='scatter'), eo.event_matvec(spk, idx, 2 * w, n_pre))
+
+
+def test_host_buffer_pipeline_event_driven_reverse(cuda):
+    from brainstate_b200.host import HostEventProducts
+    n, K = 1000, 37
+    conn, idx, _, w = make(n, n, K, 31, True, cuda)
+    spk = np.random.RandomState(45).random_sample((40, n)) < 0.02
+    hs = torch.from_numpy(spk).pin_memory()
+    h1 = torch.empty((40, n), dtype=torch.float32).pin_memory()
+    h2 = torch.empty((40, n), dtype=torch.float32).pin_memory()
+    pipe = HostEventProducts(conn, chunk=16, reverse_method='scatter')
+    pipe(hs, h1, h2)
+    pipe(hs, h1, h2)
+    torch.cuda.synchronize()
+    close(h1, eo.event_vecmat(spk, idx, w, n))
+    close(h2, eo.event_matvec(spk, idx, w, n))
+    with pytest.raises(ValueError):
+        HostEventProducts(conn, reverse_method='sorted')
