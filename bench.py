@@ -229,8 +229,12 @@ class DevicePass:
         # transposed copy) beats the gather over all rows; above it the gather wins
         self.matvec_method = 'scatter' if RATE <= 0.03 else 'gather'
         self.st_t = self.conn._transposed_struct(self.tw) if self.matvec_method == 'scatter' else None
-        # per product: compact + scatter; for the gather: transpose-pack + one pass per 16 vectors
-        self.launches_per_pass = 2 + (2 if self.matvec_method == 'scatter' else 1 + self.passes)
+        # which scatter kernel the library picks for this batch: output slices in shared memory
+        # (one launch per product) or global atomics (compaction + scatter launch)
+        self.scatter_variant = self.lib.bsx_event_vecmat_variant(C.byref(self.st), self._lib.SPK_BOOL8, vectors)
+        per_scatter = 1 if self.scatter_variant == self._lib.VECMAT_SHARED_SLICES else 2
+        # for the gather: transpose-pack + one pass per 16 vectors
+        self.launches_per_pass = per_scatter + (per_scatter if self.matvec_method == 'scatter' else 1 + self.passes)
 
     def vecmat(self, spk_dev, stream):
         self._lib.check(self.lib.bsx_event_vecmat(C.byref(self.st), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
@@ -351,7 +355,7 @@ def run_ours(args):
 
     from brainstate_b200.host import HostEventProducts
     # public host-buffer API: upload, products, download overlap
-    pipe = HostEventProducts(layer.conn, chunk=16, reverse_method=dp.matvec_method)
+    pipe = HostEventProducts(layer.conn, chunk=64, reverse_method=dp.matvec_method)
 
     def e2e_pass():
         pipe(host_spk, host_y1, host_y2)               # spike @ W and W @ spike, host memory in and out
@@ -406,10 +410,17 @@ def run_ours(args):
                 'unit': 'GB/s', 'frac': a / peak, 'bytes_per_launch': nbytes, 'avg_launch_us': sec * 1e6,
                 'share_of_step': share, 'traffic': None, 'note': note}
 
-    r_s = roof('scatter_queue_kernel<hetero> (+compact)', s_bytes, s_launch_s, ms_scatter / ms_total,
-               'spike@W over the rows' + (' and W@spike over the transposed copy' if dp.matvec_method == 'scatter' else '')
-               + '; limited by the L2 rate of red.global.add.f32 (about 190 G adds/s in a stand-alone probe), '
-               'not by HBM')
+    smem_variant = dp.scatter_variant == _lib.VECMAT_SHARED_SLICES
+    what = 'spike@W over the rows' + (' and W@spike over the transposed copy' if dp.matvec_method == 'scatter' else '')
+    if smem_variant:
+        r_s = roof('scatter_smem_kernel<hetero>', s_bytes, s_launch_s, ms_scatter / ms_total,
+                   what + '; one block per (spike vector, 32768-column slice of the output held in shared memory); '
+                   'every active row is read once per slice (the second read from L2); limited by load latency '
+                   'at one block per SM and by the shared-memory atomic rate')
+    else:
+        r_s = roof('scatter_queue_kernel<hetero> (+compact)', s_bytes, s_launch_s, ms_scatter / ms_total,
+                   what + '; limited by the L2 rate of red.global.add.f32 (about 190 G adds/s in a stand-alone '
+                   'probe), not by HBM')
     r_s['atomic_adds_per_s'] = events_vec / s_launch_s
     if dp.matvec_method == 'scatter':
         r_g = roof('event_matvec_b16_kernel<hetero>', g_bytes, g_launch_s, 0.0,
@@ -428,7 +439,10 @@ def run_ours(args):
         try:
             tr = json.load(open(prof))
             r_g['traffic'] = float(tr['event_matvec_b16_kernel'])                      # captured at this launch size
-            r_s['traffic'] = float(tr['scatter_queue_kernel_per_16_vectors']) * T / 16  # grows with the events
+            if smem_variant:
+                r_s['traffic'] = float(tr['scatter_smem_kernel_per_vector']) * T          # one pair of blocks per vector
+            else:
+                r_s['traffic'] = float(tr['scatter_queue_kernel_per_16_vectors']) * T / 16  # grows with the events
         except Exception:
             pass
 
@@ -448,7 +462,7 @@ def run_ours(args):
         'roofline_other_kernel': roofline_2,
         'cpu_baseline': cpu,
         'events_per_step': events_all,
-        'variants': {'spike@W': 'scatter', 'W@spike': dp.matvec_method + (' over the transposed copy' if dp.matvec_method == 'scatter' else ''),
+        'variants': {'spike@W': 'scatter', 'scatter_kernel': 'shared-memory slices' if smem_variant else 'global atomics', 'W@spike': dp.matvec_method + (' over the transposed copy' if dp.matvec_method == 'scatter' else ''),
                      'chosen_for_rate': RATE},
         'network': network,
     }
@@ -510,9 +524,13 @@ def run_cases(torch, dev, dp, idx, w, peak):
             st = conn._struct()
             h = int(conn.hetero)
 
-            def vecmat():
-                _lib.check(lib.bsx_event_vecmat(C.byref(st), sd.data_ptr(), _lib.SPK_BOOL8, T, dp.y_vecmat.data_ptr(),
-                                                0, dp.ws.data_ptr(), dp.ws_bytes, stream))
+            def vecmat(bps=8):
+                _lib.check(lib.bsx_event_vecmat_tuned(C.byref(st), sd.data_ptr(), _lib.SPK_BOOL8, T,
+                                                      dp.y_vecmat.data_ptr(), 0, dp.ws.data_ptr(), dp.ws_bytes,
+                                                      0, bps, stream))
+
+            def vecmat_smem():
+                vecmat(-1)
 
             def matvec():
                 _lib.check(lib.bsx_pack_spikes(sd.data_ptr(), _lib.SPK_BOOL8, T, n, dp.bits.data_ptr(), stream))
@@ -527,15 +545,18 @@ def run_cases(torch, dev, dp, idx, w, peak):
             st_t = conn._transposed_struct(conn.data)
 
             def matvec_scatter():
-                _lib.check(lib.bsx_event_vecmat(C.byref(st_t), sd.data_ptr(), _lib.SPK_BOOL8, T, dp.y_matvec.data_ptr(),
-                                                0, dp.ws.data_ptr(), dp.ws_bytes, stream))
+                _lib.check(lib.bsx_event_vecmat_tuned(C.byref(st_t), sd.data_ptr(), _lib.SPK_BOOL8, T,
+                                                      dp.y_matvec.data_ptr(), 0, dp.ws.data_ptr(), dp.ws_bytes,
+                                                      0, -1, stream))
 
-            for prod, fn, alg in (('spike@W scatter', vecmat, events * (4 + 4 * h) + T * (n + 4 * n)),
+            for prod, fn, alg in (('spike@W scatter, global atomics', vecmat, events * (4 + 4 * h) + T * (n + 4 * n)),
+                                  ('spike@W scatter, output slices in shared memory', vecmat_smem,
+                                   events * (4 + 4 * h) + T * (n + 4 * n)),
                                   ('W@spike gather, one vector per pass', matvec,
                                    T * (n * K * 4 + n / 8 + 4 * n) + events * 4 * h),
                                   ('W@spike gather, 16 vectors per pass', matvec_b16,
                                    dp.passes * (n * K * 4 + 2 * n) + T * 4 * n + events * 4 * h),
-                                  ('W@spike scatter over the transposed copy', matvec_scatter,
+                                  ('W@spike scatter over the transposed copy, output slices in shared memory', matvec_scatter,
                                    events * (4 + 4 * h) + T * (n + 4 * n))):
                 for _ in range(3):
                     fn()

@@ -20,6 +20,7 @@ BSX_ERR_WORKSPACE = -4
 BSX_ERR_UNSUPPORTED = -5
 BSX_ERR_TIMEOUT = -6
 
+VECMAT_GLOBAL_ATOMICS, VECMAT_SHARED_SLICES = 0, 1
 SPK_BOOL8, SPK_F32, SPK_BITS32, SPK_LIST = 0, 1, 2, 3
 
 
@@ -97,6 +98,7 @@ SIGNATURES = {
     'bsx_event_vecmat_workspace_bytes': (_sz, [_i64, _i64]),
     'bsx_event_vecmat': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp, _sz, _vp]),
     'bsx_event_vecmat_tuned': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp, _sz, _i32, _i32, _vp]),
+    'bsx_event_vecmat_variant': (_i32, [_connp, _i32, _i64]),
     'bsx_event_vecmat_static': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp]),
     'bsx_float_vecmat': (_i32, [_connp, _vp, _i64, _vp, _i32, _vp, _sz, _vp]),
     'bsx_event_matvec_workspace_bytes': (_sz, [_i64, _i64]),

@@ -22,6 +22,7 @@ int vecmat_common(const bsx_conn_t* conn, const void* in, int format, const floa
 
 // Batched scatter with the output slice in shared memory (scatter_smem.cu).
 bool scatter_smem_applies(const bsx_conn_t* conn, int format, int64_t batch);
+bool scatter_smem_preferred(const bsx_conn_t* conn, int format, int64_t batch);
 int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, const float* x, int64_t batch,
                         float* out, int accumulate, cudaStream_t st);
 

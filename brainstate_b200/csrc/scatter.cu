@@ -107,10 +107,14 @@ int vecmat_common(const bsx_conn_t* conn, const void* in, int format, const floa
   if ((double)batch * (double)conn->n_pre >= 4294967296.0)
     return fail(BSX_ERR_UNSUPPORTED, "batch * n_pre must be below 2^32");
 
-  // blocks_per_sm < 0 asks for the variant that keeps output slices in shared memory.  It
-  // pays off only at high firing rates (measured: 1.5x faster at 10 %, slower at 1 %), and
-  // the rate is not known on the host, so it is never chosen automatically.
-  if (blocks_per_sm < 0) {
+  // The variant that keeps output slices in shared memory runs one block per (batch row,
+  // slice): it needs about as many of those as there are SMs, and re-reads every active row
+  // once per slice.  blocks_per_sm < 0 asks for it wherever it applies; with every tuning
+  // argument at 0 it is chosen when the batch fills the GPU and the output has at most two
+  // slices (measured at 65 536 columns: 1.0-1.1x the global-atomic kernel at 0.1 % firing,
+  // 1.5-2.2x at 1 %, 1.8-2.3x at 10 %, for 64 to 296 vectors).  A positive blocks_per_sm or
+  // chunk keeps the global-atomic kernel.
+  if (blocks_per_sm < 0 || (blocks_per_sm == 0 && chunk == 0 && scatter_smem_preferred(conn, format, batch))) {
     if (scatter_smem_applies(conn, format, batch))
       return launch_scatter_smem(conn, in, format, x, batch, out, accumulate, st);
     blocks_per_sm = 0;
@@ -155,6 +159,15 @@ int bsx_event_vecmat_tuned(const bsx_conn_t* conn, const void* spikes, int spike
     return fail(BSX_ERR_INVALID_ARG, "unknown spike format %d", spike_format);
   return vecmat_common(conn, spikes, spike_format, nullptr, batch, out, accumulate, workspace,
                        workspace_bytes, chunk, blocks_per_sm, as_stream(stream));
+}
+
+int bsx_event_vecmat_variant(const bsx_conn_t* conn, int spike_format, int64_t batch) {
+  if (spike_format < BSX_SPK_BOOL8 || spike_format > BSX_SPK_LIST)
+    return fail(BSX_ERR_INVALID_ARG, "unknown spike format %d", spike_format);
+  const int rc = check_conn(conn);
+  if (rc) return rc;
+  if (batch < 0) return fail(BSX_ERR_INVALID_ARG, "negative batch");
+  return scatter_smem_preferred(conn, spike_format, batch) ? BSX_VECMAT_SHARED_SLICES : BSX_VECMAT_GLOBAL_ATOMICS;
 }
 
 int bsx_event_vecmat(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,

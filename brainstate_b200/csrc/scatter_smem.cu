@@ -2,31 +2,85 @@
 //
 // For a batch of spike vectors and a modest number of postsynaptic neurons, one
 // thread block owns a slice of up to 32 768 columns of ONE batch row's output and keeps
-// it in shared memory (128 KB).  The block scans the spike row, lists the active
-// presynaptic rows, streams their indices and weights with 128-bit loads and adds the
-// entries that fall into its slice with shared-memory atomics — about four times the
-// rate of red.global.add.f32 — then writes the slice to global memory once, coalesced.
-// With n_post = 65 536 two blocks share a batch row and each reads every active row
-// (the second read hits L2); beyond four slices the re-reading outweighs any gain.
-// No workspace, no separate clearing of the output.  Like every atomic scatter, the
+// it in shared memory (128 KB).  The block lists the active presynaptic rows of its
+// spike vector (count, block-wide scan, write: one round when they fit the 8192-entry
+// list, rounds over 8192-neuron spans otherwise), then its warps take rows from the list
+// one at a time, issue all 128-bit index and weight loads of a 384-entry stretch before
+// touching any of them, and add the entries that fall into the slice with shared-memory
+// atomics — about four times the rate of red.global.add.f32.  The slice is written to
+// global memory once, coalesced: no workspace, no separate clearing of the output.
+// With n_post = 65 536 two blocks share a batch row and each reads every active row;
+// the two are neighbours in launch order, so the second read is served by L2.  Beyond
+// four slices the re-reading outweighs any gain.  Like every atomic scatter, the
 // summation order of heterogeneous weights is not fixed.
 //
-// Measured on B200 (65 536^2, 64 vectors): 1.5x faster than the global-atomic kernel
-// (scatter.cu) at 10 % firing, 1.2x slower at 1 %, 3.5x slower at 0.1 % — one block per
-// SM with 128 KB of accumulators leaves too few loads in flight to hide the latency of
-// the index stream when rows are scarce.  It is therefore opt-in (blocks_per_sm = -1 in
-// bsx_event_vecmat_tuned), never chosen automatically.
+// One block per SM: the kernel needs batch * slices >= the number of SMs to fill the
+// GPU, which is what the automatic choice in vecmat_common checks.
 #include "common.cuh"
 #include "internal.cuh"
 
 namespace bsx {
 
 constexpr int kSsThreads = 1024;
+constexpr int kSsWarps = kSsThreads / 32;
 constexpr int kSsSlice = 32768;   // floats of output per block
-constexpr int kSsList = 4096;     // active rows buffered per round
+constexpr int kSsList = 8192;     // active rows listed per round
+constexpr int kSsUnroll = 3;      // 128-bit loads in flight per lane and array
 
 __device__ __forceinline__ void smem_add(float* p, float v) {
   asm volatile("red.shared.add.f32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "f"(v) : "memory");
+}
+
+// Active spikes among the positions [i0, i1) of batch row b; their positions go to dst
+// when it is not null.  i0 is a multiple of 32.
+template <int FORMAT>
+__device__ __forceinline__ int list_span(const void* __restrict__ spikes, int64_t b, int64_t n_pre, int64_t words,
+                                         int64_t i0, int64_t i1, int32_t* dst) {
+  int c = 0;
+  if (i0 >= i1) return 0;
+  if (FORMAT == BSX_SPK_BITS32) {
+    const uint32_t* __restrict__ wp = static_cast<const uint32_t*>(spikes) + b * words;
+    for (int64_t k = i0 >> 5; k < ((i1 + 31) >> 5); ++k) {
+      uint32_t wd = __ldg(wp + k);
+      while (wd) {
+        const int64_t i = (k << 5) + (__ffs(wd) - 1);
+        wd &= wd - 1;
+        if (i < i1) {
+          if (dst) dst[c] = (int32_t)i;
+          ++c;
+        }
+      }
+    }
+  } else if (FORMAT == BSX_SPK_BOOL8) {
+    const uint8_t* __restrict__ sp = static_cast<const uint8_t*>(spikes) + b * n_pre;
+    int64_t i = i0;
+    for (; i < i1 && ((reinterpret_cast<uintptr_t>(sp + i) & 3) != 0); ++i)
+      if (sp[i]) { if (dst) dst[c] = (int32_t)i; ++c; }
+    for (; i + 4 <= i1; i += 4) {
+      const uint32_t wd = __ldg(reinterpret_cast<const uint32_t*>(sp + i));
+      if (wd == 0) continue;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if ((wd >> (8 * k)) & 0xffu) { if (dst) dst[c] = (int32_t)(i + k); ++c; }
+    }
+    for (; i < i1; ++i)
+      if (sp[i]) { if (dst) dst[c] = (int32_t)i; ++c; }
+  } else {
+    const float* __restrict__ fp = static_cast<const float*>(spikes) + b * n_pre;
+    for (int64_t i = i0; i < i1; ++i)
+      if (__ldg(fp + i) != 0.0f) { if (dst) dst[c] = (int32_t)i; ++c; }
+  }
+  return c;
+}
+
+template <bool HETERO>
+__device__ __forceinline__ void add_four(float* acc, int32_t col0, uint32_t ncol, const int4 j, const float4 t, float v) {
+  const uint32_t c0 = (uint32_t)(j.x - col0), c1 = (uint32_t)(j.y - col0), c2 = (uint32_t)(j.z - col0),
+                 c3 = (uint32_t)(j.w - col0);
+  if (c0 < ncol) smem_add(acc + c0, HETERO ? __fmul_rn(v, t.x) : v);
+  if (c1 < ncol) smem_add(acc + c1, HETERO ? __fmul_rn(v, t.y) : v);
+  if (c2 < ncol) smem_add(acc + c2, HETERO ? __fmul_rn(v, t.z) : v);
+  if (c3 < ncol) smem_add(acc + c3, HETERO ? __fmul_rn(v, t.w) : v);
 }
 
 template <bool HETERO, bool HAS_X, int FORMAT>
@@ -37,52 +91,56 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
   extern __shared__ __align__(16) unsigned char ss_raw[];
   float* acc = reinterpret_cast<float*>(ss_raw);
   int32_t* list = reinterpret_cast<int32_t*>(ss_raw + sizeof(float) * kSsSlice);
-  __shared__ int32_t warp_cnt[kSsThreads / 32];
-  __shared__ int32_t list_n;
+  __shared__ int32_t warp_tot[kSsWarps];
+  __shared__ int32_t s_next;
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int64_t b = blockIdx.y;
   const int32_t col0 = (int32_t)blockIdx.x * kSsSlice;
-  const int32_t ncol = (int32_t)((n_post - col0) < kSsSlice ? (n_post - col0) : kSsSlice);
+  const uint32_t ncol = (uint32_t)((n_post - col0) < kSsSlice ? (n_post - col0) : kSsSlice);
   for (int i = tid; i < kSsSlice / 4; i += kSsThreads) reinterpret_cast<float4*>(acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   const float w0 = HETERO ? 1.0f : __ldg(w);
   const int64_t words = (n_pre + 31) >> 5;
   const int4* __restrict__ idx4 = reinterpret_cast<const int4*>(idx);
   const float4* __restrict__ w4 = reinterpret_cast<const float4*>(w);
-  int64_t next = 0;
-  while (next < n_pre) {
-    // ---- list up to kSsList active rows starting at `next`, in ascending order
-    if (tid == 0) list_n = 0;
-    __syncthreads();
-    while (next < n_pre) {
-      const int64_t i = next + tid;
-      bool on = false;
-      if (i < n_pre) {
-        if (FORMAT == BSX_SPK_BITS32)
-          on = (static_cast<const uint32_t*>(spikes)[b * words + (i >> 5)] >> (i & 31)) & 1u;
-        else
-          on = spike_at<FORMAT>(spikes, b * n_pre + i);
-      }
-      const uint32_t m = __ballot_sync(0xffffffffu, on);
-      if (lane == 0) warp_cnt[wid] = __popc(m);
-      __syncthreads();
-      int base = list_n, total = 0;
-      for (int k = 0; k < kSsThreads / 32; ++k) {
-        if (k < wid) base += warp_cnt[k];
-        total += warp_cnt[k];
-      }
-      const bool fits = list_n + total <= kSsList;
-      if (fits && on) list[base + __popc(m & ((1u << lane) - 1u))] = (int32_t)i;
-      __syncthreads();
-      if (!fits) break;
-      if (tid == 0) list_n += total;
-      next += kSsThreads;
-      __syncthreads();
-      if (list_n > kSsList - kSsThreads) break;
+
+  int64_t span = n_pre;      // first try: all active rows of the vector in one round
+  int64_t lo = 0;
+  while (lo < n_pre) {
+    const int64_t hi = (n_pre - lo) < span ? n_pre : lo + span;
+    const int64_t per = (((hi - lo + kSsThreads - 1) / kSsThreads) + 31) & ~int64_t(31);
+    const int64_t i0 = lo + (int64_t)tid * per;
+    const int64_t i1 = (hi - i0) < per ? hi : i0 + per;
+    // ---- count, block-wide exclusive scan
+    const int c = list_span<FORMAT>(spikes, b, n_pre, words, i0, i1, nullptr);
+    int incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
     }
+    if (lane == 31) warp_tot[wid] = incl;
     __syncthreads();
-    const int n = list_n;
-    // ---- one warp per listed row
-    for (int t = wid; t < n; t += kSsThreads / 32) {
+    int base = incl - c, total = 0;
+#pragma unroll 8
+    for (int k = 0; k < kSsWarps; ++k) {
+      const int t = warp_tot[k];
+      if (k < wid) base += t;
+      total += t;
+    }
+    if (total > kSsList) {   // only with span > kSsList: spans of kSsList neurons always fit
+      span = kSsList;
+      __syncthreads();
+      continue;
+    }
+    if (c) list_span<FORMAT>(spikes, b, n_pre, words, i0, i1, list + base);
+    if (tid == 0) s_next = 0;
+    __syncthreads();
+    // ---- warps take listed rows one at a time
+    for (;;) {
+      int t = 0;
+      if (lane == 0) t = atomicAdd(&s_next, 1);
+      t = __shfl_sync(0xffffffffu, t, 0);
+      if (t >= total) break;
       const int64_t row = list[t];
       int64_t s, e;
       rm.range(row, s, e);
@@ -95,39 +153,40 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
         a1 = e & ~int64_t(3);
         if (a1 < a0) a1 = a0;
       }
+      // 128-bit body: every load of a stretch is issued before its first use
+      const int64_t q1 = a1 >> 2;
+      for (int64_t q = (a0 >> 2) + lane; q < q1; q += 32 * kSsUnroll) {
+        int4 j[kSsUnroll];
+        float4 t4[kSsUnroll];
+#pragma unroll
+        for (int u = 0; u < kSsUnroll; ++u) {
+          const bool in = q + 32 * u < q1;
+          j[u] = in ? __ldg(idx4 + q + 32 * u) : make_int4(-1, -1, -1, -1);
+          if (HETERO) t4[u] = in ? __ldg(w4 + q + 32 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+          else t4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < kSsUnroll; ++u) add_four<HETERO>(acc, col0, ncol, j[u], t4[u], v);
+      }
+      // unaligned head and tail of the row
       for (int64_t p = s + lane; p < a0; p += 32) {
-        const uint32_t c = (uint32_t)(__ldg(idx + p) - col0);
-        if (c < (uint32_t)ncol) smem_add(acc + c, HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
+        const uint32_t cc = (uint32_t)(__ldg(idx + p) - col0);
+        if (cc < ncol) smem_add(acc + cc, HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
       }
       for (int64_t p = a1 + lane; p < e; p += 32) {
-        const uint32_t c = (uint32_t)(__ldg(idx + p) - col0);
-        if (c < (uint32_t)ncol) smem_add(acc + c, HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
-      }
-      const int64_t q1 = a1 >> 2;
-#pragma unroll 2
-      for (int64_t q = (a0 >> 2) + lane; q < q1; q += 32) {
-        const int4 j = __ldg(idx4 + q);
-        float4 ww = make_float4(v, v, v, v);
-        if (HETERO) {
-          const float4 t4 = __ldg(w4 + q);
-          ww = make_float4(__fmul_rn(v, t4.x), __fmul_rn(v, t4.y), __fmul_rn(v, t4.z), __fmul_rn(v, t4.w));
-        }
-        const uint32_t c0 = (uint32_t)(j.x - col0), c1 = (uint32_t)(j.y - col0), c2 = (uint32_t)(j.z - col0),
-                       c3 = (uint32_t)(j.w - col0);
-        if (c0 < (uint32_t)ncol) smem_add(acc + c0, ww.x);
-        if (c1 < (uint32_t)ncol) smem_add(acc + c1, ww.y);
-        if (c2 < (uint32_t)ncol) smem_add(acc + c2, ww.z);
-        if (c3 < (uint32_t)ncol) smem_add(acc + c3, ww.w);
+        const uint32_t cc = (uint32_t)(__ldg(idx + p) - col0);
+        if (cc < ncol) smem_add(acc + cc, HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
       }
     }
     __syncthreads();
+    lo = hi;
   }
   // ---- write the slice
   float* __restrict__ ob = out + b * n_post + col0;
   if (((reinterpret_cast<uintptr_t>(ob) & 15) == 0) && (ncol % 4 == 0)) {
     float4* o4 = reinterpret_cast<float4*>(ob);
     const float4* a4 = reinterpret_cast<const float4*>(acc);
-    for (int i = tid; i < ncol / 4; i += kSsThreads) {
+    for (int i = tid; i < (int)(ncol / 4); i += kSsThreads) {
       float4 r = a4[i];
       if (accumulate) {
         const float4 old = o4[i];
@@ -136,7 +195,7 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
       o4[i] = r;
     }
   } else {
-    for (int i = tid; i < ncol; i += kSsThreads) ob[i] = accumulate ? ob[i] + acc[i] : acc[i];
+    for (int i = tid; i < (int)ncol; i += kSsThreads) ob[i] = accumulate ? ob[i] + acc[i] : acc[i];
   }
 }
 
@@ -144,6 +203,13 @@ bool scatter_smem_applies(const bsx_conn_t* conn, int format, int64_t batch) {
   if (format != BSX_SPK_BOOL8 && format != BSX_SPK_F32 && format != BSX_SPK_BITS32) return false;
   const int64_t slices = (conn->n_post + kSsSlice - 1) / kSsSlice;
   return batch >= 16 && batch <= 65535 && slices >= 1 && slices <= 4;
+}
+
+bool scatter_smem_preferred(const bsx_conn_t* conn, int format, int64_t batch) {
+  if (!scatter_smem_applies(conn, format, batch)) return false;
+  const int64_t slices = (conn->n_post + kSsSlice - 1) / kSsSlice;
+  const int sms = sm_count();
+  return sms > 0 && slices <= 2 && batch * slices * 4 >= (int64_t)sms * 3;
 }
 
 int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, const float* x, int64_t batch,

@@ -174,13 +174,23 @@ size_t bsx_event_vecmat_workspace_bytes(int64_t batch, int64_t n_pre);
 int bsx_event_vecmat(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                      float* out, int accumulate, void* workspace, size_t workspace_bytes,
                      bsx_stream_t stream);
-/* Same, with explicit launch geometry for tuning (0 = default): entries per
- * work item of a fixed-number row, and resident blocks per SM.  blocks_per_sm = -1
- * selects the variant that accumulates output slices in shared memory (batch >= 16,
- * n_post <= 131072; faster only at firing rates of several percent). */
+/* Same, with explicit launch geometry for tuning: entries per work item of a
+ * fixed-number row, and resident blocks per SM of the global-atomic kernel.
+ * blocks_per_sm = -1 asks for the variant that accumulates output slices of
+ * 32768 columns in shared memory wherever it applies (batch >= 16, n_post <=
+ * 131072).  With both at 0 (what bsx_event_vecmat passes) the library chooses:
+ * the shared-memory variant when batch * slices is at least 3/4 of the SM count
+ * and n_post <= 65536, the global-atomic kernel otherwise.  Any positive value
+ * keeps the global-atomic kernel. */
 int bsx_event_vecmat_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                            float* out, int accumulate, void* workspace, size_t workspace_bytes,
                            int chunk, int blocks_per_sm, bsx_stream_t stream);
+/* Which kernel bsx_event_vecmat runs for this connectivity, spike format and batch:
+ * BSX_VECMAT_GLOBAL_ATOMICS (compaction launch + scatter launch, uses the workspace) or
+ * BSX_VECMAT_SHARED_SLICES (one launch, workspace untouched).  Negative on invalid input. */
+#define BSX_VECMAT_GLOBAL_ATOMICS 0
+#define BSX_VECMAT_SHARED_SLICES 1
+int bsx_event_vecmat_variant(const bsx_conn_t* conn, int spike_format, int64_t batch);
 
 /*
  * Event vecmat without a workspace argument.  No counterpart in the reference:

@@ -541,3 +541,23 @@ def test_host_buffer_pipeline_event_driven_reverse(cuda):
     close(h2, eo.event_matvec(spk, idx, w, n))
     with pytest.raises(ValueError):
         HostEventProducts(conn, reverse_method='sorted')
+
+
+@pytest.mark.parametrize('rate', [0.0, 0.02, 0.5, 1.0])
+def test_shared_memory_scatter_lists_many_presynaptic_rows(rate, bsx, cuda):
+    """More presynaptic neurons than one round of the in-block row list holds (8192): sparse
+    vectors take one round over the whole vector, dense ones fall back to 8192-neuron spans.
+    Odd sizes put the byte, float and word scans on unaligned starts."""
+    from brainstate_b200 import _lib
+    from brainstate_b200.event import pack_spikes
+    n_pre, n_post, K, B = 20011, 40001, 5, 17
+    conn, idx, indptr, w = make(n_pre, n_post, K, 47, True, cuda)
+    spk = np.random.RandomState(48).random_sample((B, n_pre)) < rate
+    ref = eo.event_vecmat(spk, idx, w, n_post)
+    ts = torch.from_numpy(spk).to(cuda)
+    st = conn._struct()
+    stream = _lib.current_stream()
+    for t, fmt in ((ts, _lib.SPK_BOOL8), (ts.to(torch.float32) * 3.0, _lib.SPK_F32), (pack_spikes(ts), _lib.SPK_BITS32)):
+        out = torch.full((B, n_post), 7.0, device=cuda)
+        _lib.check(bsx.bsx_event_vecmat_tuned(C.byref(st), t.data_ptr(), fmt, B, out.data_ptr(), 0, None, 0, 0, -1, stream))
+        close(out, ref, scale=4)
