@@ -440,7 +440,9 @@ def run_ours(args):
             tr = json.load(open(prof))
             r_g['traffic'] = float(tr['event_matvec_b16_kernel'])                      # captured at this launch size
             if smem_variant:
-                r_s['traffic'] = float(tr['scatter_smem_kernel_per_vector']) * T          # one pair of blocks per vector
+                # L2 serves rows that several vectors share, so DRAM traffic does not grow in proportion
+                # to the vectors: the capture is of this launch size and is used for no other
+                r_s['traffic'] = float(tr['scatter_smem_kernel_296_vectors']) if T == 296 else None
             else:
                 r_s['traffic'] = float(tr['scatter_queue_kernel_per_16_vectors']) * T / 16  # grows with the events
         except Exception:
@@ -581,7 +583,8 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--vectors', type=int, default=256, help='spike vectors per step (per GPU)')
+    ap.add_argument('--vectors', type=int, default=296,
+                    help='spike vectors per step (per GPU); 296 vectors x 2 output slices = 4 blocks on each of the 148 SMs')
     ap.add_argument('--cases', action='store_true', help='also time the full rate x weight x product grid')
     ap.add_argument('--no-network', action='store_true', help='skip the sharded network run reported beside the headline')
     ap.add_argument('--profile', action='store_true',
