@@ -232,17 +232,29 @@ class DevicePass:
         # which scatter kernel the library picks for this batch: output slices in shared memory
         # (one launch per product) or global atomics (compaction + scatter launch)
         self.scatter_variant = self.lib.bsx_event_vecmat_variant(C.byref(self.st), self._lib.SPK_BOOL8, vectors)
-        per_scatter = 1 if self.scatter_variant == self._lib.VECMAT_SHARED_SLICES else 2
+        self.sliced = self.scatter_variant == self._lib.VECMAT_SHARED_SLICES
+        per_scatter = 1 if self.sliced else 2
+        if self.sliced:       # copies whose rows are grouped by output slice, built once like the matrix
+            self.st_s = self.conn._sliced_struct(self.tw)
+            if self.matvec_method == 'scatter':
+                self.st_t = self.conn._transposed_sliced_struct(self.tw)
         # for the gather: transpose-pack + one pass per 16 vectors
         self.launches_per_pass = per_scatter + (per_scatter if self.matvec_method == 'scatter' else 1 + self.passes)
 
     def vecmat(self, spk_dev, stream):
+        if self.sliced:
+            self._lib.check(self.lib.bsx_event_vecmat_sliced(C.byref(self.st_s), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
+                                                             self.T, self.y_vecmat.data_ptr(), 0, stream))
+            return
         self._lib.check(self.lib.bsx_event_vecmat(C.byref(self.st), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
                                                   self.T, self.y_vecmat.data_ptr(), 0, self.ws.data_ptr(),
                                                   self.ws_bytes, stream))
 
     def matvec(self, spk_dev, stream):
-        if self.matvec_method == 'scatter':
+        if self.matvec_method == 'scatter' and self.sliced:
+            self._lib.check(self.lib.bsx_event_vecmat_sliced(C.byref(self.st_t), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
+                                                             self.T, self.y_matvec.data_ptr(), 0, stream))
+        elif self.matvec_method == 'scatter':
             self._lib.check(self.lib.bsx_event_vecmat(C.byref(self.st_t), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
                                                       self.T, self.y_matvec.data_ptr(), 0, self.ws.data_ptr(),
                                                       self.ws_bytes, stream))
@@ -551,8 +563,22 @@ def run_cases(torch, dev, dp, idx, w, peak):
                                                       dp.y_matvec.data_ptr(), 0, dp.ws.data_ptr(), dp.ws_bytes,
                                                       0, -1, stream))
 
+            st_s, st_ts = conn._sliced_struct(conn.data), conn._transposed_sliced_struct(conn.data)
+
+            def vecmat_sliced():
+                _lib.check(lib.bsx_event_vecmat_sliced(C.byref(st_s), sd.data_ptr(), _lib.SPK_BOOL8, T,
+                                                       dp.y_vecmat.data_ptr(), 0, stream))
+
+            def matvec_sliced():
+                _lib.check(lib.bsx_event_vecmat_sliced(C.byref(st_ts), sd.data_ptr(), _lib.SPK_BOOL8, T,
+                                                       dp.y_matvec.data_ptr(), 0, stream))
+
             for prod, fn, alg in (('spike@W scatter, global atomics', vecmat, events * (4 + 4 * h) + T * (n + 4 * n)),
                                   ('spike@W scatter, output slices in shared memory', vecmat_smem,
+                                   events * (4 + 4 * h) + T * (n + 4 * n)),
+                                  ('spike@W scatter, shared-memory slices, rows grouped by slice', vecmat_sliced,
+                                   events * (4 + 4 * h) + T * (n + 4 * n)),
+                                  ('W@spike scatter over the transposed copy, shared-memory slices, grouped', matvec_sliced,
                                    events * (4 + 4 * h) + T * (n + 4 * n)),
                                   ('W@spike gather, one vector per pass', matvec,
                                    T * (n * K * 4 + n / 8 + 4 * n) + events * 4 * h),

@@ -99,6 +99,9 @@ SIGNATURES = {
     'bsx_event_vecmat': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp, _sz, _vp]),
     'bsx_event_vecmat_tuned': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp, _sz, _i32, _i32, _vp]),
     'bsx_event_vecmat_variant': (_i32, [_connp, _i32, _i64]),
+    'bsx_sliced_slices': (_i64, [_i64]),
+    'bsx_sliced_build': (_i32, [_connp, _vp, _vp, _vp, _vp]),
+    'bsx_event_vecmat_sliced': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp]),
     'bsx_event_vecmat_static': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp]),
     'bsx_float_vecmat': (_i32, [_connp, _vp, _i64, _vp, _i32, _vp, _sz, _vp]),
     'bsx_event_matvec_workspace_bytes': (_sz, [_i64, _i64]),

@@ -87,7 +87,7 @@ template <bool HETERO, bool HAS_X, int FORMAT>
 __global__ void __launch_bounds__(kSsThreads, 1)
 scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
                     const void* __restrict__ spikes, const float* __restrict__ x, int64_t n_pre,
-                    int64_t n_post, float* __restrict__ out, int accumulate, bool vec_ok) {
+                    int64_t n_post, float* __restrict__ out, int accumulate, bool vec_ok, int row_mul) {
   extern __shared__ __align__(16) unsigned char ss_raw[];
   float* acc = reinterpret_cast<float*>(ss_raw);
   int32_t* list = reinterpret_cast<int32_t*>(ss_raw + sizeof(float) * kSsSlice);
@@ -110,8 +110,29 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
     const int64_t per = (((hi - lo + kSsThreads - 1) / kSsThreads) + 31) & ~int64_t(31);
     const int64_t i0 = lo + (int64_t)tid * per;
     const int64_t i1 = (hi - i0) < per ? hi : i0 + per;
-    // ---- count, block-wide exclusive scan
-    const int c = list_span<FORMAT>(spikes, b, n_pre, words, i0, i1, nullptr);
+    // ---- count, block-wide exclusive scan.  Byte spikes in aligned 64-neuron portions are held
+    // in registers (four 128-bit loads in flight at once) for both the count and the write.
+    uint32_t rw[16];
+    bool in_regs = false;
+    int c;
+    if (FORMAT == BSX_SPK_BOOL8 && per == 64 && i0 + 64 <= hi &&
+        ((reinterpret_cast<uintptr_t>(static_cast<const uint8_t*>(spikes) + b * n_pre + i0) & 15) == 0)) {
+      in_regs = true;
+      const uint4* __restrict__ sp4 = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(spikes) + b * n_pre + i0);
+      c = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint4 t = __ldg(sp4 + k);
+        rw[4 * k + 0] = __vcmpne4(t.x, 0u) & 0x01010101u;
+        rw[4 * k + 1] = __vcmpne4(t.y, 0u) & 0x01010101u;
+        rw[4 * k + 2] = __vcmpne4(t.z, 0u) & 0x01010101u;
+        rw[4 * k + 3] = __vcmpne4(t.w, 0u) & 0x01010101u;
+      }
+#pragma unroll
+      for (int k = 0; k < 16; ++k) c += __popc(rw[k]);
+    } else {
+      c = list_span<FORMAT>(spikes, b, n_pre, words, i0, i1, nullptr);
+    }
     int incl = c;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -132,7 +153,21 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
       __syncthreads();
       continue;
     }
-    if (c) list_span<FORMAT>(spikes, b, n_pre, words, i0, i1, list + base);
+    if (c) {
+      if (in_regs) {
+        int32_t* dst = list + base;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          uint32_t m = rw[k];
+          while (m) {
+            *dst++ = (int32_t)(i0 + 4 * k + ((__ffs(m) - 1) >> 3));
+            m &= m - 1;
+          }
+        }
+      } else {
+        list_span<FORMAT>(spikes, b, n_pre, words, i0, i1, list + base);
+      }
+    }
     if (tid == 0) s_next = 0;
     __syncthreads();
     // ---- warps take listed rows one at a time
@@ -143,7 +178,8 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
       if (t >= total) break;
       const int64_t row = list[t];
       int64_t s, e;
-      rm.range(row, s, e);
+      // rows grouped by output slice: group (row, slice) is row `row * slices + slice` of the map
+      rm.range(row_mul > 1 ? row * row_mul + blockIdx.x : row, s, e);
       float v = HAS_X ? __ldg(x + b * n_pre + row) : 1.0f;
       if (!HETERO) v = __fmul_rn(v, w0);
       int64_t a0 = e, a1 = e;
@@ -152,6 +188,16 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
         if (a0 > e) a0 = e;
         a1 = e & ~int64_t(3);
         if (a1 < a0) a1 = a0;
+      }
+      // the unaligned head and tail of the row (at most 3 + 3 entries with 128-bit loads allowed):
+      // loaded now, applied after the body, so that they share the body's first round trip
+      const int nh = (int)(a0 - s), nt = (int)(e - a1);
+      int32_t hj = -1;
+      float hw = 0.0f;
+      if (vec_ok && lane < nh + nt) {
+        const int64_t p = lane < nh ? s + lane : a1 + (lane - nh);
+        hj = __ldg(idx + p);
+        if (HETERO) hw = __ldg(w + p);
       }
       // 128-bit body: every load of a stretch is issued before its first use
       const int64_t q1 = a1 >> 2;
@@ -168,14 +214,14 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
 #pragma unroll
         for (int u = 0; u < kSsUnroll; ++u) add_four<HETERO>(acc, col0, ncol, j[u], t4[u], v);
       }
-      // unaligned head and tail of the row
-      for (int64_t p = s + lane; p < a0; p += 32) {
-        const uint32_t cc = (uint32_t)(__ldg(idx + p) - col0);
-        if (cc < ncol) smem_add(acc + cc, HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
-      }
-      for (int64_t p = a1 + lane; p < e; p += 32) {
-        const uint32_t cc = (uint32_t)(__ldg(idx + p) - col0);
-        if (cc < ncol) smem_add(acc + cc, HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
+      if (vec_ok) {
+        const uint32_t cc = (uint32_t)(hj - col0);
+        if (cc < ncol) smem_add(acc + cc, HETERO ? __fmul_rn(v, hw) : v);
+      } else {
+        for (int64_t p = s + lane; p < e; p += 32) {
+          const uint32_t cc = (uint32_t)(__ldg(idx + p) - col0);
+          if (cc < ncol) smem_add(acc + cc, HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
+        }
       }
     }
     __syncthreads();
@@ -199,6 +245,62 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
   }
 }
 
+// Groups the entries of every row by output slice (slice = column / 32768), keeping
+// their order inside a group.  s_indptr[row * S + k] is where group k of the row starts;
+// the row keeps its place [start, end) in the arrays.  With s_indices == nullptr only the
+// offsets are written (for rows that are already grouped, e.g. sorted by column).
+// One warp per row.  Columns beyond the last slice are kept in the last group.
+__global__ void __launch_bounds__(256)
+slice_rows_kernel(RowMap rm, const int32_t* __restrict__ idx, int64_t n_pre, int S, int64_t nnz,
+                  int64_t* __restrict__ s_indptr, int32_t* __restrict__ s_indices, int32_t* __restrict__ s_perm) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const uint32_t lt = (1u << lane) - 1u;
+  if (warp == 0 && lane == 0) s_indptr[n_pre * S] = nnz;
+  for (int64_t row = warp; row < n_pre; row += nwarps) {
+    int64_t s, e;
+    rm.range(row, s, e);
+    int cnt[4] = {0, 0, 0, 0};
+    for (int64_t p = s + lane; p < e; p += 32) {
+      uint32_t sl = (uint32_t)__ldg(idx + p) / (uint32_t)kSsSlice;
+      if (sl > (uint32_t)(S - 1)) sl = (uint32_t)(S - 1);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) cnt[k] += (sl == (uint32_t)k);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) cnt[k] += __shfl_xor_sync(0xffffffffu, cnt[k], o);
+    int64_t base[4];
+    base[0] = s;
+#pragma unroll
+    for (int k = 1; k < 4; ++k) base[k] = base[k - 1] + cnt[k - 1];
+    if (lane < S) s_indptr[row * S + lane] = lane == 0 ? base[0] : lane == 1 ? base[1] : lane == 2 ? base[2] : base[3];
+    if (!s_indices) continue;
+    for (int64_t p0 = s; p0 < e; p0 += 32) {
+      const int64_t p = p0 + lane;
+      int32_t j = 0;
+      uint32_t sl = 0xffffffffu;
+      if (p < e) {
+        j = __ldg(idx + p);
+        sl = (uint32_t)j / (uint32_t)kSsSlice;
+        if (sl > (uint32_t)(S - 1)) sl = (uint32_t)(S - 1);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t m = __ballot_sync(0xffffffffu, sl == (uint32_t)k);
+        if (sl == (uint32_t)k) {
+          const int64_t pos = base[k] + __popc(m & lt);
+          s_indices[pos] = j;
+          s_perm[pos] = (int32_t)p;
+        }
+        base[k] += __popc(m);
+      }
+    }
+  }
+}
+
 bool scatter_smem_applies(const bsx_conn_t* conn, int format, int64_t batch) {
   if (format != BSX_SPK_BOOL8 && format != BSX_SPK_F32 && format != BSX_SPK_BITS32) return false;
   const int64_t slices = (conn->n_post + kSsSlice - 1) / kSsSlice;
@@ -213,7 +315,7 @@ bool scatter_smem_preferred(const bsx_conn_t* conn, int format, int64_t batch) {
 }
 
 int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, const float* x, int64_t batch,
-                        float* out, int accumulate, cudaStream_t st) {
+                        float* out, int accumulate, cudaStream_t st, int row_mul) {
   if (sm_count() <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
   const int64_t slices = (conn->n_post + kSsSlice - 1) / kSsSlice;
   const dim3 grid((unsigned)slices, (unsigned)batch, 1);
@@ -226,7 +328,7 @@ int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, 
                                   (int)smem));                                                               \
     scatter_smem_kernel<H, X, F><<<grid, kSsThreads, smem, st>>>(rm, conn->indices, conn->weights, spikes, x, \
                                                                  conn->n_pre, conn->n_post, out, accumulate, \
-                                                                 vec_ok);                                    \
+                                                                 vec_ok, row_mul);                           \
   } while (0)
 #define BSX_SS_F(H, X)                                           \
   do {                                                           \
@@ -246,3 +348,51 @@ int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, 
 }
 
 }  // namespace bsx
+
+using namespace bsx;
+
+extern "C" {
+
+int64_t bsx_sliced_slices(int64_t n_post) { return n_post <= 0 ? 0 : (n_post + kSsSlice - 1) / kSsSlice; }
+
+int bsx_sliced_build(const bsx_conn_t* conn, int64_t* s_indptr, int32_t* s_indices, int32_t* s_perm,
+                     bsx_stream_t stream) {
+  const int rc = check_conn(conn);
+  if (rc) return rc;
+  const int64_t S = bsx_sliced_slices(conn->n_post);
+  if (S < 1 || S > 4) return fail(BSX_ERR_UNSUPPORTED, "the sliced layout covers 1 to 131072 columns");
+  if (!s_indptr) return fail(BSX_ERR_INVALID_ARG, "s_indptr is NULL");
+  if ((s_indices == nullptr) != (s_perm == nullptr))
+    return fail(BSX_ERR_INVALID_ARG, "s_indices and s_perm are given together or not at all");
+  if (conn->nnz >= (int64_t)INT32_MAX) return fail(BSX_ERR_UNSUPPORTED, "nnz must be below 2^31");
+  const int sms = sm_count();
+  if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  int64_t blocks = (conn->n_pre + 7) / 8;
+  if (blocks < 1) blocks = 1;
+  if (blocks > (int64_t)sms * 16) blocks = (int64_t)sms * 16;
+  slice_rows_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(make_rowmap(conn), conn->indices, conn->n_pre,
+                                                                     (int)S, conn->nnz, s_indptr, s_indices, s_perm);
+  BSX_LAUNCH_CHECK("slice_rows_kernel");
+  return BSX_OK;
+}
+
+int bsx_event_vecmat_sliced(const bsx_conn_t* sliced, const void* spikes, int spike_format, int64_t batch,
+                            float* out, int accumulate, bsx_stream_t stream) {
+  const int rc = check_conn(sliced);
+  if (rc) return rc;
+  if (!sliced->indptr || !sliced->indptr_is_64)
+    return fail(BSX_ERR_INVALID_ARG, "the sliced layout has 64-bit group offsets in indptr");
+  if (batch < 0) return fail(BSX_ERR_INVALID_ARG, "negative batch");
+  if (batch == 0 || sliced->n_post == 0) return BSX_OK;
+  if (!out) return fail(BSX_ERR_INVALID_ARG, "out is NULL");
+  if (sliced->n_pre == 0) return accumulate ? BSX_OK : launch_zero(out, batch * sliced->n_post, as_stream(stream));
+  if (!spikes) return fail(BSX_ERR_INVALID_ARG, "input vector is NULL");
+  if (spike_format != BSX_SPK_BOOL8 && spike_format != BSX_SPK_F32 && spike_format != BSX_SPK_BITS32)
+    return fail(BSX_ERR_UNSUPPORTED, "the sliced scatter takes byte, float or packed spikes");
+  const int64_t S = bsx_sliced_slices(sliced->n_post);
+  if (S > 4 || batch > 65535) return fail(BSX_ERR_UNSUPPORTED, "the sliced scatter covers up to 131072 columns and 65535 vectors");
+  return launch_scatter_smem(sliced, spikes, spike_format, nullptr, batch, out, accumulate, as_stream(stream), (int)S);
+}
+
+}  // extern "C"
+

@@ -89,6 +89,8 @@ class _SparseConn:
                 raise ValueError('indptr must have n_pre + 1 entries')
             self.indptr = indptr.contiguous()
         self._transposed: Optional[_Transposed] = None
+        self._sliced = None
+        self._t_groups = None
         self.matvec_method = 'gather'    # what ``conn @ EventArray`` uses; see ``event_matvec``
         self._set_data(data)
 
@@ -108,7 +110,8 @@ class _SparseConn:
             raise ValueError(f'weights of shape {tuple(data.shape)} match neither a scalar nor the '
                              f'indices {tuple(self.indices.shape)}')
         self.data = data
-        self._t_weights = None          # permuted copy for the transposed layout, made on demand
+        self._t_weights = None          # permuted copies for the transposed and the sliced layout,
+        self._s_weights = None          # made on demand
 
     def with_data(self, data):
         """A view of the same connectivity with other weights
@@ -203,6 +206,59 @@ class _SparseConn:
         s._keep = (wt,)
         return s
 
+    # -- rows grouped by output slice (for the batched scatter that keeps slices in shared memory)
+    def _group_offsets(self, st: BsxConn, n_rows: int, regroup: bool):
+        S = int(lib().bsx_sliced_slices(st.n_post))
+        dev = self.indices.device
+        s_indptr = torch.empty(n_rows * S + 1, dtype=torch.int64, device=dev)
+        s_indices = s_perm = None
+        if regroup:
+            s_indices = torch.empty(self.nnz, dtype=torch.int32, device=dev)
+            s_perm = torch.empty(self.nnz, dtype=torch.int32, device=dev)
+        check(lib().bsx_sliced_build(C.byref(st), ptr(s_indptr), ptr(s_indices) if regroup else None,
+                                     ptr(s_perm) if regroup else None, _lib.current_stream()))
+        return s_indptr, s_indices, s_perm
+
+    def _sliced_struct(self, weights: torch.Tensor):
+        """``bsx_conn_t`` of the copy whose rows are grouped by output slice (built once); the
+        regrouped weights are kept until the weight tensor changes."""
+        if getattr(self, '_sliced', None) is None:
+            self._sliced = self._group_offsets(self._struct(), self.shape[0], regroup=True)
+        s_indptr, s_indices, s_perm = self._sliced
+        if self.hetero:
+            wsrc = weights.contiguous()
+            key = (wsrc.data_ptr(), wsrc._version, wsrc.numel())
+            cached = getattr(self, '_s_weights', None)
+            if cached is not None and cached[0] == key:
+                ws_ = cached[1]
+            else:
+                ws_ = torch.empty(self.nnz, dtype=torch.float32, device=weights.device)
+                check(lib().bsx_permute_f32(ptr(wsrc), ptr(s_perm), self.nnz, ptr(ws_), _lib.current_stream()))
+                self._s_weights = (key, ws_, wsrc)
+        else:
+            ws_ = weights.contiguous()
+        s = BsxConn()
+        s.n_pre, s.n_post = self.shape
+        s.conn_num = 0
+        s.nnz = self.nnz
+        s.indices = s_indices.data_ptr() if self.nnz else None
+        s.indptr = s_indptr.data_ptr()
+        s.indptr_is_64 = 1
+        s.hetero = int(self.hetero)
+        s.weights = ws_.data_ptr()
+        s._keep = (ws_, s_indptr, s_indices)
+        return s
+
+    def _transposed_sliced_struct(self, weights: torch.Tensor):
+        """The transposed copy read as a sliced layout: its rows are sorted by source neuron, hence
+        already grouped, so only the group offsets are added."""
+        st = self._transposed_struct(weights)
+        if getattr(self, '_t_groups', None) is None:
+            self._t_groups = self._group_offsets(st, self.shape[1], regroup=False)[0]
+        st.indptr = self._t_groups.data_ptr()
+        st._keep = st._keep + (self._t_groups,)
+        return st
+
     # -- products ------------------------------------------------------------------
     def _vecmat(self, x, event: bool, method: str = 'scatter'):
         return _VecMat.apply(x, self.data, self, event, method)
@@ -284,6 +340,11 @@ def _raw_vecmat(conn: _SparseConn, x: torch.Tensor, weights: torch.Tensor, event
     if method not in ('scatter', 'gather'):
         raise ValueError(f"method must be 'scatter' or 'gather', got {method!r}")
     st = conn._struct(weights)
+    if event and lib().bsx_event_vecmat_variant(C.byref(st), spike_format_of(xb), batch) == _lib.VECMAT_SHARED_SLICES:
+        # a batch that fills the GPU: one launch over the copy whose rows are grouped by output slice
+        check(lib().bsx_event_vecmat_sliced(C.byref(conn._sliced_struct(weights)), ptr(xb), spike_format_of(xb),
+                                            batch, ptr(out), int(accumulate), stream))
+        return out.reshape(lead + (n_post,))
     ws_bytes = lib().bsx_event_vecmat_workspace_bytes(batch, n_pre)
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
     if event:
@@ -333,6 +394,10 @@ def event_matvec(conn: _SparseConn, spk: torch.Tensor, bits: bool = False, metho
     out = torch.empty((batch, n_pre), dtype=torch.float32, device=spk.device)
     if method == 'scatter':
         st = conn._transposed_struct(conn.data)
+        if lib().bsx_event_vecmat_variant(C.byref(st), fmt, batch) == _lib.VECMAT_SHARED_SLICES:
+            check(lib().bsx_event_vecmat_sliced(C.byref(conn._transposed_sliced_struct(conn.data)), ptr(xb), fmt,
+                                                batch, ptr(out), 0, _lib.current_stream()))
+            return out.reshape(lead + (n_pre,))
         ws_bytes = lib().bsx_event_vecmat_workspace_bytes(batch, n_post)
         ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=spk.device)
         check(lib().bsx_event_vecmat(C.byref(st), ptr(xb), fmt, batch, ptr(out), 0, ptr(ws), ws_bytes,

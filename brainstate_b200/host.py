@@ -59,6 +59,12 @@ class HostEventProducts:
         self.ws_f = torch.empty(max(self.ws_f_bytes, 1), dtype=torch.uint8, device=dev)   # compute is serial: one set
         self.ws_r = torch.empty(max(self.ws_r_bytes, 1), dtype=torch.uint8, device=dev)
         self.st = conn._struct()
+        # chunks that fill the GPU run the scatter over the copies grouped by output slice
+        self.sliced = l.bsx_event_vecmat_variant(C.byref(self.st), _lib.SPK_BOOL8, self.chunk) == _lib.VECMAT_SHARED_SLICES
+        if self.sliced:
+            self.st_f = conn._sliced_struct(conn.data) if forward else None
+            if reverse and reverse_method == 'scatter':
+                self.st_t = conn._transposed_sliced_struct(conn.data)
 
     def __call__(self, spk_host: torch.Tensor, y_fwd_host: Optional[torch.Tensor] = None,
                  y_rev_host: Optional[torch.Tensor] = None):
@@ -92,11 +98,17 @@ class HostEventProducts:
                 if c >= self.slots:
                     self.s_comp.wait_event(ev_out[c - self.slots])     # the slot's results were downloaded
                 stream = self.s_comp.cuda_stream
-                if self.forward:
+                if self.forward and self.sliced:
+                    check(l.bsx_event_vecmat_sliced(C.byref(self.st_f), self.spk[slot].data_ptr(), _lib.SPK_BOOL8, nb,
+                                                    self.y_fwd[slot].data_ptr(), 0, stream))
+                elif self.forward:
                     check(l.bsx_event_vecmat(C.byref(self.st), self.spk[slot].data_ptr(), _lib.SPK_BOOL8, nb,
                                              self.y_fwd[slot].data_ptr(), 0, self.ws_f.data_ptr(), self.ws_f_bytes,
                                              stream))
-                if self.reverse and self.reverse_method == 'scatter':
+                if self.reverse and self.reverse_method == 'scatter' and self.sliced:
+                    check(l.bsx_event_vecmat_sliced(C.byref(self.st_t), self.spk[slot].data_ptr(), _lib.SPK_BOOL8, nb,
+                                                    self.y_rev[slot].data_ptr(), 0, stream))
+                elif self.reverse and self.reverse_method == 'scatter':
                     check(l.bsx_event_vecmat(C.byref(self.st_t), self.spk[slot].data_ptr(), _lib.SPK_BOOL8, nb,
                                              self.y_rev[slot].data_ptr(), 0, self.ws_r.data_ptr(), self.ws_r_bytes,
                                              stream))

@@ -193,6 +193,30 @@ int bsx_event_vecmat_tuned(const bsx_conn_t* conn, const void* spikes, int spike
 int bsx_event_vecmat_variant(const bsx_conn_t* conn, int spike_format, int64_t batch);
 
 /*
+ * Sliced layout for the shared-memory variant.  No counterpart in the reference: a
+ * derived copy, like the transposed one.  The entries of every row are grouped by
+ * output slice (slice = column / 32768, original order kept inside a group), so that
+ * the block that owns a slice reads only its own entries instead of the whole row:
+ *   s_indptr  (n_pre*S+1) int64   start of group (row, slice) = entry row*S + slice;
+ *                                 S = bsx_sliced_slices(n_post), at most 4
+ *   s_indices (nnz)       int32   the targets, regrouped
+ *   s_perm    (nnz)       int32   position of each entry in the original arrays
+ *                                 (weights of the copy = bsx_permute_f32(w, s_perm))
+ * With s_indices = s_perm = NULL only s_indptr is written: for rows that are already
+ * grouped (sorted targets, as in the transposed copy) the original arrays serve.
+ * bsx_event_vecmat_sliced takes a bsx_conn_t whose indptr is s_indptr (64-bit), whose
+ * indices/weights are the regrouped arrays and whose n_pre, n_post, nnz, hetero are
+ * those of the original, and computes what bsx_event_vecmat computes, in one launch
+ * with no workspace.  It is worth calling where bsx_event_vecmat_variant answers
+ * BSX_VECMAT_SHARED_SLICES; below that batch size it leaves SMs idle.
+ */
+int64_t bsx_sliced_slices(int64_t n_post);
+int bsx_sliced_build(const bsx_conn_t* conn, int64_t* s_indptr, int32_t* s_indices, int32_t* s_perm,
+                     bsx_stream_t stream);
+int bsx_event_vecmat_sliced(const bsx_conn_t* sliced, const void* spikes, int spike_format, int64_t batch,
+                            float* out, int accumulate, bsx_stream_t stream);
+
+/*
  * Event vecmat without a workspace argument.  No counterpart in the reference:
  * it exists for callers that cannot obtain device memory when they call (a
  * custom-call handler inside a framework that owns the GPU's memory pool; a

@@ -561,3 +561,93 @@ def test_shared_memory_scatter_lists_many_presynaptic_rows(rate, bsx, cuda):
         out = torch.full((B, n_post), 7.0, device=cuda)
         _lib.check(bsx.bsx_event_vecmat_tuned(C.byref(st), t.data_ptr(), fmt, B, out.data_ptr(), 0, None, 0, 0, -1, stream))
         close(out, ref, scale=4)
+
+
+@pytest.mark.parametrize('n_post', [1000, 32768, 40001, 70003, 131072])
+@pytest.mark.parametrize('layout', ['fixed', 'csr'])
+def test_rows_grouped_by_output_slice(n_post, layout, bsx, cuda):
+    """``bsx_sliced_build``: every row's entries stably partitioned by ``column // 32768``;
+    offsets, regrouped targets and the permutation bit for bit against NumPy."""
+    from brainstate_b200 import _lib
+    n_pre, K = 333, 57
+    conn, idx, indptr, w = make(n_pre, n_post, K, 51, True, cuda, 0.7 if layout == 'csr' else None)
+    S = int(bsx.bsx_sliced_slices(n_post))
+    assert S == (n_post + 32767) // 32768
+    flat = idx.reshape(-1)
+    ip = indptr if indptr is not None else np.arange(n_pre + 1, dtype=np.int64) * K
+    ref_ptr = np.empty(n_pre * S + 1, dtype=np.int64)
+    ref_idx, ref_perm = np.empty_like(flat), np.empty(flat.size, dtype=np.int32)
+    for i in range(n_pre):
+        s, e = int(ip[i]), int(ip[i + 1])
+        sl = flat[s:e] // 32768
+        order = np.argsort(sl, kind='stable')
+        ref_idx[s:e] = flat[s:e][order]
+        ref_perm[s:e] = s + order
+        ref_ptr[i * S:(i + 1) * S] = s + np.concatenate(([0], np.cumsum(np.bincount(sl, minlength=S))[:-1]))
+    ref_ptr[-1] = flat.size
+    s_indptr, s_indices, s_perm = conn._group_offsets(conn._struct(), n_pre, regroup=True)
+    assert np.array_equal(s_indptr.cpu().numpy(), ref_ptr)
+    assert np.array_equal(s_indices.cpu().numpy(), ref_idx)
+    assert np.array_equal(s_perm.cpu().numpy(), ref_perm)
+    only_ptr = conn._group_offsets(conn._struct(), n_pre, regroup=False)[0]
+    assert torch.equal(only_ptr, s_indptr)
+    st = conn._struct()
+    assert bsx.bsx_sliced_build(C.byref(st), s_indptr.data_ptr(), s_indices.data_ptr(), None, None) == _lib.BSX_ERR_INVALID_ARG
+
+
+@pytest.mark.parametrize('n_post', [1000, 40001, 70003, 131072])
+@pytest.mark.parametrize('hetero', [False, True])
+def test_scatter_over_rows_grouped_by_slice(n_post, hetero, bsx, cuda):
+    """``bsx_event_vecmat_sliced`` on the regrouped copy (and on the transposed copy with group
+    offsets only) against the oracle, for every spike format and when accumulating."""
+    from brainstate_b200 import _lib
+    from brainstate_b200.event import pack_spikes, event_matvec
+    n_pre, K, B = 777, 29, 19
+    rs = np.random.RandomState(n_post % 89)
+    for layout in (None, 0.7):
+        conn, idx, indptr, w = make(n_pre, n_post, K, 53, hetero, cuda, layout)
+        spk = rs.random_sample((B, n_pre)) < 0.15
+        ref = eo.event_vecmat(spk, idx, w, n_post, indptr)
+        ts = torch.from_numpy(spk).to(cuda)
+        st = conn._sliced_struct(conn.data)
+        stream = _lib.current_stream()
+
+        def sliced(t, fmt, out, accumulate=0):
+            _lib.check(bsx.bsx_event_vecmat_sliced(C.byref(st), t.data_ptr(), fmt, B, out.data_ptr(), accumulate, stream))
+            return out
+
+        y = sliced(ts, _lib.SPK_BOOL8, torch.full((B, n_post), 9.0, device=cuda))
+        close(y, ref)
+        if not hetero:
+            assert np.array_equal(y.cpu().numpy(), ref)
+        xf = torch.from_numpy((spk * rs.uniform(0.5, 2, spk.shape)).astype(np.float32)).to(cuda)
+        close(sliced(xf, _lib.SPK_F32, torch.empty_like(y)), ref)
+        close(sliced(pack_spikes(ts), _lib.SPK_BITS32, y.clone(), accumulate=1), 2 * ref)
+        # W @ spikes over the transposed copy, whose sorted rows only need the group offsets
+        spk_post = rs.random_sample((B, n_post)) < 0.05
+        tp = torch.from_numpy(spk_post).to(cuda)
+        st_t = conn._transposed_sliced_struct(conn.data)
+        yt = torch.empty((B, n_pre), dtype=torch.float32, device=cuda)
+        _lib.check(bsx.bsx_event_vecmat_sliced(C.byref(st_t), tp.data_ptr(), _lib.SPK_BOOL8, B, yt.data_ptr(), 0, stream))
+        close(yt, eo.event_matvec(spk_post, idx, w, n_pre, indptr=indptr))
+
+
+def test_large_batches_take_the_sliced_copy(cuda):
+    """Batches that fill the GPU go through the copy grouped by output slice, in both directions,
+    and agree with the small-batch path."""
+    from brainstate_b200 import EventArray, _lib
+    from brainstate_b200.event import event_matvec
+    n, K, B = 3000, 41, 160
+    conn, idx, _, w = make(n, n, K, 55, True, cuda)
+    spk = np.random.RandomState(56).random_sample((B, n)) < 0.03
+    ts = torch.from_numpy(spk).to(cuda)
+    st = conn._struct()
+    assert _lib.lib().bsx_event_vecmat_variant(C.byref(st), _lib.SPK_BOOL8, B) == _lib.VECMAT_SHARED_SLICES
+    assert _lib.lib().bsx_event_vecmat_variant(C.byref(st), _lib.SPK_BOOL8, 8) == _lib.VECMAT_GLOBAL_ATOMICS
+    y = EventArray(ts) @ conn
+    assert conn._sliced is not None
+    close(y, eo.event_vecmat(spk, idx, w, n))
+    close(y[:8], (EventArray(ts[:8]) @ conn).cpu().numpy())
+    z = event_matvec(conn, ts, method='scatter')
+    assert conn._t_groups is not None
+    close(z, eo.event_matvec(spk, idx, w, n))
