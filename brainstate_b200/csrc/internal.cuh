@@ -24,7 +24,7 @@ int vecmat_common(const bsx_conn_t* conn, const void* in, int format, const floa
 bool scatter_smem_applies(const bsx_conn_t* conn, int format, int64_t batch);
 bool scatter_smem_preferred(const bsx_conn_t* conn, int format, int64_t batch);
 int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, const float* x, int64_t batch,
-                        float* out, int accumulate, cudaStream_t st, int row_mul = 1);
+                        float* out, int accumulate, cudaStream_t st, int row_mul = 0);   // row_mul >= 1: sliced layout with that many slices
 
 // Batched event matvec, 16 spike vectors per pass over the indices (gather_batched.cu).
 size_t b16_mask_bytes(int64_t batch, int64_t n_post);

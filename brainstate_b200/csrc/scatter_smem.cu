@@ -26,6 +26,7 @@ constexpr int kSsWarps = kSsThreads / 32;
 constexpr int kSsSlice = 32768;   // floats of output per block
 constexpr int kSsList = 8192;     // active rows listed per round
 constexpr int kSsUnroll = 3;      // 128-bit loads in flight per lane and array
+constexpr int kSsDeal = 12;       // 32-entry stretches in flight per warp over the sliced layout
 
 __device__ __forceinline__ void smem_add(float* p, float v) {
   asm volatile("red.shared.add.f32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "f"(v) : "memory");
@@ -83,7 +84,7 @@ __device__ __forceinline__ void add_four(float* acc, int32_t col0, uint32_t ncol
   if (c3 < ncol) smem_add(acc + c3, HETERO ? __fmul_rn(v, t.w) : v);
 }
 
-template <bool HETERO, bool HAS_X, int FORMAT>
+template <bool HETERO, bool HAS_X, int FORMAT, bool SLICED>
 __global__ void __launch_bounds__(kSsThreads, 1)
 scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
                     const void* __restrict__ spikes, const float* __restrict__ x, int64_t n_pre,
@@ -179,9 +180,29 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
       const int64_t row = list[t];
       int64_t s, e;
       // rows grouped by output slice: group (row, slice) is row `row * slices + slice` of the map
-      rm.range(row_mul > 1 ? row * row_mul + blockIdx.x : row, s, e);
+      rm.range(SLICED ? row * row_mul + blockIdx.x : row, s, e);
       float v = HAS_X ? __ldg(x + b * n_pre + row) : 1.0f;
       if (!HETERO) v = __fmul_rn(v, w0);
+      if (SLICED) {
+        // the group is laid out in 32-entry stretches whose entries fall into distinct banks:
+        // one coalesced 4-byte load per lane and stretch, all issued before the first add
+        for (int64_t p0 = s + lane; p0 < e; p0 += 32 * kSsDeal) {
+          int32_t j[kSsDeal];
+          float t[kSsDeal];
+#pragma unroll
+          for (int u = 0; u < kSsDeal; ++u) {
+            const bool in = p0 + 32 * u < e;
+            j[u] = in ? __ldg(idx + p0 + 32 * u) : -1;
+            t[u] = (HETERO && in) ? __ldg(w + p0 + 32 * u) : 0.0f;
+          }
+#pragma unroll
+          for (int u = 0; u < kSsDeal; ++u) {
+            const uint32_t cc = (uint32_t)(j[u] - col0);
+            if (cc < ncol) smem_add(acc + cc, HETERO ? __fmul_rn(v, t[u]) : v);
+          }
+        }
+        continue;
+      }
       int64_t a0 = e, a1 = e;
       if (vec_ok) {
         a0 = (s + 3) & ~int64_t(3);
@@ -245,15 +266,33 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
   }
 }
 
-// Groups the entries of every row by output slice (slice = column / 32768), keeping
-// their order inside a group.  s_indptr[row * S + k] is where group k of the row starts;
-// the row keeps its place [start, end) in the arrays.  With s_indices == nullptr only the
-// offsets are written (for rows that are already grouped, e.g. sorted by column).
-// One warp per row.  Columns beyond the last slice are kept in the last group.
-__global__ void __launch_bounds__(256)
+// Groups the entries of every row by output slice (slice = column / 32768).
+// s_indptr[row * S + k] is where group k of the row starts; the row keeps its place
+// [start, end) in the arrays.  Inside a group the entries are laid out for the scatter
+// kernel, whose warps read 32 consecutive entries per instruction and add them to shared
+// memory: the group is sorted by shared-memory bank (column mod 32, original order kept
+// inside a bank) and dealt round-robin over its 32-entry stretches, so that the entries
+// of one stretch fall into distinct banks as far as the group allows.  Entry number k of
+// the bank-sorted group of n entries, J = ceil(n / 32) stretches, the last one holding
+// m = n - 32 (J - 1):  k < m J  ->  stretch k mod J, slot k div J;  otherwise, with
+// k' = k - m J:  stretch k' mod (J - 1), slot m + k' div (J - 1).
+// With s_indices == nullptr only the offsets are written (for rows that are already
+// grouped, e.g. sorted by column).  One warp per row.  Columns beyond the last slice
+// are kept in the last group.
+constexpr int kSliceWarps = 8;
+
+__device__ __forceinline__ uint32_t slice_key(int32_t col, int S) {
+  uint32_t sl = (uint32_t)col / (uint32_t)kSsSlice;
+  if (sl > (uint32_t)(S - 1)) sl = (uint32_t)(S - 1);
+  return sl * 32u + ((uint32_t)col & 31u);
+}
+
+__global__ void __launch_bounds__(kSliceWarps * 32)
 slice_rows_kernel(RowMap rm, const int32_t* __restrict__ idx, int64_t n_pre, int S, int64_t nnz,
                   int64_t* __restrict__ s_indptr, int32_t* __restrict__ s_indices, int32_t* __restrict__ s_perm) {
+  __shared__ int32_t hist_all[kSliceWarps][128];
   const int lane = threadIdx.x & 31;
+  int32_t* hist = hist_all[threadIdx.x >> 5];
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   const uint32_t lt = (1u << lane) - 1u;
@@ -261,43 +300,68 @@ slice_rows_kernel(RowMap rm, const int32_t* __restrict__ idx, int64_t n_pre, int
   for (int64_t row = warp; row < n_pre; row += nwarps) {
     int64_t s, e;
     rm.range(row, s, e);
-    int cnt[4] = {0, 0, 0, 0};
-    for (int64_t p = s + lane; p < e; p += 32) {
-      uint32_t sl = (uint32_t)__ldg(idx + p) / (uint32_t)kSsSlice;
-      if (sl > (uint32_t)(S - 1)) sl = (uint32_t)(S - 1);
+    // entries per (slice, bank)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) cnt[k] += (sl == (uint32_t)k);
-    }
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) cnt[k] += __shfl_xor_sync(0xffffffffu, cnt[k], o);
+    for (int k = 0; k < 4; ++k) hist[32 * k + lane] = 0;
+    __syncwarp();
+    for (int64_t p = s + lane; p < e; p += 32) atomicAdd(&hist[slice_key(__ldg(idx + p), S)], 1);
+    __syncwarp();
+    // group sizes and starts; hist becomes the running start of every bank inside its group
+    int n[4];
     int64_t base[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = hist[32 * k + lane];
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      n[k] = __shfl_sync(0xffffffffu, incl, 31);
+      hist[32 * k + lane] = incl - c;
+    }
     base[0] = s;
 #pragma unroll
-    for (int k = 1; k < 4; ++k) base[k] = base[k - 1] + cnt[k - 1];
+    for (int k = 1; k < 4; ++k) base[k] = base[k - 1] + n[k - 1];
     if (lane < S) s_indptr[row * S + lane] = lane == 0 ? base[0] : lane == 1 ? base[1] : lane == 2 ? base[2] : base[3];
+    __syncwarp();
     if (!s_indices) continue;
     for (int64_t p0 = s; p0 < e; p0 += 32) {
       const int64_t p = p0 + lane;
-      int32_t j = 0;
-      uint32_t sl = 0xffffffffu;
+      int32_t col = 0;
+      uint32_t key = 0xffffffffu;
       if (p < e) {
-        j = __ldg(idx + p);
-        sl = (uint32_t)j / (uint32_t)kSsSlice;
-        if (sl > (uint32_t)(S - 1)) sl = (uint32_t)(S - 1);
+        col = __ldg(idx + p);
+        key = slice_key(col, S);
       }
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint32_t m = __ballot_sync(0xffffffffu, sl == (uint32_t)k);
-        if (sl == (uint32_t)k) {
-          const int64_t pos = base[k] + __popc(m & lt);
-          s_indices[pos] = j;
-          s_perm[pos] = (int32_t)p;
+      const uint32_t same = __match_any_sync(0xffffffffu, key);
+      int k_sorted = 0;
+      if (p < e) k_sorted = hist[key] + __popc(same & lt);
+      __syncwarp();
+      if (p < e && (same & lt) == 0) hist[key] += __popc(same);    // the first lane of every key moves it on
+      __syncwarp();
+      if (p < e) {
+        const int sl = (int)(key >> 5);
+        const int ng = sl == 0 ? n[0] : sl == 1 ? n[1] : sl == 2 ? n[2] : n[3];
+        const int64_t gb = sl == 0 ? base[0] : sl == 1 ? base[1] : sl == 2 ? base[2] : base[3];
+        const int J = (ng + 31) >> 5;
+        const int m = ng - 32 * (J - 1);
+        int stretch, slot;
+        if (k_sorted < m * J) {
+          stretch = k_sorted % J;
+          slot = k_sorted / J;
+        } else {
+          const int k2 = k_sorted - m * J;
+          stretch = k2 % (J - 1);
+          slot = m + k2 / (J - 1);
         }
-        base[k] += __popc(m);
+        const int64_t pos = gb + 32 * stretch + slot;
+        s_indices[pos] = col;
+        s_perm[pos] = (int32_t)p;
       }
     }
+    __syncwarp();
   }
 }
 
@@ -322,13 +386,18 @@ int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, 
   const size_t smem = sizeof(float) * kSsSlice + sizeof(int32_t) * kSsList;
   const bool vec_ok = aligned16(conn->indices) && (!conn->hetero || aligned16(conn->weights));
   const RowMap rm = make_rowmap(conn);
-#define BSX_SS(H, X, F)                                                                                      \
-  do {                                                                                                       \
-    BSX_CUDA(cudaFuncSetAttribute(scatter_smem_kernel<H, X, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                  (int)smem));                                                               \
-    scatter_smem_kernel<H, X, F><<<grid, kSsThreads, smem, st>>>(rm, conn->indices, conn->weights, spikes, x, \
-                                                                 conn->n_pre, conn->n_post, out, accumulate, \
-                                                                 vec_ok, row_mul);                           \
+#define BSX_SS2(H, X, F, SL)                                                                                    \
+  do {                                                                                                          \
+    BSX_CUDA(cudaFuncSetAttribute(scatter_smem_kernel<H, X, F, SL>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                  (int)smem));                                                                  \
+    scatter_smem_kernel<H, X, F, SL><<<grid, kSsThreads, smem, st>>>(rm, conn->indices, conn->weights, spikes,  \
+                                                                     x, conn->n_pre, conn->n_post, out,         \
+                                                                     accumulate, vec_ok, row_mul);              \
+  } while (0)
+#define BSX_SS(H, X, F)                          \
+  do {                                           \
+    if (row_mul >= 1) BSX_SS2(H, X, F, true);    \
+    else BSX_SS2(H, X, F, false);                \
   } while (0)
 #define BSX_SS_F(H, X)                                           \
   do {                                                           \
@@ -343,6 +412,7 @@ int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, 
   }
 #undef BSX_SS_F
 #undef BSX_SS
+#undef BSX_SS2
   BSX_LAUNCH_CHECK("scatter_smem_kernel");
   return BSX_OK;
 }
@@ -367,10 +437,10 @@ int bsx_sliced_build(const bsx_conn_t* conn, int64_t* s_indptr, int32_t* s_indic
   if (conn->nnz >= (int64_t)INT32_MAX) return fail(BSX_ERR_UNSUPPORTED, "nnz must be below 2^31");
   const int sms = sm_count();
   if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
-  int64_t blocks = (conn->n_pre + 7) / 8;
+  int64_t blocks = (conn->n_pre + kSliceWarps - 1) / kSliceWarps;
   if (blocks < 1) blocks = 1;
   if (blocks > (int64_t)sms * 16) blocks = (int64_t)sms * 16;
-  slice_rows_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(make_rowmap(conn), conn->indices, conn->n_pre,
+  slice_rows_kernel<<<(unsigned)blocks, kSliceWarps * 32, 0, as_stream(stream)>>>(make_rowmap(conn), conn->indices, conn->n_pre,
                                                                      (int)S, conn->nnz, s_indptr, s_indices, s_perm);
   BSX_LAUNCH_CHECK("slice_rows_kernel");
   return BSX_OK;

@@ -112,6 +112,7 @@ class _SparseConn:
         self.data = data
         self._t_weights = None          # permuted copies for the transposed and the sliced layout,
         self._s_weights = None          # made on demand
+        self._ts_weights = None
 
     def with_data(self, data):
         """A view of the same connectivity with other weights
@@ -250,14 +251,45 @@ class _SparseConn:
         return s
 
     def _transposed_sliced_struct(self, weights: torch.Tensor):
-        """The transposed copy read as a sliced layout: its rows are sorted by source neuron, hence
-        already grouped, so only the group offsets are added."""
-        st = self._transposed_struct(weights)
-        if getattr(self, '_t_groups', None) is None:
-            self._t_groups = self._group_offsets(st, self.shape[1], regroup=False)[0]
-        st.indptr = self._t_groups.data_ptr()
-        st._keep = st._keep + (self._t_groups,)
-        return st
+        """``bsx_conn_t`` of the transposed copy regrouped by output slice (of the transposed
+        product, i.e. by presynaptic neuron).  Built once; its permutation is composed with the
+        transposed copy's, so the weights are gathered from the original array in one pass."""
+        t = self.transposed()
+        n_pre, n_post = self.shape
+        if self._t_groups is None:
+            b = BsxConn()
+            b.n_pre, b.n_post = t.n_rows, t.n_cols
+            b.conn_num, b.nnz = 0, self.nnz
+            b.indices = t.indices.data_ptr() if self.nnz else None
+            b.indptr, b.indptr_is_64 = t.indptr.data_ptr(), 1
+            b.hetero, b.weights = 0, self.data.data_ptr()
+            s_indptr, s_indices, s_perm = self._group_offsets(b, t.n_rows, regroup=True)
+            comp = t.perm[s_perm.long()].contiguous() if self.nnz else s_perm
+            self._t_groups = (s_indptr, s_indices, comp)
+        s_indptr, s_indices, comp = self._t_groups
+        if self.hetero:
+            wsrc = weights.contiguous()
+            key = (wsrc.data_ptr(), wsrc._version, wsrc.numel())
+            cached = getattr(self, '_ts_weights', None)
+            if cached is not None and cached[0] == key:
+                wt = cached[1]
+            else:
+                wt = torch.empty(self.nnz, dtype=torch.float32, device=weights.device)
+                check(lib().bsx_permute_f32(ptr(wsrc), ptr(comp), self.nnz, ptr(wt), _lib.current_stream()))
+                self._ts_weights = (key, wt, wsrc)
+        else:
+            wt = weights.contiguous()
+        s = BsxConn()
+        s.n_pre, s.n_post = t.n_rows, t.n_cols
+        s.conn_num = 0
+        s.nnz = self.nnz
+        s.indices = s_indices.data_ptr() if self.nnz else None
+        s.indptr = s_indptr.data_ptr()
+        s.indptr_is_64 = 1
+        s.hetero = int(self.hetero)
+        s.weights = wt.data_ptr()
+        s._keep = (wt, s_indptr, s_indices)
+        return s
 
     # -- products ------------------------------------------------------------------
     def _vecmat(self, x, event: bool, method: str = 'scatter'):

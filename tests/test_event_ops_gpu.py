@@ -566,29 +566,45 @@ def test_shared_memory_scatter_lists_many_presynaptic_rows(rate, bsx, cuda):
 @pytest.mark.parametrize('n_post', [1000, 32768, 40001, 70003, 131072])
 @pytest.mark.parametrize('layout', ['fixed', 'csr'])
 def test_rows_grouped_by_output_slice(n_post, layout, bsx, cuda):
-    """``bsx_sliced_build``: every row's entries stably partitioned by ``column // 32768``;
-    offsets, regrouped targets and the permutation bit for bit against NumPy."""
+    """``bsx_sliced_build``: every row's entries grouped by ``column // 32768``; inside a group
+    sorted by shared-memory bank (``column % 32``, stable) and dealt round-robin over the group's
+    32-entry stretches.  Offsets, regrouped targets and the permutation bit for bit against NumPy."""
     from brainstate_b200 import _lib
-    n_pre, K = 333, 57
+    n_pre, K = 333, 157
     conn, idx, indptr, w = make(n_pre, n_post, K, 51, True, cuda, 0.7 if layout == 'csr' else None)
     S = int(bsx.bsx_sliced_slices(n_post))
     assert S == (n_post + 32767) // 32768
     flat = idx.reshape(-1)
     ip = indptr if indptr is not None else np.arange(n_pre + 1, dtype=np.int64) * K
     ref_ptr = np.empty(n_pre * S + 1, dtype=np.int64)
-    ref_idx, ref_perm = np.empty_like(flat), np.empty(flat.size, dtype=np.int32)
+    ref_idx, ref_perm = np.full_like(flat, -7), np.full(flat.size, -7, dtype=np.int32)
     for i in range(n_pre):
         s, e = int(ip[i]), int(ip[i + 1])
         sl = flat[s:e] // 32768
-        order = np.argsort(sl, kind='stable')
-        ref_idx[s:e] = flat[s:e][order]
-        ref_perm[s:e] = s + order
-        ref_ptr[i * S:(i + 1) * S] = s + np.concatenate(([0], np.cumsum(np.bincount(sl, minlength=S))[:-1]))
+        start = s
+        for k in range(S):
+            ref_ptr[i * S + k] = start
+            members = np.nonzero(sl == k)[0]                       # original order
+            n = members.size
+            by_bank = members[np.argsort(flat[s:e][members] % 32, kind='stable')]
+            J = (n + 31) // 32
+            m = n - 32 * (J - 1)
+            for ks, src in enumerate(by_bank):
+                if ks < m * J:
+                    stretch, slot = ks % J, ks // J
+                else:
+                    k2 = ks - m * J
+                    stretch, slot = k2 % (J - 1), m + k2 // (J - 1)
+                ref_idx[start + 32 * stretch + slot] = flat[s + src]
+                ref_perm[start + 32 * stretch + slot] = s + src
+            start += n
     ref_ptr[-1] = flat.size
+    assert (ref_perm >= 0).all()                                   # the dealing is a bijection
     s_indptr, s_indices, s_perm = conn._group_offsets(conn._struct(), n_pre, regroup=True)
     assert np.array_equal(s_indptr.cpu().numpy(), ref_ptr)
     assert np.array_equal(s_indices.cpu().numpy(), ref_idx)
     assert np.array_equal(s_perm.cpu().numpy(), ref_perm)
+    # full stretches of a group hold one entry per bank unless a bank has more entries than stretches
     only_ptr = conn._group_offsets(conn._struct(), n_pre, regroup=False)[0]
     assert torch.equal(only_ptr, s_indptr)
     st = conn._struct()
