@@ -195,15 +195,19 @@ int bsx_event_vecmat_variant(const bsx_conn_t* conn, int spike_format, int64_t b
 /*
  * Sliced layout for the shared-memory variant.  No counterpart in the reference: a
  * derived copy, like the transposed one.  The entries of every row are grouped by
- * output slice (slice = column / 32768, original order kept inside a group), so that
- * the block that owns a slice reads only its own entries instead of the whole row:
+ * output slice (slice = column / 32768), so that the block that owns a slice reads
+ * only its own entries instead of the whole row; inside a group they are sorted by
+ * column mod 32 (original order kept among equals) and dealt round-robin over the
+ * group's 32-entry stretches, so that the 32 entries a warp adds to shared memory
+ * in one instruction fall into distinct banks as far as the group allows:
  *   s_indptr  (n_pre*S+1) int64   start of group (row, slice) = entry row*S + slice;
  *                                 S = bsx_sliced_slices(n_post), at most 4
  *   s_indices (nnz)       int32   the targets, regrouped
  *   s_perm    (nnz)       int32   position of each entry in the original arrays
  *                                 (weights of the copy = bsx_permute_f32(w, s_perm))
- * With s_indices = s_perm = NULL only s_indptr is written: for rows that are already
- * grouped (sorted targets, as in the transposed copy) the original arrays serve.
+ * With s_indices = s_perm = NULL only s_indptr is written (rows that are already
+ * grouped, e.g. sorted targets, can then be scattered from the original arrays; they
+ * give the right sums but not the bank-friendly order).
  * bsx_event_vecmat_sliced takes a bsx_conn_t whose indptr is s_indptr (64-bit), whose
  * indices/weights are the regrouped arrays and whose n_pre, n_post, nnz, hetero are
  * those of the original, and computes what bsx_event_vecmat computes, in one launch

@@ -545,8 +545,8 @@ def test_host_buffer_pipeline_event_driven_reverse(cuda):
 
 @pytest.mark.parametrize('rate', [0.0, 0.02, 0.5, 1.0])
 def test_shared_memory_scatter_lists_many_presynaptic_rows(rate, bsx, cuda):
-    """More presynaptic neurons than one round of the in-block row list holds (8192): sparse
-    vectors take one round over the whole vector, dense ones fall back to 8192-neuron spans.
+    """More presynaptic neurons than one round of the in-block row list holds (2048): sparse
+    vectors take one round over the whole vector, dense ones fall back to 2048-neuron spans.
     Odd sizes put the byte, float and word scans on unaligned starts."""
     from brainstate_b200 import _lib
     from brainstate_b200.event import pack_spikes
