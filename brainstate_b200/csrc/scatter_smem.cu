@@ -4,7 +4,7 @@
 // thread block owns a slice of up to 32 768 columns of ONE batch row's output and keeps
 // it in shared memory (128 KB).  The block lists the active presynaptic rows of its
 // spike vector (count, block-wide scan, write: one round when they fit the 2048-entry
-// list, rounds over 2048-neuron spans otherwise) and fetches all their ranges at once, then its warps take rows from the list
+// list, rounds over spans sized to the density otherwise) and fetches all their ranges at once, then its warps take rows from the list
 // one at a time, issue all 128-bit index and weight loads of a 384-entry stretch before
 // touching any of them, and add the entries that fall into the slice with shared-memory
 // atomics — about four times the rate of red.global.add.f32.  The slice is written to
@@ -119,14 +119,14 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
     uint32_t rw[16];
     bool in_regs = false;
     int c;
-    if (FORMAT == BSX_SPK_BOOL8 && per == 64 && i0 + 64 <= hi &&
+    if (FORMAT == BSX_SPK_BOOL8 && (per == 64 || per == 32) && i0 + per <= hi &&
         ((reinterpret_cast<uintptr_t>(static_cast<const uint8_t*>(spikes) + b * n_pre + i0) & 15) == 0)) {
       in_regs = true;
       const uint4* __restrict__ sp4 = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(spikes) + b * n_pre + i0);
       c = 0;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const uint4 t = __ldg(sp4 + k);
+        const uint4 t = (16 * k < per) ? __ldg(sp4 + k) : make_uint4(0u, 0u, 0u, 0u);
         rw[4 * k + 0] = __vcmpne4(t.x, 0u) & 0x01010101u;
         rw[4 * k + 1] = __vcmpne4(t.y, 0u) & 0x01010101u;
         rw[4 * k + 2] = __vcmpne4(t.z, 0u) & 0x01010101u;
@@ -152,8 +152,12 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
       if (k < wid) base += t;
       total += t;
     }
-    if (total > kSsList) {   // only with span > kSsList: spans of kSsList neurons always fit
-      span = kSsList;
+    if (total > kSsList) {
+      // too many for the list (only with span > kSsList: a span of kSsList neurons always fits).
+      // Take spans that would hold about 0.9 lists at this density, halve on a further miss.
+      int64_t next = ((hi - lo) * (kSsList - kSsList / 10) / total) & ~int64_t(1023);
+      if (next > span / 2) next = (span / 2) & ~int64_t(1023);
+      span = next < kSsList ? kSsList : next;
       __syncthreads();
       continue;
     }
