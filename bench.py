@@ -134,7 +134,7 @@ def cpu_pass(co, idx, w, spk_sample):
     co.event_matvec_u8(spk_sample, idx, w, n)
 
 
-def cpu_baseline(idx, w, spk, budget_s=12.0, sample_vectors=8):
+def cpu_baseline(idx, w, spk, sample_s=12.0, sample_vectors=8):
     from oracle import c_oracle as co
     co.build()
     co.use_all_cores()
@@ -147,7 +147,7 @@ def cpu_baseline(idx, w, spk, budget_s=12.0, sample_vectors=8):
         cpu_pass(co, idx, w, sample)
         passes += 1
         el = time.perf_counter() - t0
-        if el >= budget_s and passes >= 2:
+        if el >= sample_s and passes >= 2:
             break
     return {'value': events * passes / el, 'unit': 'synaptic events/s', 'cores': co.num_threads(),
             'kind': 'port',
