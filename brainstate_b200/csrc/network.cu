@@ -395,6 +395,107 @@ net_run_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict__ raster
   }
 }
 
+// ---- the same, with the neuron state resident in shared memory --------------------
+// 148 SMs hold 33 MB of shared memory: up to about two million neurons can keep V, g_e,
+// g_i (float32) and the refractory count (int16) on chip for the whole run, one 1024-thread
+// block per SM owning a contiguous range of spike words.  Per step a neuron then costs one
+// read of its two synaptic increments from L2 (and a store where they were not zero)
+// instead of a read and a write of its whole state; all increments of a warp's words are
+// requested before the first is used.  The increments stay in global memory because
+// every SM scatters into them.  Arithmetic, spike words, lists and raster are those of
+// net_run_kernel; the state is read from global memory at the start and written back at
+// the end of the launch.
+constexpr int kResThreads = 1024;
+constexpr int kResWarps = kResThreads / 32;
+constexpr int kResWordsPerWarp = 8;                       // words a warp has in flight at once
+constexpr int kResMaxWords = 448;                         // words (of 32 neurons) per block: 196 KB of state
+constexpr int kResBytesPerNeuron = 3 * sizeof(float) + sizeof(int16_t);
+
+__global__ void __launch_bounds__(kResThreads, 1)
+net_run_resident_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict__ raster,
+                        int32_t* __restrict__ spike_counts, int words_per_block) {
+  cg::grid_group grid = cg::this_grid();
+  extern __shared__ __align__(16) unsigned char res_raw[];
+  const int cap = words_per_block * 32;
+  float* sV = reinterpret_cast<float*>(res_raw);
+  float* sge = sV + cap;
+  float* sgi = sge + cap;
+  int16_t* sref = reinterpret_cast<int16_t*>(sgi + cap);
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t words = (a.n_local + 31) >> 5;
+  const int64_t word0 = (int64_t)blockIdx.x * words_per_block;
+  int64_t my_words = words - word0;
+  if (my_words > words_per_block) my_words = words_per_block;
+  if (my_words < 0) my_words = 0;
+  const int64_t n0 = word0 * 32;
+  for (int64_t li = tid; li < my_words * 32; li += kResThreads) {
+    const int64_t i = n0 + li;
+    const bool valid = i < a.n_local;
+    sV[li] = valid ? a.V[i] : 0.0f;
+    sge[li] = valid ? a.g_e[i] : 0.0f;
+    sgi[li] = valid ? a.g_i[i] : 0.0f;
+    sref[li] = valid ? (int16_t)a.ref[i] : (int16_t)0;
+  }
+  __syncthreads();
+  for (int t = 0; t < steps; ++t) {
+    const int64_t step = step0 + t;
+    int32_t* lnext = a.slot(step);   // not among the slots read this step: ring >= max delay + 2
+    if (warp == 0 && lane == 0) lnext[0] = 0;
+    phase_scatter(a, step, warp, nwarps, lane);
+    grid.sync();
+    for (int64_t wl0 = wid; wl0 < my_words; wl0 += kResWarps * kResWordsPerWarp) {
+      float de[kResWordsPerWarp], di[kResWordsPerWarp];
+#pragma unroll
+      for (int k = 0; k < kResWordsPerWarp; ++k) {
+        const int64_t wl = wl0 + (int64_t)k * kResWarps;
+        const int64_t i = n0 + wl * 32 + lane;
+        const bool valid = wl < my_words && i < a.n_local;
+        de[k] = valid ? a.delta_e[i] : 0.0f;
+        di[k] = valid ? a.delta_i[i] : 0.0f;
+      }
+#pragma unroll
+      for (int k = 0; k < kResWordsPerWarp; ++k) {
+        const int64_t wl = wl0 + (int64_t)k * kResWarps;
+        if (wl >= my_words) break;                       // uniform across the warp
+        const int64_t li = wl * 32 + lane;
+        const int64_t i = n0 + li;
+        bool spk = false;
+        if (i < a.n_local) {
+          const int32_t r = sref[li];
+          const NeuronOut o = neuron_math(a.p, de[k], di[k], sge[li], sgi[li], sV[li], r, (uint32_t)(a.first + i), step);
+          if (de[k] != 0.0f) a.delta_e[i] = 0.0f;
+          if (di[k] != 0.0f) a.delta_i[i] = 0.0f;
+          sge[li] = o.ge;
+          sgi[li] = o.gi;
+          sV[li] = o.V;
+          if (o.r != r) sref[li] = (int16_t)o.r;
+          spk = o.spk;
+        }
+        const uint32_t m = __ballot_sync(0xffffffffu, spk);
+        const int64_t wd = word0 + wl;
+        if (lane == 0) {
+          a.bits[wd] = m;
+          if (raster) raster[(int64_t)t * words + wd] = m;
+        }
+        append_spikes(m, spk, lane, i, lnext);
+      }
+    }
+    grid.sync();
+    if (spike_counts && warp == 0 && lane == 0) spike_counts[t] = lnext[0];
+  }
+  for (int64_t li = tid; li < my_words * 32; li += kResThreads) {
+    const int64_t i = n0 + li;
+    if (i < a.n_local) {
+      a.V[i] = sV[li];
+      a.g_e[i] = sge[li];
+      a.g_i[i] = sgi[li];
+      a.ref[i] = sref[li];
+    }
+  }
+}
+
 // ---- split phases (multi-GPU driver) ----------------------------------------------
 __global__ void __launch_bounds__(256) net_scatter_kernel(NetDev a, int64_t step) {
   const int lane = threadIdx.x & 31;
@@ -669,6 +770,22 @@ int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t st
     BSX_LAUNCH_CHECK("net_run_small_kernel");
     return BSX_OK;
   }
+  int steps_i = steps;
+  int64_t step0_i = step0;
+  // the neuron state fits the shared memory of the SMs: one resident block per SM
+  const int64_t words = (net->n_local + 31) / 32;
+  if (blocks == 0 && params->ref_steps < 32768 && words <= (int64_t)sms * kResMaxWords) {
+    int64_t wpb = (words + sms - 1) / sms;
+    if (wpb < kResWarps) wpb = kResWarps;                  // at least one word per warp
+    const int64_t grid_blocks = (words + wpb - 1) / wpb;
+    int wpb_i = (int)wpb;
+    const size_t smem = (size_t)wpb * 32 * kResBytesPerNeuron;
+    BSX_CUDA(cudaFuncSetAttribute(net_run_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    void* rargs[] = {&a, &steps_i, &step0_i, &raster, &spike_counts, &wpb_i};
+    BSX_CUDA(cudaLaunchCooperativeKernel((const void*)net_run_resident_kernel, dim3((unsigned)grid_blocks),
+                                         dim3(kResThreads), rargs, smem, as_stream(stream)));
+    return BSX_OK;
+  }
   int per_sm = 0;
   BSX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, net_run_kernel, 256, 0));
   if (per_sm < 1) return fail(BSX_ERR_CUDA, "the network kernel does not fit on an SM");
@@ -676,8 +793,6 @@ int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t st
   int64_t want = blocks > 0 ? blocks : (net->n_local + 255) / 256;
   if (want < 1) want = 1;
   if (want > max_blocks) want = max_blocks;
-  int steps_i = steps;
-  int64_t step0_i = step0;
   void* args[] = {&a, &steps_i, &step0_i, &raster, &spike_counts};
   BSX_CUDA(cudaLaunchCooperativeKernel((const void*)net_run_kernel, dim3((unsigned)want), dim3(256), args, 0,
                                        as_stream(stream)));

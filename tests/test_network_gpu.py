@@ -277,3 +277,31 @@ def test_long_csr_rows_in_the_network_step(cuda):
     assert torch.equal(ra, rb) and torch.equal(ra, rc)
     from brainstate_b200.sim import unpack_raster
     assert np.array_equal(unpack_raster(ra, 512), orc.run(steps))
+
+
+@pytest.mark.parametrize('coba', [False, True])
+def test_state_resident_in_shared_memory_equals_oracle_and_global_state_kernel(coba, cuda):
+    """Networks beyond one SM run with V, g_e, g_i and the refractory count resident in the shared
+    memory of all SMs (default) — same raster as the oracle and as the kernel that keeps the state
+    in global memory (explicit grid size), also when the run is cut into launches, with delays and
+    with the background drive.  20 011 neurons: the last spike word is partial."""
+    from brainstate_b200.sim import unpack_raster
+    n_exc, n_inh, K = 16009, 4002, 40
+    w_e, w_i = (0.6, 6.7) if coba else (1.62, -9.0)
+    kw = dict(delay_e=2, delay_i=0, ext=(300.0, 0.5 if coba else 1.0, 7))
+    a, orc = build(n_exc, n_inh, K, coba, cuda, w_e, w_i, **kw)
+    b, _ = build(n_exc, n_inh, K, coba, cuda, w_e, w_i, **kw)
+    c, _ = build(n_exc, n_inh, K, coba, cuda, w_e, w_i, **kw)
+    steps = 160
+    r_res, counts = a.run(steps)                                   # resident state
+    r_glob, _ = b.run(steps, blocks=120)                           # state in global memory
+    r_cut = torch.cat([c.run(k)[0] for k in (1, 59, 100)])         # state written back and reloaded
+    ref = orc.run(steps)
+    assert ref.sum() > 500
+    assert np.array_equal(counts.cpu().numpy(), ref.sum(axis=1))
+    assert np.array_equal(unpack_raster(r_res, n_exc + n_inh), ref)
+    assert torch.equal(r_res, r_glob) and torch.equal(r_res, r_cut)
+    for x, y in ((a.V, b.V), (a.g_e, b.g_e), (a.g_i, b.g_i), (a.ref, b.ref), (a.V, c.V), (a.ref, c.ref)):
+        assert torch.equal(x, y)
+    np.testing.assert_allclose(a.V.cpu().numpy(), orc.V, rtol=1e-5, atol=1e-6)
+    assert np.array_equal(a.ref.cpu().numpy(), orc.ref)
