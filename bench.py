@@ -302,6 +302,11 @@ def run_ours(args):
 
     # ---- device-resident timing -------------------------------------------------
     # at least 3 warm-up steps, and enough of them for the SM clock to leave idle
+    # nvidia-smi delivers a sample every 100 ms and the timed region may be a few milliseconds long, so
+    # the sampler starts before the warm-up (the same kernels, back to back) and runs through the timed region
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     t_w, n_w = time.perf_counter(), 0
     while n_w < (args.warmup if args.profile else max(args.warmup, 3)) or (not args.profile and time.perf_counter() - t_w < 0.5):
         dp.run(spk_dev, stream)
@@ -309,9 +314,6 @@ def run_ours(args):
         if n_w % 8 == 0:
             torch.cuda.synchronize()
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     mv = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
@@ -606,7 +608,7 @@ def run_cases(torch, dev, dp, idx, w, peak):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--steps', type=int, default=200)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--vectors', type=int, default=296,
