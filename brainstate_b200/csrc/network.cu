@@ -405,22 +405,35 @@ net_run_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict__ raster
 // every SM scatters into them.  Arithmetic, spike words, lists and raster are those of
 // net_run_kernel; the state is read from global memory at the start and written back at
 // the end of the launch.
+//
+// ONE_BARRIER (projections without delay): a block scatters the spikes of its own neurons
+// right after it has updated them, so nothing waits for the complete spike list and a step
+// needs one grid-wide barrier instead of two.  A fast block must not add step t+1's
+// increments to a neuron whose owner has not consumed step t's yet, so the increments are
+// double-buffered by step parity; the second pair of buffers are the V and g_e arrays in
+// global memory, which nobody reads while the state is on chip (they are cleared at the
+// start and rewritten with the state at the end).  The spikes of the step before the launch
+// come from their list, as in every other kernel, and the last step of a launch leaves its
+// spikes to the list, so launches can be chained and mixed with the other kernels.
 constexpr int kResThreads = 1024;
 constexpr int kResWarps = kResThreads / 32;
 constexpr int kResWordsPerWarp = 8;                       // words a warp has in flight at once
-constexpr int kResMaxWords = 448;                         // words (of 32 neurons) per block: 196 KB of state
-constexpr int kResBytesPerNeuron = 3 * sizeof(float) + sizeof(int16_t);
+constexpr int kResMaxWords = 432;                         // words (of 32 neurons) per block: 216 KB
+constexpr int kResBytesPerNeuron = 3 * sizeof(float) + 2 * sizeof(int16_t);   // state + own-spike list
 
+template <bool ONE_BARRIER>
 __global__ void __launch_bounds__(kResThreads, 1)
 net_run_resident_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict__ raster,
                         int32_t* __restrict__ spike_counts, int words_per_block) {
   cg::grid_group grid = cg::this_grid();
   extern __shared__ __align__(16) unsigned char res_raw[];
+  __shared__ int s_spikes;
   const int cap = words_per_block * 32;
   float* sV = reinterpret_cast<float*>(res_raw);
   float* sge = sV + cap;
   float* sgi = sge + cap;
   int16_t* sref = reinterpret_cast<int16_t*>(sgi + cap);
+  uint16_t* smine = reinterpret_cast<uint16_t*>(sref + cap);      // neurons of this block that spiked this step
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -439,12 +452,39 @@ net_run_resident_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict
     sref[li] = valid ? (int16_t)a.ref[i] : (int16_t)0;
   }
   __syncthreads();
+  if (ONE_BARRIER) {
+    // every block reads only its own part of V and g_e, so they can be cleared right away
+    for (int64_t li = tid; li < my_words * 32; li += kResThreads) {
+      const int64_t i = n0 + li;
+      if (i < a.n_local) {
+        a.V[i] = 0.0f;
+        a.g_e[i] = 0.0f;
+      }
+    }
+    if (warp == 0 && lane == 0) a.slot(step0)[0] = 0;
+    phase_scatter(a, step0, warp, nwarps, lane);          // the spikes of step0 - 1, from their list
+    grid.sync();
+  }
+  const int cpr = a.exc.cpr > a.inh.cpr ? a.exc.cpr : a.inh.cpr;
   for (int t = 0; t < steps; ++t) {
     const int64_t step = step0 + t;
     int32_t* lnext = a.slot(step);   // not among the slots read this step: ring >= max delay + 2
-    if (warp == 0 && lane == 0) lnext[0] = 0;
-    phase_scatter(a, step, warp, nwarps, lane);
-    grid.sync();
+    if (!ONE_BARRIER) {
+      if (warp == 0 && lane == 0) lnext[0] = 0;
+      phase_scatter(a, step, warp, nwarps, lane);
+      grid.sync();
+    }
+    const bool odd = ONE_BARRIER && (t & 1);
+    float* __restrict__ de_cur = odd ? a.V : a.delta_e;
+    float* __restrict__ di_cur = odd ? a.g_e : a.delta_i;
+    float* __restrict__ de_nxt = odd ? a.delta_e : a.V;
+    float* __restrict__ di_nxt = odd ? a.delta_i : a.g_e;
+    const bool pass_on = ONE_BARRIER && t + 1 < steps;     // the last step leaves its spikes to the list
+    if (ONE_BARRIER) {
+      if (tid == 0) s_spikes = 0;
+      if (pass_on && warp == 0 && lane == 0) a.slot(step + 1)[0] = 0;   // no list is read in this mode
+      __syncthreads();
+    }
     for (int64_t wl0 = wid; wl0 < my_words; wl0 += kResWarps * kResWordsPerWarp) {
       float de[kResWordsPerWarp], di[kResWordsPerWarp];
 #pragma unroll
@@ -452,8 +492,8 @@ net_run_resident_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict
         const int64_t wl = wl0 + (int64_t)k * kResWarps;
         const int64_t i = n0 + wl * 32 + lane;
         const bool valid = wl < my_words && i < a.n_local;
-        de[k] = valid ? a.delta_e[i] : 0.0f;
-        di[k] = valid ? a.delta_i[i] : 0.0f;
+        de[k] = valid ? de_cur[i] : 0.0f;
+        di[k] = valid ? di_cur[i] : 0.0f;
       }
 #pragma unroll
       for (int k = 0; k < kResWordsPerWarp; ++k) {
@@ -465,8 +505,8 @@ net_run_resident_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict
         if (i < a.n_local) {
           const int32_t r = sref[li];
           const NeuronOut o = neuron_math(a.p, de[k], di[k], sge[li], sgi[li], sV[li], r, (uint32_t)(a.first + i), step);
-          if (de[k] != 0.0f) a.delta_e[i] = 0.0f;
-          if (di[k] != 0.0f) a.delta_i[i] = 0.0f;
+          if (de[k] != 0.0f) de_cur[i] = 0.0f;
+          if (di[k] != 0.0f) di_cur[i] = 0.0f;
           sge[li] = o.ge;
           sgi[li] = o.gi;
           sV[li] = o.V;
@@ -480,6 +520,25 @@ net_run_resident_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict
           if (raster) raster[(int64_t)t * words + wd] = m;
         }
         append_spikes(m, spk, lane, i, lnext);
+        if (pass_on && m) {
+          int base = 0;
+          if (lane == 0) base = atomicAdd(&s_spikes, __popc(m));
+          base = __shfl_sync(0xffffffffu, base, 0);
+          if (spk) smine[base + __popc(m & ((1u << lane) - 1u))] = (uint16_t)li;
+        }
+      }
+    }
+    if (pass_on) {
+      __syncthreads();
+      const int items = s_spikes * cpr;
+      for (int it = wid; it < items; it += kResWarps) {
+        const int q = it / cpr, c = it - q * cpr;
+        const int64_t id = a.first + n0 + smine[q];
+        if (id < a.n_exc) {
+          if (c < a.exc.cpr) scatter_one(a.exc, id, c, a.chunk, lane, de_nxt);
+        } else {
+          if (c < a.inh.cpr) scatter_one(a.inh, id - a.n_exc, c, a.chunk, lane, di_nxt);
+        }
       }
     }
     grid.sync();
@@ -780,10 +839,12 @@ int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t st
     const int64_t grid_blocks = (words + wpb - 1) / wpb;
     int wpb_i = (int)wpb;
     const size_t smem = (size_t)wpb * 32 * kResBytesPerNeuron;
-    BSX_CUDA(cudaFuncSetAttribute(net_run_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const bool one_barrier = a.delay_e == 0 && a.delay_i == 0;
+    const void* fn = one_barrier ? (const void*)net_run_resident_kernel<true> : (const void*)net_run_resident_kernel<false>;
+    BSX_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     void* rargs[] = {&a, &steps_i, &step0_i, &raster, &spike_counts, &wpb_i};
-    BSX_CUDA(cudaLaunchCooperativeKernel((const void*)net_run_resident_kernel, dim3((unsigned)grid_blocks),
-                                         dim3(kResThreads), rargs, smem, as_stream(stream)));
+    BSX_CUDA(cudaLaunchCooperativeKernel(fn, dim3((unsigned)grid_blocks), dim3(kResThreads), rargs, smem,
+                                         as_stream(stream)));
     return BSX_OK;
   }
   int per_sm = 0;
