@@ -360,6 +360,7 @@ net_run_small_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict__ 
 }
 
 // ---- one cooperative launch for many steps (single GPU) ------------------------
+constexpr int kRunWords = 4;
 __global__ void __launch_bounds__(256)
 net_run_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict__ raster,
                int32_t* __restrict__ spike_counts) {
@@ -374,21 +375,27 @@ net_run_kernel(NetDev a, int steps, int64_t step0, uint32_t* __restrict__ raster
     if (warp == 0 && lane == 0) lnext[0] = 0;
     phase_scatter(a, step, warp, nwarps, lane);
     grid.sync();
-    for (int64_t wd = warp; wd < words; wd += 2 * nwarps) {
-      const int64_t wd1 = wd + nwarps < words ? wd + nwarps : -1;
-      bool spk0, spk1;
-      uint32_t m0, m1;
-      update_two_words(a, wd, wd1, lane, step, &m0, &m1, &spk0, &spk1);
-      if (lane == 0) {
-        a.bits[wd] = m0;
-        if (raster) raster[(int64_t)t * words + wd] = m0;
-        if (wd1 >= 0) {
-          a.bits[wd1] = m1;
-          if (raster) raster[(int64_t)t * words + wd1] = m1;
-        }
+    // four words per warp and round trip: networks too large for the resident kernel are bound
+    // by the latency of the state loads, not by their bandwidth
+    for (int64_t wd0 = warp; wd0 < words; wd0 += kRunWords * nwarps) {
+      NeuronIn in[kRunWords];
+#pragma unroll
+      for (int k = 0; k < kRunWords; ++k) {
+        const int64_t wd = wd0 + k * nwarps;
+        in[k] = load_neuron(a, wd < words ? wd * 32 + lane : -1);
       }
-      append_spikes(m0, spk0, lane, wd * 32 + lane, lnext);
-      if (wd1 >= 0) append_spikes(m1, spk1, lane, wd1 * 32 + lane, lnext);
+#pragma unroll
+      for (int k = 0; k < kRunWords; ++k) {
+        const int64_t wd = wd0 + k * nwarps;
+        if (wd >= words) break;                          // uniform across the warp
+        const bool spk = step_neuron(a, wd * 32 + lane, step, in[k]);
+        const uint32_t m = __ballot_sync(0xffffffffu, spk);
+        if (lane == 0) {
+          a.bits[wd] = m;
+          if (raster) raster[(int64_t)t * words + wd] = m;
+        }
+        append_spikes(m, spk, lane, wd * 32 + lane, lnext);
+      }
     }
     grid.sync();
     if (spike_counts && warp == 0 && lane == 0) spike_counts[t] = lnext[0];
