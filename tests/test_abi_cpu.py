@@ -78,6 +78,15 @@ def test_argument_validation_needs_no_gpu(bsx):
     assert bsx.bsx_status_name(-3) == b'BSX_ERR_INDEX_RANGE'
     assert bsx.bsx_event_vecmat_workspace_bytes(2, 100) >= 16 + 800
     assert bsx.bsx_transpose_workspace_bytes(10, 10, 50) >= 4 * 11 + 4 * 50
+    # sliced layout: one slice per 32 768 columns; its entry points validate on the host too
+    assert [bsx.bsx_sliced_slices(n) for n in (0, 1, 32768, 32769, 65536, 131072, 131073)] == [0, 1, 1, 2, 2, 4, 5]
+    st.nnz = 8
+    assert bsx.bsx_sliced_build(C.byref(st), None, None, None, None) == BSX_ERR_INVALID_ARG
+    assert b's_indptr' in bsx.bsx_last_error_string()
+    assert bsx.bsx_event_vecmat_sliced(C.byref(st), None, 0, 1, None, 0, None) == BSX_ERR_INVALID_ARG
+    assert b'64-bit' in bsx.bsx_last_error_string()
+    assert bsx.bsx_event_vecmat_variant(C.byref(st), 9, 4) == BSX_ERR_INVALID_ARG
+    assert bsx.bsx_event_vecmat_variant(C.byref(st), 0, 4) in (0, 1)
 
 
 def test_no_cpu_fallback(bsx):
