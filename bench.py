@@ -18,11 +18,20 @@ ending with the results back in host memory.  Data are synthetic, generated from
 the seeds above; the matrix (343 MB) is larger than the 126 MB L2.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--vectors T] [--cases]
+                    [--vectors T] [--no-cases] [--no-network] [--no-large]
 
 With N > 1 (torchrun, one rank per GPU) every rank runs the same pass on its own
 T spike vectors against its own replica of the matrix: the batch of spike vectors
 is data-parallel, no collective is on the data path (weak scaling).
+
+Reported beside the headline, in the same JSON line (none of them part of ``value``):
+``cases`` — the microbenchmark grid (firing rates 0.1 / 1 / 10 %, homogeneous and
+heterogeneous weights, both products) with the HBM fraction of each; ``single_vector_us``
+— one spike vector per call, calls replayed back to back from a CUDA graph;
+``training_step`` — the batched event matmul with its reverse mode (64 x 65 536 spikes at
+2 %); ``network`` — the 10^6-neuron conductance-based network and ``network_large`` — the
+8 * 10^6-neuron / 8 * 10^9-synapse network, both postsynaptic-sharded over the N ranks,
+their per-step spike counts compared with the committed one-GPU record.
 """
 from __future__ import annotations
 
@@ -50,11 +59,14 @@ SEED_CONN, SEED_W, SEED_SPK = 200, 201, 211
 # workload
 # ----------------------------------------------------------------------------
 
-def build_workload(vectors, rank=0, rate=RATE, seed_spk=SEED_SPK):
-    from brainstate_b200.nn import fixed_num_indices
+def build_workload(vectors, rank=0, rate=RATE, seed_spk=SEED_SPK, use_numpy=False):
     n = N_NEURONS
     K = int(n * PROB)
-    idx = fixed_num_indices(SEED_CONN, n, n, K)
+    if use_numpy:       # the reference arm must not touch the product: NumPy's own generator call
+        idx = np.random.RandomState(SEED_CONN).randint(0, n, size=(n, K)).astype(np.int32)
+    else:
+        from brainstate_b200.nn import fixed_num_indices
+        idx = fixed_num_indices(SEED_CONN, n, n, K)
     w = np.random.RandomState(SEED_W).normal(0.1, 0.01, (n, K)).astype(np.float32)
     spk = np.random.RandomState(seed_spk + 1000 * rank).random_sample((vectors, n)) < rate
     return n, K, idx, w, spk
@@ -127,53 +139,79 @@ class ClockSampler:
 # CPU baseline (oracle port), bounded sample
 # ----------------------------------------------------------------------------
 
-def cpu_pass(co, idx, w, spk_sample):
-    """One pass of the same hot path on the host: both products for every sampled vector."""
-    n = idx.shape[0]
-    co.event_vecmat_u8(spk_sample, idx, w, n)
-    co.event_matvec_u8(spk_sample, idx, w, n)
+class CpuPath:
+    """The same hot path on the host cores (C/OpenMP restatement under oracle/): spike@W as
+    a scatter over the active rows, W@spike either as the row gather the reference's CPU
+    kernels do or as the event-driven scatter over a column-major copy (built once, like the
+    device's transposed copy) — whichever is faster on this host."""
+
+    def __init__(self, idx, w, probe):
+        from oracle import c_oracle as co
+        co.build()
+        self.co = co
+        self.cores = co.use_all_cores()
+        self.idx, self.w = idx, w
+        self.n = idx.shape[0]
+        t_indptr, t_rows, t_perm = co.transpose(idx, self.n, self.n)
+        self.t_indptr, self.t_rows = t_indptr, t_rows
+        self.t_w = np.ascontiguousarray(w.reshape(-1)[t_perm])
+        self.reverse = 'scatter over the column-major copy'
+        t0 = time.perf_counter(); self.matvec(probe); a = time.perf_counter() - t0
+        self.reverse = 'row gather'
+        t0 = time.perf_counter(); self.matvec(probe); b = time.perf_counter() - t0
+        if a < b:
+            self.reverse = 'scatter over the column-major copy'
+
+    def vecmat(self, spk):
+        return self.co.event_vecmat_u8(spk, self.idx, self.w, self.n)
+
+    def matvec(self, spk):
+        if self.reverse == 'row gather':
+            return self.co.event_matvec_u8(spk, self.idx, self.w, self.n)
+        return self.co.event_vecmat_u8(spk, self.t_rows, self.t_w, self.n, self.t_indptr)
+
+    def run(self, spk):
+        self.vecmat(spk)
+        self.matvec(spk)
 
 
-def cpu_baseline(idx, w, spk, sample_s=12.0, sample_vectors=8):
-    from oracle import c_oracle as co
-    co.build()
-    co.use_all_cores()
-    K = idx.shape[1]
+def cpu_baseline(idx, w, spk, sample_s=12.0, sample_vectors=32):
     sample = np.ascontiguousarray(spk[:sample_vectors]).astype(np.uint8)
+    cpu = CpuPath(idx, w, sample)
+    K = idx.shape[1]
     events = 2 * int(sample.sum()) * K
-    cpu_pass(co, idx, w, sample)                       # warm-up (page-in, thread start)
+    cpu.run(sample)                                    # warm-up (page-in, thread start)
     passes, t0 = 0, time.perf_counter()
     while True:
-        cpu_pass(co, idx, w, sample)
+        cpu.run(sample)
         passes += 1
         el = time.perf_counter() - t0
         if el >= sample_s and passes >= 2:
             break
-    return {'value': events * passes / el, 'unit': 'synaptic events/s', 'cores': co.num_threads(),
-            'kind': 'port',
-            'sample': f'{passes} passes over {sample.shape[0]} spike vectors (both products each), '
-                      f'{el:.1f} s, C/OpenMP restatement of the reference CPU path'}, events, passes, el
+    return {'value': events * passes / el, 'unit': 'synaptic events/s', 'cores': cpu.cores, 'kind': 'port',
+            'sample': f'{passes} passes over {sample.shape[0]} spike vectors (both products each), {el:.1f} s, '
+                      f'C/OpenMP restatement of the reference CPU path, W@spike as {cpu.reverse}'}
 
 
 def run_reference_arm(args):
     """``--impl reference``: the reference's CPU implementation of the path.  The
     reference's own kernels live in the un-vendored package brainevent, which is not
     installed and cannot be (no network), so the timed code is the C/OpenMP
-    restatement under oracle/ (kind "port"), on all host threads."""
+    restatement under oracle/ (kind "port"), on all host threads, on the same
+    workload: the same matrix (drawn here with NumPy, the reference's own call), the same
+    ``--vectors`` spike vectors per step, both products."""
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
         return 0
-    n, K, idx, w, spk = build_workload(max(args.vectors, 8))
-    from oracle import c_oracle as co
-    co.build()
-    co.use_all_cores()
-    sample = np.ascontiguousarray(spk[:8]).astype(np.uint8)
+    n, K, idx, w, spk = build_workload(args.vectors, use_numpy=True)
+    sample = np.ascontiguousarray(spk).astype(np.uint8)
+    cpu = CpuPath(idx, w, sample[:min(16, len(sample))])
     events = 2 * int(sample.sum()) * K
-    for _ in range(max(args.warmup, 1)):
-        cpu_pass(co, idx, w, sample)
+    for _ in range(max(min(args.warmup, 2), 1)):       # a pass takes about a second: two warm-up passes
+        cpu.run(sample)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_pass(co, idx, w, sample)
+        cpu.run(sample)
     el = time.perf_counter() - t0
     value = events * args.steps / el
     unit = 'synaptic events/s'
@@ -182,10 +220,11 @@ def run_reference_arm(args):
         'value': value, 'unit': unit, 'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup,
         'ms_per_step': 1e3 * el / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
         'dtype': 'f32', 'data': 'synthetic',
-        'config': workload_config(8, 'host memory (CPU run)'),
-        'cpu_baseline': {'value': value, 'unit': unit, 'cores': co.num_threads(), 'kind': 'port',
-                         'sample': '8 spike vectors per step, both products; brainevent (the reference\'s kernel '
-                                   'package) is not installable here, so the C/OpenMP restatement is timed'},
+        'config': workload_config(args.vectors, 'inputs larger than L2 (343 MB matrix vs 126 MB L2), no flush'),
+        'cpu_baseline': {'value': value, 'unit': unit, 'cores': cpu.cores, 'kind': 'port',
+                         'sample': f'the full step: {args.vectors} spike vectors, both products, W@spike as '
+                                   f'{cpu.reverse}; brainevent (the reference\'s kernel package) is not '
+                                   'installable here, so the C/OpenMP restatement is timed'},
         'e2e': {'value': value, 'unit': unit, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
     }
@@ -394,9 +433,23 @@ def run_ours(args):
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
     e2e_value = events_all * e2e_steps / float(t_e2e.item())
 
-    network = None
+    peak, peak_kind = measured_hbm_peak()
+    facts = {'passes': dp.passes, 'matvec_method': dp.matvec_method, 'scatter_variant': dp.scatter_variant,
+             'launches_per_pass': dp.launches_per_pass}
+    cases = single = training = None
+    if rank == 0 and not args.no_cases:
+        cases = run_cases(torch, dev, dp, peak)
+        single = run_single_vector(torch, dev, dp, peak)
+        training = run_training_step(torch, dev, dp, peak)
+    # the network legs build their own connectivity: release the microbenchmark's buffers first
+    idx_host, w_host = idx, w
+    del dp, pipe, layer, spk_dev, host_spk, host_y1, host_y2
+    torch.cuda.empty_cache()
+    network = network_large = None
     if not args.no_network:
-        network = run_network(torch, dist, dev, world, rank)
+        network = run_network(torch, dist, dev, world, rank, 'coba', steps=1000, warm=200)
+        if not args.no_large:
+            network_large = run_network(torch, dist, dev, world, rank, 'large', steps=500, warm=0)
 
     if rank != 0:
         if world > 1:
@@ -404,15 +457,14 @@ def run_ours(args):
         return 0
 
     # ---- roofline of the two kernels of a step; the dominant one is reported first --
-    peak, peak_kind = measured_hbm_peak()
     nnz = n * K
     events_vec = float(spk.sum()) * K                      # events of one product over the batch
     # gather: one launch = one pass over the indices for 16 vectors
-    g_bytes = nnz * 4 + (events_vec / dp.passes) * 4 + n * 2 + min(T, 16) * 4 * n
-    g_launch_s = (ms_gather * 1e-3) / dp.passes                  # includes the transpose-pack launch (~2 %)
+    g_bytes = nnz * 4 + (events_vec / facts['passes']) * 4 + n * 2 + min(T, 16) * 4 * n
+    g_launch_s = (ms_gather * 1e-3) / facts['passes']                  # includes the transpose-pack launch (~2 %)
     # scatter: one launch = all T vectors of one product
     s_bytes = events_vec * 8 + T * (n + 4 * n)
-    if dp.matvec_method == 'scatter':
+    if facts['matvec_method'] == 'scatter':
         s_launches, ms_scatter = 2 * args.steps, ms_total
     else:
         s_launches, ms_scatter = args.steps, ms_total - ms_matvec
@@ -422,10 +474,10 @@ def run_ours(args):
         a = nbytes / sec / 1e9
         return {'bound': 'hbm', 'kernel': kernel, 'achieved': a, 'peak': peak, 'peak_kind': peak_kind,
                 'unit': 'GB/s', 'frac': a / peak, 'bytes_per_launch': nbytes, 'avg_launch_us': sec * 1e6,
-                'share_of_step': share, 'traffic': None, 'note': note}
+                'share_of_step': share, 'traffic': None, 'frac_dram': None, 'note': note}
 
-    smem_variant = dp.scatter_variant == _lib.VECMAT_SHARED_SLICES
-    what = 'spike@W over the rows' + (' and W@spike over the transposed copy' if dp.matvec_method == 'scatter' else '')
+    smem_variant = facts['scatter_variant'] == _lib.VECMAT_SHARED_SLICES
+    what = 'spike@W over the rows' + (' and W@spike over the transposed copy' if facts['matvec_method'] == 'scatter' else '')
     if smem_variant:
         r_s = roof('scatter_smem_kernel<hetero>', s_bytes, s_launch_s, ms_scatter / ms_total,
                    what + '; one block per (spike vector, 32768-column slice of the output held in shared memory); '
@@ -436,7 +488,7 @@ def run_ours(args):
                    what + '; limited by the L2 rate of red.global.add.f32 (about 190 G adds/s in a stand-alone '
                    'probe), not by HBM')
     r_s['atomic_adds_per_s'] = events_vec / s_launch_s
-    if dp.matvec_method == 'scatter':
+    if facts['matvec_method'] == 'scatter':
         r_g = roof('event_matvec_b16_kernel<hetero>', g_bytes, g_launch_s, 0.0,
                    'the deterministic W@spike (16 vectors per pass over the indices), timed in its own loop after '
                    'the steps: at this firing rate the step uses the event-driven form, which is '
@@ -461,8 +513,11 @@ def run_ours(args):
                 r_s['traffic'] = float(tr['scatter_queue_kernel_per_16_vectors']) * T / 16  # grows with the events
         except Exception:
             pass
+    for r in (r_s, r_g):      # what actually crossed the HBM interface (ncu), as a fraction of the peak
+        if r['traffic']:
+            r['frac_dram'] = r['traffic'] / (r['avg_launch_us'] * 1e-6) / 1e9 / peak
 
-    cpu, _, _, _ = cpu_baseline(idx, w, spk)
+    cpu = cpu_baseline(idx_host, w_host, spk)
 
     line = {
         'metric': 'synaptic events/s (event matvec microbenchmark, both products)',
@@ -473,98 +528,145 @@ def run_ours(args):
         'clocks': clocks,
         'e2e': {'value': e2e_value, 'unit': 'synaptic events/s', 'h2d_bytes_per_step': int(spk.nbytes),
                 'd2h_bytes_per_step': int(2 * T * n * 4), 'steps': e2e_steps},
-        'gpu_launches': int(dp.launches_per_pass * args.steps),
+        'gpu_launches': int(facts['launches_per_pass'] * args.steps),
         'roofline': roofline,
         'roofline_other_kernel': roofline_2,
         'cpu_baseline': cpu,
         'events_per_step': events_all,
-        'variants': {'spike@W': 'scatter', 'scatter_kernel': 'shared-memory slices' if smem_variant else 'global atomics', 'W@spike': dp.matvec_method + (' over the transposed copy' if dp.matvec_method == 'scatter' else ''),
+        'variants': {'spike@W': 'scatter', 'scatter_kernel': 'shared-memory slices' if smem_variant else 'global atomics', 'W@spike': facts['matvec_method'] + (' over the transposed copy' if facts['matvec_method'] == 'scatter' else ''),
                      'chosen_for_rate': RATE},
+        'cases': cases,
+        'single_vector_us': single,
+        'training_step': training,
         'network': network,
+        'network_large': network_large,
     }
-    if args.cases:
-        line['cases'] = run_cases(torch, dev, dp, idx, w, peak)
+    records = {}
+    for leg in (network, network_large):
+        if leg:
+            records.update(leg.pop('_records'))
+    if args.write_fixtures and world == 1 and records:
+        os.makedirs(os.path.join(ROOT, 'gpurun_out'), exist_ok=True)
+        np.savez_compressed(os.path.join(ROOT, 'gpurun_out', 'network_counts.npz'),
+                            **{k: v.astype(np.int32) for k, v in records.items()})
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
     return 0
 
 
-def run_network(torch, dist, dev, world, rank, steps=1000, warm=200):
-    """The scaled COBA E/I network (1 000 000 neurons, 100 targets per neuron, dt 0.1 ms),
-    postsynaptic-sharded over the ranks, all steps in one cooperative launch per GPU with
-    the spike exchange inside the kernel.  Reported beside the headline, not part of it."""
-    from brainstate_b200.sim import EINet, LIFParams
-    n_exc, n_inh, K = 800000, 200000, 100
-    n = n_exc + n_inh
-    V0 = np.random.RandomState(302).uniform(-60, -50, n).astype(np.float32)
-    params = LIFParams(coba=True, R=0.1, E_e=0., E_i=-80., tau_e=5., tau_i=10.)
-    net = EINet(n_exc, n_inh, K, 0.6, 6.7, seed_e=300, seed_i=301, V0=V0, params=params, device=dev,
-                group=dist.group.WORLD if world > 1 else None, exchange='p2p')
-    net.run(warm, record=False)
+FIXTURE = os.path.join(ROOT, 'tests', 'golden', 'network_counts.npz')
+
+
+def run_network(torch, dist, dev, world, rank, name, steps, warm):
+    """One of the network recipes (``brainstate_b200.sim.preset``), postsynaptic-sharded over
+    the ranks: all steps in one cooperative launch per GPU with the spike exchange inside the
+    kernel.  Timed with CUDA events, maximum over ranks.  The per-step spike counts are
+    compared with the committed record of the one-GPU run (``tests/golden/network_counts.npz``,
+    written by ``--write-fixtures``).  The large recipe has heterogeneous weights: it is timed
+    with float32 sums and run once more with fixed-point sums, whose counts do not depend on
+    the order of the adds and so must equal the record at any number of GPUs."""
+    from brainstate_b200.sim import from_preset, preset
+    p = preset(name)
+    n = p['n_exc'] + p['n_inh']
+    K = p['conn_num']
+    group = dist.group.WORLD if world > 1 else None
+    hetero = not isinstance(p['w_e'], float)
+    t0 = time.perf_counter()
+    net = from_preset(name, dev, group, shard_kernel=True)
     torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
+    build_s = time.perf_counter() - t0
+
+    def timed(net):
+        pre = net.run(warm, record=False)[1] if warm else None
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        _, counts = net.run(steps, record=False)
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        all_counts = counts if pre is None else torch.cat([pre, counts])
+        return float(t.item()), counts, all_counts.cpu().numpy()
+
+    net.run(50, record=False)                  # module load, clocks; then start again from the seeded state
+    fresh = from_preset(name, dev, group, shard_kernel=True, conn=(net.conn_e, net.conn_i))
+    ms, counts, record = timed(fresh)
+    fresh.close()
+    spikes = int(counts.sum().item())
+    out = {'workload': {'coba': 'COBA E/I LIF network, 1e6 neurons (800k E / 200k I), 100 targets per neuron, g_exc 0.6, '
+                                'g_inh 6.7, E_exc 0 mV, E_inh -80 mV, constant bias tuned to ~10 Hz, dt 0.1 ms',
+                        'large': 'LIF network, 8e6 neurons (80% E / 20% I), 1000 targets per neuron (8e9 synapses, int32), '
+                                 'lognormal(-2, 0.5) f32 weights signed by population, hashed background drive (~5 Hz), '
+                                 'dt 0.1 ms'}[name] + '; postsynaptic neurons sharded over the GPUs',
+           'steps': steps, 'warmup_steps': warm, 'us_per_step': ms * 1e3 / steps, 'spikes': spikes,
+           'mean_rate_hz': spikes / n / (steps * 1e-4), 'synaptic_events_per_s': spikes * K / (ms * 1e-3),
+           'build_s': build_s, 'launches': 1,
+           'kernel': 'net_run_sharded_kernel (state in shared memory)' if net._links['links'].words_per_block <= 432
+                     else 'net_run_sharded_kernel (state in global memory)',
+           'exchange': 'spike-id lists pushed by peer stores inside the step kernel' if world > 1 else 'none (one GPU)',
+           'accumulation': 'float32 atomics'}
+    fixture = dict(np.load(FIXTURE)) if os.path.exists(FIXTURE) else {}
+    written = {}
+    if hetero:
+        det = from_preset(name, dev, group, deterministic=True, conn=(net.conn_e, net.conn_i))
+        ms_d, counts_d, record_d = timed(det)
+        out['deterministic'] = {'us_per_step': ms_d * 1e3 / steps, 'spikes': int(counts_d.sum().item()),
+                                'accumulation': '2^-32 fixed point, 64-bit integer atomics'}
+        written[name + '_deterministic'] = record_d
+        if name + '_deterministic' in fixture:
+            out['matches_n1'] = bool(np.array_equal(fixture[name + '_deterministic'], record_d))
+        else:
+            out['matches_n1'] = None
+        if name in fixture:        # float sums: equal only as long as no sum met a different rounding
+            same = fixture[name] == record
+            out['float_counts_equal_n1_for_steps'] = int(len(same) if same.all() else np.argmin(same))
+        det.close()
+    else:
+        out['matches_n1'] = bool(np.array_equal(fixture[name], record)) if name in fixture else None
+    written[name] = record
+    out['_records'] = written
+    net.close()
+    return out
+
+
+def _time(torch, fn, reps=5, warm=3):
+    for _ in range(warm):
+        fn()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
     a.record()
-    _, counts = net.run(steps, record=False)
+    for _ in range(reps):
+        fn()
     b.record()
     torch.cuda.synchronize()
-    t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    spikes = int(counts.sum().item())
-    net.close()
-    return {'workload': 'COBA E/I LIF network, 1e6 neurons (800k E / 200k I), 100 targets per neuron, '
-                        'g_exc 0.6, g_inh 6.7, E_exc 0 mV, E_inh -80 mV, dt 0.1 ms; postsynaptic neurons sharded',
-            'steps': steps, 'us_per_step': ms * 1e3 / steps, 'spikes': spikes,
-            'mean_rate_hz': spikes / n / (steps * 1e-4), 'synaptic_events_per_s': spikes * K / (ms * 1e-3),
-            'launches': 1, 'exchange': 'peer stores inside the step kernel' if world > 1 else 'none (one GPU)'}
+    return a.elapsed_time(b) * 1e-3 / reps
 
 
-def run_cases(torch, dev, dp, idx, w, peak):
-    """The rest of the microbenchmark grid (rates x weight modes x products), each
-    timed on its own with CUDA events after warm-up; reported beside the headline."""
+def run_cases(torch, dev, dp, peak):
+    """The microbenchmark grid: firing rates 0.1 / 1 / 10 %, homogeneous (0.1) and
+    heterogeneous weights, both products — ``spike@W`` as the batched scatter, ``W@spike``
+    both event-driven (scatter over the transposed copy) and as the deterministic gather
+    (16 vectors per pass) — each timed on its own with CUDA events after warm-up.
+    ``frac`` = algorithmic bytes / time / measured HBM peak."""
     from brainstate_b200 import _lib, FixedPostNumConn
     lib = _lib.lib()
     n, K, T = dp.n, dp.K, dp.T
     stream = torch.cuda.current_stream().cuda_stream
     homo = FixedPostNumConn((0.1, dp.ti), shape=(n, n))
+    homo._derived = dp.conn._derived           # same connectivity: share the derived layouts
     out = []
     for r_id, rate in enumerate((0.001, 0.01, 0.1)):
         spk = np.random.RandomState(210 + r_id).random_sample((T, n)) < rate
         sd = torch.from_numpy(spk).to(dev)
         events = float(spk.sum()) * K
-        for name, conn in (('homo', homo), ('hetero', dp.conn)):
+        for name, conn in (('homogeneous', homo), ('heterogeneous', dp.conn)):
             st = conn._struct()
             h = int(conn.hetero)
-
-            def vecmat(bps=8):
-                _lib.check(lib.bsx_event_vecmat_tuned(C.byref(st), sd.data_ptr(), _lib.SPK_BOOL8, T,
-                                                      dp.y_vecmat.data_ptr(), 0, dp.ws.data_ptr(), dp.ws_bytes,
-                                                      0, bps, stream))
-
-            def vecmat_smem():
-                vecmat(-1)
-
-            def matvec():
-                _lib.check(lib.bsx_pack_spikes(sd.data_ptr(), _lib.SPK_BOOL8, T, n, dp.bits.data_ptr(), stream))
-                for t in range(T):
-                    _lib.check(lib.bsx_event_matvec(C.byref(st), dp.bits.data_ptr() + t * dp.words * 4, _lib.SPK_BITS32,
-                                                    1, dp.y_matvec.data_ptr() + t * n * 4, None, 0, stream))
-
-            def matvec_b16():
-                _lib.check(lib.bsx_event_matvec(C.byref(st), sd.data_ptr(), _lib.SPK_BOOL8, T, dp.y_matvec.data_ptr(),
-                                                dp.mv_ws.data_ptr(), dp.mv_ws_bytes, stream))
-
-            st_t = conn._transposed_struct(conn.data)
-
-            def matvec_scatter():
-                _lib.check(lib.bsx_event_vecmat_tuned(C.byref(st_t), sd.data_ptr(), _lib.SPK_BOOL8, T,
-                                                      dp.y_matvec.data_ptr(), 0, dp.ws.data_ptr(), dp.ws_bytes,
-                                                      0, -1, stream))
-
             st_s, st_ts = conn._sliced_struct(conn.data), conn._transposed_sliced_struct(conn.data)
 
             def vecmat_sliced():
@@ -575,34 +677,109 @@ def run_cases(torch, dev, dp, idx, w, peak):
                 _lib.check(lib.bsx_event_vecmat_sliced(C.byref(st_ts), sd.data_ptr(), _lib.SPK_BOOL8, T,
                                                        dp.y_matvec.data_ptr(), 0, stream))
 
-            for prod, fn, alg in (('spike@W scatter, global atomics', vecmat, events * (4 + 4 * h) + T * (n + 4 * n)),
-                                  ('spike@W scatter, output slices in shared memory', vecmat_smem,
-                                   events * (4 + 4 * h) + T * (n + 4 * n)),
-                                  ('spike@W scatter, shared-memory slices, rows grouped by slice', vecmat_sliced,
-                                   events * (4 + 4 * h) + T * (n + 4 * n)),
-                                  ('W@spike scatter over the transposed copy, shared-memory slices, grouped', matvec_sliced,
-                                   events * (4 + 4 * h) + T * (n + 4 * n)),
-                                  ('W@spike gather, one vector per pass', matvec,
-                                   T * (n * K * 4 + n / 8 + 4 * n) + events * 4 * h),
-                                  ('W@spike gather, 16 vectors per pass', matvec_b16,
-                                   dp.passes * (n * K * 4 + 2 * n) + T * 4 * n + events * 4 * h),
-                                  ('W@spike scatter over the transposed copy, output slices in shared memory', matvec_scatter,
-                                   events * (4 + 4 * h) + T * (n + 4 * n))):
-                for _ in range(3):
-                    fn()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                torch.cuda.synchronize()
-                a.record()
-                reps = 5
-                for _ in range(reps):
-                    fn()
-                b.record()
-                torch.cuda.synchronize()
-                s = a.elapsed_time(b) * 1e-3 / reps
+            def matvec_b16():
+                _lib.check(lib.bsx_event_matvec(C.byref(st), sd.data_ptr(), _lib.SPK_BOOL8, T, dp.y_matvec.data_ptr(),
+                                                dp.mv_ws.data_ptr(), dp.mv_ws_bytes, stream))
+
+            scatter_bytes = events * (4 + 4 * h) + T * (n + 4 * n)
+            for prod, fn, alg in (('spike@W, scatter (output slices in shared memory)', vecmat_sliced, scatter_bytes),
+                                  ('W@spike, event-driven scatter over the transposed copy', matvec_sliced, scatter_bytes),
+                                  ('W@spike, deterministic gather (16 vectors per pass)', matvec_b16,
+                                   dp.passes * (n * K * 4 + 2 * n) + T * 4 * n + events * 4 * h)):
+                sec = _time(torch, fn)
                 out.append({'rate': rate, 'weights': name, 'product': prod, 'vectors': T,
-                            'events_per_s': events / s, 'us_per_vector': s / T * 1e6,
-                            'algorithmic_GBps': alg / s / 1e9, 'frac_of_peak': alg / s / 1e9 / peak})
+                            'events_per_s': events / sec, 'us_per_vector': sec / T * 1e6,
+                            'algorithmic_GBps': alg / sec / 1e9, 'frac': alg / sec / 1e9 / peak})
     return out
+
+
+def run_single_vector(torch, dev, dp, peak, calls=64):
+    """One spike vector per call — what ``EventFixedProb.update(spk)`` sees inside a
+    simulation loop: ``calls`` back-to-back ``bsx_event_vecmat`` calls on distinct spike
+    vectors, captured in a CUDA graph and replayed; microseconds per call."""
+    from brainstate_b200 import _lib, FixedPostNumConn
+    lib = _lib.lib()
+    n, K = dp.n, dp.K
+    homo = FixedPostNumConn((0.1, dp.ti), shape=(n, n))
+    ws_bytes = lib.bsx_event_vecmat_workspace_bytes(1, n)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    y = torch.empty((calls, n), dtype=torch.float32, device=dev)
+    out = []
+    for r_id, rate in enumerate((0.001, 0.01, 0.1)):
+        spk = np.random.RandomState(230 + r_id).random_sample((calls, n)) < rate
+        sd = torch.from_numpy(spk).to(dev)
+        events = float(spk.sum()) * K / calls
+        for name, conn in (('homogeneous', homo), ('heterogeneous', dp.conn)):
+            st = conn._struct()
+            h = int(conn.hetero)
+
+            def burst():
+                stream = torch.cuda.current_stream().cuda_stream
+                for c in range(calls):
+                    _lib.check(lib.bsx_event_vecmat(C.byref(st), sd.data_ptr() + c * n, _lib.SPK_BOOL8, 1,
+                                                    y.data_ptr() + 4 * c * n, 0, ws.data_ptr(), ws_bytes, stream))
+
+            burst()
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side):
+                    burst()
+            torch.cuda.current_stream().wait_stream(side)
+            sec = _time(torch, g.replay, reps=10) / calls
+            alg = events * (4 + 4 * h) + n + 4 * n
+            out.append({'rate': rate, 'weights': name, 'us_per_call': sec * 1e6, 'events_per_s': events / sec,
+                        'algorithmic_GBps': alg / sec / 1e9, 'frac': alg / sec / 1e9 / peak,
+                        'launches_per_call': int(lib.bsx_event_vecmat_launches(C.byref(st), _lib.SPK_BOOL8, 1))})
+            del g
+    return out
+
+
+def run_training_step(torch, dev, dp, peak):
+    """The batched event matmul with its reverse mode: 64 x 65 536 spikes at 2 %, the
+    heterogeneous matrix, cotangent N(0, 1).  Forward, input cotangent, weight cotangent and
+    the whole step, with the algorithmic bytes of each (reverse mode reads every index and
+    weight once and writes one float per synapse)."""
+    from brainstate_b200 import _lib
+    lib = _lib.lib()
+    n, K, B = dp.n, dp.K, 64
+    nnz = n * K
+    spk = np.random.RandomState(220).random_sample((B, n)) < 0.02
+    ct = np.random.RandomState(221).standard_normal((B, n)).astype(np.float32)
+    sd, ctd = torch.from_numpy(spk).to(dev), torch.from_numpy(ct).to(dev)
+    events = float(spk.sum()) * K
+    y = torch.empty((B, n), dtype=torch.float32, device=dev)
+    dx = torch.empty((B, n), dtype=torch.float32, device=dev)
+    dw = torch.empty((n, K), dtype=torch.float32, device=dev)
+    st, st_s = dp.conn._struct(), dp.conn._sliced_struct(dp.conn.data)
+    ws_bytes = lib.bsx_vecmat_vjp_batched_workspace_bytes(B, n)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def fwd():
+        _lib.check(lib.bsx_event_vecmat_sliced(C.byref(st_s), sd.data_ptr(), _lib.SPK_BOOL8, B, y.data_ptr(), 0, stream))
+
+    def bwd(want_dx, want_dw):
+        _lib.check(lib.bsx_vecmat_vjp_batched(C.byref(st), sd.data_ptr(), _lib.SPK_BOOL8, 1, ctd.data_ptr(), B,
+                                              dx.data_ptr() if want_dx else None, dw.data_ptr() if want_dw else None,
+                                              ws.data_ptr(), ws_bytes, stream))
+
+    def step():
+        fwd()
+        bwd(True, True)
+
+    t_f, t_dx, t_dw = _time(torch, fwd), _time(torch, lambda: bwd(True, False)), _time(torch, lambda: bwd(False, True))
+    t_b, t_s = _time(torch, lambda: bwd(True, True)), _time(torch, step)
+    b_fwd = events * 8 + B * (n + 4 * n)
+    b_dx = nnz * 8 + 2 * B * n * 4
+    b_dw = nnz * 4 + nnz * 4 + B * n * 4 + B * n
+    b_bwd = nnz * 8 + nnz * 4 + 2 * B * n * 4
+    leg = lambda t, nb: {'us': t * 1e6, 'algorithmic_bytes': nb, 'algorithmic_GBps': nb / t / 1e9, 'frac': nb / t / 1e9 / peak}
+    return {'workload': '64 x 65536 Bernoulli(2 %) spikes, heterogeneous 65536 x 655 matrix, cotangent N(0,1)',
+            'forward': leg(t_f, b_fwd), 'dx_only': leg(t_dx, b_dx), 'dw_only': leg(t_dw, b_dw),
+            'backward': leg(t_b, b_bwd), 'step_us': t_s * 1e6, 'events_per_s_forward': events / t_f}
 
 
 def main():
@@ -613,8 +790,12 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--vectors', type=int, default=296,
                     help='spike vectors per step (per GPU); 296 vectors x 2 output slices = 4 blocks on each of the 148 SMs')
-    ap.add_argument('--cases', action='store_true', help='also time the full rate x weight x product grid')
-    ap.add_argument('--no-network', action='store_true', help='skip the sharded network run reported beside the headline')
+    ap.add_argument('--no-cases', action='store_true', help='skip the rate x weight x product grid, the single-vector '
+                    'calls and the training step')
+    ap.add_argument('--no-network', action='store_true', help='skip the sharded network runs reported beside the headline')
+    ap.add_argument('--no-large', action='store_true', help='skip the 8e6-neuron network')
+    ap.add_argument('--write-fixtures', action='store_true',
+                    help='one GPU: write the per-step spike counts of the network runs to gpurun_out/network_counts.npz')
     ap.add_argument('--profile', action='store_true',
                     help='run only the device-resident loop (for ncu); prints no bench line')
     args = ap.parse_args()

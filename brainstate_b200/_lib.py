@@ -64,11 +64,22 @@ class BsxNet(C.Structure):
     ]
 
 
-class BsxNetPeers(C.Structure):
-    """Mirror of ``bsx_net_peers_t``."""
-    _fields_ = [('world', C.c_int32), ('rank', C.c_int32), ('words_per_rank', C.c_int64),
-                ('spin_limit', C.c_int64), ('bits', C.c_void_p * 16), ('flags', C.c_void_p * 16),
-                ('status', C.c_void_p)]
+class BsxNetShard(C.Structure):
+    """Mirror of ``bsx_net_shard_t``."""
+    _fields_ = [
+        ('n_global', C.c_int64), ('n_exc', C.c_int64), ('first', C.c_int64), ('n_local', C.c_int64),
+        ('exc', BsxConn), ('inh', BsxConn),
+        ('V', C.c_void_p), ('g_e', C.c_void_p), ('g_i', C.c_void_p), ('ref', C.c_void_p),
+        ('incr_e', C.c_void_p), ('incr_i', C.c_void_p), ('bits', C.c_void_p),
+        ('ring', C.c_int32), ('delay_e', C.c_int32), ('delay_i', C.c_int32), ('fixed_point', C.c_int32),
+    ]
+
+
+class BsxNetLinks(C.Structure):
+    """Mirror of ``bsx_net_links_t``."""
+    _fields_ = [('world', C.c_int32), ('rank', C.c_int32), ('blocks', C.c_int32), ('words_per_block', C.c_int32),
+                ('words_per_rank', C.c_int64), ('slots', C.c_int32), ('slack', C.c_int32),
+                ('spin_limit', C.c_int64), ('seq0', C.c_int64), ('inbox', C.c_void_p * 16), ('sync', C.c_void_p)]
 
 
 _i64, _i32, _vp, _sz, _f32 = C.c_int64, C.c_int, C.c_void_p, C.c_size_t, C.c_float
@@ -76,7 +87,8 @@ _connp = C.POINTER(BsxConn)
 _netp = C.POINTER(BsxNet)
 _lifp = C.POINTER(BsxLifParams)
 
-# name -> (restype, argtypes); every symbol include/bsx.h declares
+# name -> (restype, argtypes); every symbol include/bsx.h declares, plus the two tuning hooks of
+# csrc/bsx_tuning.h (INTERNAL lists them)
 SIGNATURES = {
     'bsx_version': (_i32, []),
     'bsx_last_error_string': (C.c_char_p, []),
@@ -99,6 +111,7 @@ SIGNATURES = {
     'bsx_event_vecmat': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp, _sz, _vp]),
     'bsx_event_vecmat_tuned': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp, _sz, _i32, _i32, _vp]),
     'bsx_event_vecmat_variant': (_i32, [_connp, _i32, _i64]),
+    'bsx_event_vecmat_launches': (_i32, [_connp, _i32, _i64]),
     'bsx_sliced_slices': (_i64, [_i64]),
     'bsx_sliced_build': (_i32, [_connp, _vp, _vp, _vp, _vp]),
     'bsx_event_vecmat_sliced': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp]),
@@ -116,7 +129,9 @@ SIGNATURES = {
     'bsx_net_update': (_i32, [_netp, _lifp, _i64, _vp, _vp]),
     'bsx_net_list_from_bits': (_i32, [_netp, _i64, _vp]),
     'bsx_net_scatter': (_i32, [_netp, _i64, _vp]),
-    'bsx_net_run_p2p': (_i32, [_netp, _lifp, C.POINTER(BsxNetPeers), _i32, _i64, _vp, _vp, _i32, _vp]),
+    'bsx_net_shard_geometry': (_i32, [_i64, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    'bsx_net_inbox_bytes': (_sz, [_i32, _i32, _i32, _i32]),
+    'bsx_net_run_sharded': (_i32, [C.POINTER(BsxNetShard), _lifp, C.POINTER(BsxNetLinks), _i32, _i64, _vp, _vp, _vp]),
     'bsx_ipc_alloc': (_i32, [_sz, C.POINTER(C.c_void_p), _vp]),
     'bsx_ipc_open': (_i32, [_vp, C.POINTER(C.c_void_p)]),
     'bsx_ipc_close': (_i32, [_vp]),
@@ -124,6 +139,8 @@ SIGNATURES = {
     'bsx_drive_hash': (C.c_uint32, [C.c_uint32, C.c_uint32, C.c_uint32]),
     'bsx_fill_f32': (_i32, [_vp, _i64, _f32, _vp]),
 }
+
+INTERNAL = ('bsx_event_vecmat_tuned', 'bsx_event_matvec_tuned')
 
 _lib = None
 

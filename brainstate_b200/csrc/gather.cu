@@ -7,6 +7,7 @@
 //
 // HBM traffic: 4 B per stored synapse for the indices; weights are touched only
 // where a spike hits (event) or for every synapse (float / vjp).
+#include "bsx_tuning.h"
 #include "common.cuh"
 #include "internal.cuh"
 

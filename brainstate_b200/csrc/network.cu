@@ -26,19 +26,11 @@
 
 #include "common.cuh"
 #include "internal.cuh"
+#include "network.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace bsx {
-
-struct ProjDev {
-  RowMap rm;
-  const int32_t* idx;
-  const float* w;
-  int hetero;
-  int cpr;      // chunks per row
-  bool vec_ok;
-};
 
 struct NetDev {
   int64_t n_global, n_exc, first, n_local;
@@ -100,40 +92,6 @@ __device__ __forceinline__ void phase_scatter(const NetDev& a, int64_t step, int
   }
 }
 
-// Counter-based background drive: neuron `gid` receives one external excitatory
-// event at step `step` when a 32-bit hash of (seed, gid, step) falls below the
-// threshold.  Integer arithmetic only, so a host restatement matches bit for bit.
-__host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
-  x ^= x >> 16;
-  x *= 0x7feb352du;
-  x ^= x >> 15;
-  x *= 0x846ca68bu;
-  x ^= x >> 16;
-  return x;
-}
-__host__ __device__ __forceinline__ uint32_t drive_hash(uint32_t seed, uint32_t gid, uint32_t step) {
-  return mix32(mix32(gid + seed * 0x9e3779b9u) ^ (step * 0x85ebca6bu + 0xc2b2ae35u));
-}
-
-// (exp(z) - 1) / z.  For |z| <= 0.25 (every realistic dt * df/dV) a degree-6 Taylor
-// polynomial in Horner form, each multiply and add rounded separately in float32 so
-// that a host restatement doing the same operations matches bit for bit (the
-// truncation error, z^7/5040, is below float32 resolution there); otherwise
-// evaluated in double and rounded once.
-__device__ __forceinline__ float exprel_once(float z) {
-  if (fabsf(z) <= 0.25f) {
-    float p = 0.0013888889f;                                  // 1/720
-    p = __fadd_rn(__fmul_rn(p, z), 0.008333334f);             // 1/120
-    p = __fadd_rn(__fmul_rn(p, z), 0.041666668f);             // 1/24
-    p = __fadd_rn(__fmul_rn(p, z), 0.16666667f);              // 1/6
-    p = __fadd_rn(__fmul_rn(p, z), 0.5f);
-    p = __fadd_rn(__fmul_rn(p, z), 1.0f);
-    return p;
-  }
-  const double zd = (double)z;
-  return (float)(expm1(zd) / zd);
-}
-
 // Phase B is split in two so that a warp can have the loads of two words in flight
 // before it computes either: one L2 round trip per pair instead of per word.
 struct NeuronIn {
@@ -154,44 +112,6 @@ __device__ __forceinline__ NeuronIn load_neuron(const NetDev& a, int64_t i) {
     s.r = a.ref[i];
   }
   return s;
-}
-
-// The arithmetic of one neuron for one step: synapse decay + increment (+ background
-// drive), membrane update, threshold, reset, refractory count.  Pure: state in, state out.
-struct NeuronOut {
-  float ge, gi, V;
-  int32_t r;
-  bool spk;
-};
-
-__device__ __forceinline__ NeuronOut neuron_math(const bsx_lif_params_t& p, float de, float di, float ge0,
-                                                 float gi0, float V, int32_t r, uint32_t gid, int64_t step) {
-  if (p.ext_threshold && drive_hash(p.ext_seed, gid, (uint32_t)step) < p.ext_threshold)
-    de = __fadd_rn(de, p.ext_weight);
-  NeuronOut o;
-  o.ge = __fadd_rn(__fmul_rn(ge0, p.decay_e), de);
-  o.gi = __fadd_rn(__fmul_rn(gi0, p.decay_i), di);
-  float cur;
-  if (p.coba) cur = __fadd_rn(__fmul_rn(o.ge, __fsub_rn(p.E_e, V)), __fmul_rn(o.gi, __fsub_rn(p.E_i, V)));
-  else cur = __fadd_rn(o.ge, o.gi);
-  const float drive = __fmul_rn(p.R, __fadd_rn(cur, p.I_ext));
-  const float num = __fadd_rn(__fsub_rn(p.V_rest, V), drive);
-  float Vn;
-  if (p.coba) {
-    const float f = __fmul_rn(num, p.inv_tau_m);
-    const float gsum = __fadd_rn(o.ge, o.gi);
-    const float J = __fmul_rn(-__fadd_rn(1.0f, __fmul_rn(p.R, gsum)), p.inv_tau_m);
-    const float gain = __fmul_rn(p.dt, exprel_once(__fmul_rn(p.dt, J)));
-    Vn = __fadd_rn(V, __fmul_rn(gain, f));
-  } else {
-    Vn = __fadd_rn(V, __fmul_rn(p.cuba_gain, num));
-  }
-  const bool refractory = r > 0;
-  if (refractory) Vn = V;
-  o.spk = (Vn >= p.V_th) && !refractory;
-  o.V = o.spk ? p.V_reset : Vn;
-  o.r = o.spk ? p.ref_steps : (r > 0 ? r - 1 : 0);
-  return o;
 }
 
 // Applies neuron_math to neuron i of the global-memory state; unchanged values are
@@ -593,133 +513,6 @@ net_update_kernel(NetDev a, int64_t step, int32_t* __restrict__ local_count) {
 }
 
 
-// ---- many steps, many GPUs, one launch per GPU: the exchange is part of the kernel ----
-//
-// Every rank runs this cooperative kernel over its own neurons.  After the neuron
-// update a rank stores its packed spike words straight into the exchange buffer of
-// every peer (plain stores over NVLink; buffers double-buffered by step parity),
-// fences at system scope, and raises a per-source progress counter on each peer.
-// It then waits until all sources have reached the step, and compacts the complete
-// word array into the spike list of the step.  No host round trip and no library
-// collective per step.
-//
-// Every wait is bounded: when a counter does not arrive within spin_limit polls the
-// block raises the abort word, all blocks leave together at the next grid barrier and
-// the host finds BSX_ERR_TIMEOUT in the status word.
-constexpr int kMaxPeers = 16;
-
-struct PeerDev {
-  int world, rank;
-  uint32_t* bits[kMaxPeers];
-  long long* flags[kMaxPeers];
-  int32_t* status;
-  int64_t wpr;          // words contributed per rank
-  int64_t spin_limit;
-};
-
-__device__ __forceinline__ long long load_acquire_sys(const long long* p) {
-  long long v;
-  asm volatile("ld.acquire.sys.global.s64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void store_release_sys(long long* p, long long v) {
-  asm volatile("st.release.sys.global.s64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t load_relaxed_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-__global__ void __launch_bounds__(256)
-net_run_p2p_kernel(NetDev a, PeerDev pr, int steps, int64_t step0, uint32_t* __restrict__ raster,
-                   int32_t* __restrict__ spike_counts) {
-  cg::grid_group grid = cg::this_grid();
-  __shared__ int s_abort;
-  const int lane = threadIdx.x & 31;
-  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  const int64_t words_local = (a.n_local + 31) >> 5;
-  const int64_t words_all = (a.n_global + 31) >> 5;
-  const int64_t total_words = pr.wpr * pr.world;     // size of one exchange buffer
-  const int64_t word0 = (int64_t)pr.rank * pr.wpr;
-  for (int t = 0; t < steps; ++t) {
-    const int64_t step = step0 + t;
-    const int64_t par = step & 1;
-    int32_t* lnext = a.slot(step);
-    if (warp == 0 && lane == 0) lnext[0] = 0;
-    phase_scatter(a, step, warp, nwarps, lane);
-    grid.sync();
-    // neuron update; the spike words go to every rank's exchange buffer, mine included
-    for (int64_t wd = warp; wd < words_local; wd += 2 * nwarps) {
-      const int64_t wd1 = wd + nwarps < words_local ? wd + nwarps : -1;
-      bool spk0, spk1;
-      uint32_t m0, m1;
-      update_two_words(a, wd, wd1, lane, step, &m0, &m1, &spk0, &spk1);
-      if (lane < pr.world) {
-        pr.bits[lane][par * total_words + word0 + wd] = m0;
-        if (wd1 >= 0) pr.bits[lane][par * total_words + word0 + wd1] = m1;
-      }
-    }
-    __threadfence_system();
-    grid.sync();
-    if (blockIdx.x == 0 && threadIdx.x < pr.world)
-      store_release_sys(pr.flags[threadIdx.x] + pr.rank, (long long)(step + 1));
-    // wait for every source (bounded)
-    if (threadIdx.x == 0) {
-      int bad = 0;
-      const long long* mine = pr.flags[pr.rank];
-      for (int r = 0; r < pr.world && !bad; ++r) {
-        int64_t spins = 0;
-        while (load_acquire_sys(mine + r) < (long long)(step + 1)) {
-          if (++spins > pr.spin_limit) { bad = 1; break; }
-          if (*reinterpret_cast<volatile int32_t*>(pr.status) != 0) { bad = 1; break; }
-        }
-      }
-      if (bad) atomicCAS(pr.status, 0, (int32_t)BSX_ERR_TIMEOUT);
-      s_abort = bad;
-    }
-    __syncthreads();
-    const bool skip = s_abort != 0;
-    // complete word array -> spike list of this step (+ raster, + the plain copy in a.bits)
-    if (!skip) {
-      const uint32_t* __restrict__ full = pr.bits[pr.rank] + par * total_words;
-      const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-      const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
-      for (int64_t g0 = tid - lane; g0 < words_all; g0 += nthreads) {
-        const int64_t g = g0 + lane;
-        uint32_t m = 0;
-        if (g < words_all) {
-          m = load_relaxed_sys(full + g);
-          const int64_t left = a.n_global - g * 32;
-          if (left < 32) m &= (1u << left) - 1u;
-          a.bits[g] = m;
-          if (raster) raster[(int64_t)t * words_all + g] = m;
-        }
-        uint32_t cnt = __popc(m), incl = cnt;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const uint32_t u = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane >= o) incl += u;
-        }
-        const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-        uint32_t base = 0;
-        if (lane == 31 && total) base = (uint32_t)atomicAdd(lnext, (int32_t)total);
-        base = __shfl_sync(0xffffffffu, base, 31);
-        uint32_t pos = base + incl - cnt;
-        while (m) {
-          const int k = __ffs(m) - 1;
-          m &= m - 1;
-          lnext[1 + pos++] = (int32_t)(g * 32 + k);
-        }
-      }
-    }
-    grid.sync();
-    if (*reinterpret_cast<volatile int32_t*>(pr.status) != 0) return;   // every block sees the same word here
-    if (spike_counts && warp == 0 && lane == 0) spike_counts[t] = lnext[0];
-  }
-}
-
 // Compacts the packed spike words of the whole network into a list of global ids.
 __global__ void __launch_bounds__(256)
 net_list_kernel(const uint32_t* __restrict__ bits, int64_t n_global, int32_t* __restrict__ list) {
@@ -753,19 +546,6 @@ net_list_kernel(const uint32_t* __restrict__ bits, int64_t n_global, int32_t* __
       list[1 + pos++] = (int32_t)(g * 32 + k);
     }
   }
-}
-
-static int make_proj(const bsx_conn_t* c, int chunk, ProjDev* out) {
-  int rc = check_conn(c);
-  if (rc) return rc;
-  out->rm = make_rowmap(c);
-  out->idx = c->indices;
-  out->w = c->weights;
-  out->hetero = c->hetero;
-  out->vec_ok = aligned16(c->indices) && (!c->hetero || aligned16(c->weights));
-  out->cpr = 1;
-  if (!c->indptr && c->conn_num > chunk) out->cpr = (int)((c->conn_num + chunk - 1) / chunk);
-  return BSX_OK;
 }
 
 static int make_net(const bsx_net_t* net, const bsx_lif_params_t* p, NetDev* a) {
@@ -911,52 +691,6 @@ int bsx_net_list_from_bits(const bsx_net_t* net, int64_t step, bsx_stream_t stre
   if (blocks < 1) blocks = 1;
   net_list_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(a.bits, a.n_global, list);
   BSX_LAUNCH_CHECK("net_list_kernel");
-  return BSX_OK;
-}
-
-int bsx_net_run_p2p(const bsx_net_t* net, const bsx_lif_params_t* params, const bsx_net_peers_t* peers,
-                    int32_t steps, int64_t step0, uint32_t* raster, int32_t* spike_counts, int32_t blocks,
-                    bsx_stream_t stream) {
-  if (!params || !peers) return fail(BSX_ERR_INVALID_ARG, "params or peers is NULL");
-  if (steps < 0 || step0 < 0) return fail(BSX_ERR_INVALID_ARG, "bad step range");
-  if (peers->world < 1 || peers->world > kMaxPeers || peers->rank < 0 || peers->rank >= peers->world)
-    return fail(BSX_ERR_INVALID_ARG, "world must be 1..%d and rank inside it", kMaxPeers);
-  if (!peers->status || peers->words_per_rank <= 0) return fail(BSX_ERR_INVALID_ARG, "bad peer description");
-  NetDev a;
-  int rc = make_net(net, params, &a);
-  if (rc) return rc;
-  if (net->first != peers->rank * peers->words_per_rank * 32 && net->n_local > 0)
-    return fail(BSX_ERR_INVALID_ARG, "first local neuron must be rank * words_per_rank * 32");
-  if ((net->n_local + 31) / 32 > peers->words_per_rank)
-    return fail(BSX_ERR_INVALID_ARG, "the rank owns more words than words_per_rank");
-  if (peers->words_per_rank * peers->world < (net->n_global + 31) / 32)
-    return fail(BSX_ERR_INVALID_ARG, "exchange buffers shorter than the network");
-  PeerDev pd;
-  pd.world = peers->world;
-  pd.rank = peers->rank;
-  for (int r = 0; r < kMaxPeers; ++r) {
-    pd.bits[r] = r < peers->world ? peers->bits[r] : nullptr;
-    pd.flags[r] = r < peers->world ? reinterpret_cast<long long*>(peers->flags[r]) : nullptr;
-    if (r < peers->world && (!pd.bits[r] || !pd.flags[r])) return fail(BSX_ERR_INVALID_ARG, "peer %d has a NULL buffer", r);
-  }
-  pd.status = peers->status;
-  pd.wpr = peers->words_per_rank;
-  pd.spin_limit = peers->spin_limit > 0 ? peers->spin_limit : (int64_t)1 << 21;
-  if (steps == 0) return BSX_OK;
-  int sms = sm_count();
-  if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
-  int per_sm = 0;
-  BSX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, net_run_p2p_kernel, 256, 0));
-  if (per_sm < 1) return fail(BSX_ERR_CUDA, "the network kernel does not fit on an SM");
-  int64_t max_blocks = (int64_t)sms * (per_sm < 4 ? per_sm : 4);
-  int64_t want = blocks > 0 ? blocks : (net->n_local + 255) / 256;
-  if (want < 1) want = 1;
-  if (want > max_blocks) want = max_blocks;
-  int steps_i = steps;
-  int64_t step0_i = step0;
-  void* args[] = {&a, &pd, &steps_i, &step0_i, &raster, &spike_counts};
-  BSX_CUDA(cudaLaunchCooperativeKernel((const void*)net_run_p2p_kernel, dim3((unsigned)want), dim3(256), args, 0,
-                                       as_stream(stream)));
   return BSX_OK;
 }
 

@@ -6,6 +6,7 @@
 // lane streams indices (and weights) with 128-bit loads and issues one
 // red.global.add.f32 per synapse.  HBM traffic per event is 4 B (index) + 4 B
 // (heterogeneous weight); the adds resolve in L2.
+#include "bsx_tuning.h"
 #include "common.cuh"
 #include "internal.cuh"
 
@@ -168,6 +169,13 @@ int bsx_event_vecmat_variant(const bsx_conn_t* conn, int spike_format, int64_t b
   if (rc) return rc;
   if (batch < 0) return fail(BSX_ERR_INVALID_ARG, "negative batch");
   return scatter_smem_preferred(conn, spike_format, batch) ? BSX_VECMAT_SHARED_SLICES : BSX_VECMAT_GLOBAL_ATOMICS;
+}
+
+int bsx_event_vecmat_launches(const bsx_conn_t* conn, int spike_format, int64_t batch) {
+  const int v = bsx_event_vecmat_variant(conn, spike_format, batch);
+  if (v < 0) return v;
+  if (v == BSX_VECMAT_SHARED_SLICES) return 1;
+  return spike_format == BSX_SPK_LIST ? 2 : 2;      // (clear | compaction + clear) and scatter
 }
 
 int bsx_event_vecmat(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,

@@ -55,9 +55,9 @@ extern "C" int bsx_event_vecmat_static(const bsx_conn_t* conn, const void* spike
   if (spike_format != BSX_SPK_LIST &&
       ((double)batch * (double)conn->n_pre > (double)BSX_STATIC_QUEUE_MAX_SPIKES || need > kStaticQueueBytes))
     return fail(BSX_ERR_WORKSPACE,
-                "bsx_event_vecmat_static: batch * n_pre = %lld exceeds the built-in queue of %d entries; "
+                "bsx_event_vecmat_static: batch * n_pre = %.0f exceeds the built-in queue of %d entries; "
                 "use bsx_event_vecmat with a caller-provided workspace",
-                (long long)(batch * conn->n_pre), BSX_STATIC_QUEUE_MAX_SPIKES);
+                (double)batch * (double)conn->n_pre, BSX_STATIC_QUEUE_MAX_SPIKES);
   void* queue = nullptr;
   int rc = static_queue_address(&queue);
   if (rc) return rc;

@@ -88,9 +88,10 @@ class _SparseConn:
             if indptr.numel() != self.shape[0] + 1:
                 raise ValueError('indptr must have n_pre + 1 entries')
             self.indptr = indptr.contiguous()
-        self._transposed: Optional[_Transposed] = None
-        self._sliced = None
-        self._t_groups = None
+        # derived layouts (transposed copy, copies grouped by output slice) and their permuted
+        # weights; ONE dict shared by reference with every ``with_data`` view, so that a layout
+        # built through a view (every layer call makes one) is built once for all of them
+        self._derived = {}
         self.matvec_method = 'gather'    # what ``conn @ EventArray`` uses; see ``event_matvec``
         self._set_data(data)
 
@@ -110,13 +111,11 @@ class _SparseConn:
             raise ValueError(f'weights of shape {tuple(data.shape)} match neither a scalar nor the '
                              f'indices {tuple(self.indices.shape)}')
         self.data = data
-        self._t_weights = None          # permuted copies for the transposed and the sliced layout,
-        self._s_weights = None          # made on demand
-        self._ts_weights = None
 
     def with_data(self, data):
         """A view of the same connectivity with other weights
-        (``brainevent`` ``with_data``, used at ``_event_fixedprob.py:204``)."""
+        (``brainevent`` ``with_data``, used at ``_event_fixedprob.py:204``).  The view shares
+        the derived layouts of the connectivity it was made from."""
         new = object.__new__(type(self))
         new.__dict__.update(self.__dict__)
         new._set_data(data)
@@ -163,7 +162,7 @@ class _SparseConn:
 
     def transposed(self) -> _Transposed:
         """Builds (once) and returns the postsynaptic-major copy."""
-        if self._transposed is None:
+        if 'transposed' not in self._derived:
             n_pre, n_post = self.shape
             dev = self.indices.device
             nnz = self.nnz
@@ -175,26 +174,27 @@ class _SparseConn:
             st = self._struct()
             check(lib().bsx_transpose_build(C.byref(st), nnz, ptr(t_indptr), ptr(t_indices), ptr(t_perm),
                                             ptr(ws), ws_bytes, _lib.current_stream()))
-            self._transposed = _Transposed(t_indptr, t_indices, t_perm, n_post, n_pre)
-        return self._transposed
+            self._derived['transposed'] = _Transposed(t_indptr, t_indices, t_perm, n_post, n_pre)
+        return self._derived['transposed']
+
+    def _permuted_weights(self, layout: str, weights: torch.Tensor, perm: torch.Tensor) -> torch.Tensor:
+        """``weights`` (original order) re-gathered for a derived layout.  Kept until the weight
+        tensor changes (new storage or an in-place update), so repeated products pay the
+        4-byte-per-synapse gather once."""
+        wsrc = weights.contiguous()
+        key = (wsrc.data_ptr(), wsrc._version, wsrc.numel())
+        cached = self._derived.get('w_' + layout)
+        if cached is not None and cached[0] == key:
+            return cached[1]
+        out = torch.empty(self.nnz, dtype=torch.float32, device=weights.device)
+        check(lib().bsx_permute_f32(ptr(wsrc), ptr(perm), self.nnz, ptr(out), _lib.current_stream()))
+        self._derived['w_' + layout] = (key, out, wsrc)      # wsrc held so that its address cannot be reused
+        return out
 
     def _transposed_struct(self, weights: torch.Tensor):
-        """``bsx_conn_t`` of the transposed copy with the given (original-order) weights.
-        The permuted weights are kept until the weight tensor changes (new storage or an
-        in-place update), so repeated products pay the 4-byte-per-synapse gather once."""
+        """``bsx_conn_t`` of the transposed copy with the given (original-order) weights."""
         t = self.transposed()
-        if self.hetero:
-            wsrc = weights.contiguous()
-            key = (wsrc.data_ptr(), wsrc._version, wsrc.numel())
-            cached = getattr(self, '_t_weights', None)
-            if cached is not None and cached[0] == key:
-                wt = cached[1]
-            else:
-                wt = torch.empty(self.nnz, dtype=torch.float32, device=weights.device)
-                check(lib().bsx_permute_f32(ptr(wsrc), ptr(t.perm), self.nnz, ptr(wt), _lib.current_stream()))
-                self._t_weights = (key, wt, wsrc)      # wsrc held so that its address cannot be reused
-        else:
-            wt = weights.contiguous()
+        wt = self._permuted_weights('t', weights, t.perm) if self.hetero else weights.contiguous()
         s = BsxConn()
         s.n_pre, s.n_post = t.n_rows, t.n_cols
         s.conn_num = 0
@@ -223,21 +223,10 @@ class _SparseConn:
     def _sliced_struct(self, weights: torch.Tensor):
         """``bsx_conn_t`` of the copy whose rows are grouped by output slice (built once); the
         regrouped weights are kept until the weight tensor changes."""
-        if getattr(self, '_sliced', None) is None:
-            self._sliced = self._group_offsets(self._struct(), self.shape[0], regroup=True)
-        s_indptr, s_indices, s_perm = self._sliced
-        if self.hetero:
-            wsrc = weights.contiguous()
-            key = (wsrc.data_ptr(), wsrc._version, wsrc.numel())
-            cached = getattr(self, '_s_weights', None)
-            if cached is not None and cached[0] == key:
-                ws_ = cached[1]
-            else:
-                ws_ = torch.empty(self.nnz, dtype=torch.float32, device=weights.device)
-                check(lib().bsx_permute_f32(ptr(wsrc), ptr(s_perm), self.nnz, ptr(ws_), _lib.current_stream()))
-                self._s_weights = (key, ws_, wsrc)
-        else:
-            ws_ = weights.contiguous()
+        if 'sliced' not in self._derived:
+            self._derived['sliced'] = self._group_offsets(self._struct(), self.shape[0], regroup=True)
+        s_indptr, s_indices, s_perm = self._derived['sliced']
+        ws_ = self._permuted_weights('s', weights, s_perm) if self.hetero else weights.contiguous()
         s = BsxConn()
         s.n_pre, s.n_post = self.shape
         s.conn_num = 0
@@ -256,7 +245,7 @@ class _SparseConn:
         transposed copy's, so the weights are gathered from the original array in one pass."""
         t = self.transposed()
         n_pre, n_post = self.shape
-        if self._t_groups is None:
+        if 't_groups' not in self._derived:
             b = BsxConn()
             b.n_pre, b.n_post = t.n_rows, t.n_cols
             b.conn_num, b.nnz = 0, self.nnz
@@ -265,20 +254,9 @@ class _SparseConn:
             b.hetero, b.weights = 0, self.data.data_ptr()
             s_indptr, s_indices, s_perm = self._group_offsets(b, t.n_rows, regroup=True)
             comp = t.perm[s_perm.long()].contiguous() if self.nnz else s_perm
-            self._t_groups = (s_indptr, s_indices, comp)
-        s_indptr, s_indices, comp = self._t_groups
-        if self.hetero:
-            wsrc = weights.contiguous()
-            key = (wsrc.data_ptr(), wsrc._version, wsrc.numel())
-            cached = getattr(self, '_ts_weights', None)
-            if cached is not None and cached[0] == key:
-                wt = cached[1]
-            else:
-                wt = torch.empty(self.nnz, dtype=torch.float32, device=weights.device)
-                check(lib().bsx_permute_f32(ptr(wsrc), ptr(comp), self.nnz, ptr(wt), _lib.current_stream()))
-                self._ts_weights = (key, wt, wsrc)
-        else:
-            wt = weights.contiguous()
+            self._derived['t_groups'] = (s_indptr, s_indices, comp)
+        s_indptr, s_indices, comp = self._derived['t_groups']
+        wt = self._permuted_weights('ts', weights, comp) if self.hetero else weights.contiguous()
         s = BsxConn()
         s.n_pre, s.n_post = t.n_rows, t.n_cols
         s.conn_num = 0

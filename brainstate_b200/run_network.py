@@ -6,7 +6,8 @@
 
 Presets
   cuba   4 000 LIF neurons, p = 0.02, homogeneous weights +1.62 / -9 (current-based)
-  coba   1 000 000 conductance-based LIF neurons, 100 targets per neuron, 0.6 / 6.7
+  coba   1 000 000 conductance-based LIF neurons, 100 targets per neuron, 0.6 / 6.7, constant bias
+         tuned to about 10 Hz
   large  8 000 000 LIF neurons, 1000 targets per neuron (8e9 synapses), lognormal(-2, 0.5)
          weights signed by population (inhibition x6), hashed background drive
 ``--neurons`` / ``--targets`` override the preset's size.  With several ranks the
@@ -32,12 +33,13 @@ def main():
     ap.add_argument('--steps', type=int, default=1000)
     ap.add_argument('--warmup', type=int, default=100)
     ap.add_argument('--exchange', default='p2p', choices=['p2p', 'nccl'])
+    ap.add_argument('--deterministic', action='store_true', help='fixed-point synaptic sums: order-free rasters')
     ap.add_argument('--record', action='store_true', help='keep the bit-packed raster (memory: steps * n / 8 bytes)')
     args = ap.parse_args()
 
     import torch
     import torch.distributed as dist
-    from brainstate_b200.sim import EINet, LIFParams, Lognormal
+    from brainstate_b200.sim import EINet, preset
 
     world = int(os.environ.get('WORLD_SIZE', '1'))
     rank = int(os.environ.get('RANK', '0'))
@@ -47,24 +49,18 @@ def main():
     if world > 1:
         dist.init_process_group('nccl', device_id=dev)
 
-    if args.preset == 'cuba':
-        n, K = args.neurons or 4000, args.targets or 80
-        params, w_e, w_i, seeds, v0 = LIFParams(), 1.62, -9.0, (100, 101, 102), (-60., -50.)
-    elif args.preset == 'coba':
-        n, K = args.neurons or 1000000, args.targets or 100
-        params, w_e, w_i, seeds, v0 = LIFParams(coba=True, R=0.1), 0.6, 6.7, (300, 301, 302), (-60., -50.)
-    else:
-        n, K = args.neurons or 8000000, args.targets or 1000
-        params = LIFParams(V_rest=-60., ext_rate_hz=9000., ext_weight=0.3, ext_seed=405)
-        w_e, w_i = Lognormal(-2.0, 0.5, 402, 1.0), Lognormal(-2.0, 0.5, 403, -6.0)
-        seeds, v0 = (400, 401, 404), (-65., -52.)
+    p = preset(args.preset)
+    params = p['params']
+    n = args.neurons or (p['n_exc'] + p['n_inh'])
+    K = args.targets or p['conn_num']
     n_exc = n * 4 // 5
     n_inh = n - n_exc
-    V0 = np.random.RandomState(seeds[2]).uniform(v0[0], v0[1], n).astype(np.float32)
+    V0 = np.random.RandomState(p['seed_v']).uniform(p['v0'][0], p['v0'][1], n).astype(np.float32)
 
     t0 = time.perf_counter()
-    net = EINet(n_exc, n_inh, K, w_e, w_i, seed_e=seeds[0], seed_i=seeds[1], V0=V0, params=params, device=dev,
-                group=dist.group.WORLD if world > 1 else None, exchange=args.exchange)
+    net = EINet(n_exc, n_inh, K, p['w_e'], p['w_i'], seed_e=p['seed_e'], seed_i=p['seed_i'], V0=V0, params=params,
+                device=dev, group=dist.group.WORLD if world > 1 else None, exchange=args.exchange,
+                deterministic=args.deterministic)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
     mem_gb = torch.cuda.max_memory_allocated(dev) / 1e9

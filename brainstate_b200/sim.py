@@ -11,8 +11,10 @@ the network and returns the bit-packed spike raster.
 On one GPU all steps of a ``run`` are one cooperative kernel launch.  With a
 process group the postsynaptic neurons are split into contiguous blocks, one per
 rank; every rank keeps the synapses that target its block (a CSR block drawn from
-the same seeded stream as the full matrix) and the ranks exchange one all-gather of
-the packed spike words per step.
+the same seeded stream as the full matrix).  The ranks exchange their spikes either
+inside the step kernel (``exchange='p2p'``: compact id lists pushed over NVLink, one
+launch per GPU for all steps) or with one NCCL all-gather of the packed spike words per
+step (``exchange='nccl'``, split-phase launches).
 """
 from __future__ import annotations
 
@@ -25,12 +27,12 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import BsxLifParams, BsxNet, check, lib
+from ._lib import BsxLifParams, BsxNet, BsxNetLinks, BsxNetShard, check, lib
 from .event import CSR, FixedPostNumConn
 from .nn._event_fixedprob import EventFixedProb, _device
 
 __all__ = ['LIFParams', 'Lognormal', 'EINet', 'shard_bounds', 'words_per_rank', 'sharded_block',
-           'build_projection', 'unpack_raster']
+           'build_projection', 'unpack_raster', 'preset', 'from_preset', 'population_rates', 'COBA_BIAS']
 
 
 @dataclass
@@ -199,15 +201,32 @@ class EINet:
         (``brainstate/nn/_delay.py:768-958``) for spike vectors.
     group : optional ``torch.distributed`` process group; with more than one rank
         the postsynaptic neurons are sharded.
+    exchange : ``'p2p'`` — the spike exchange is part of the step kernel (one launch per
+        GPU for all steps of a ``run``); ``'nccl'`` — one all-gather per step between
+        split-phase launches.
+    deterministic : accumulate the synaptic input in 2^-32 fixed point (64-bit integer
+        adds).  The sums are then independent of the order in which the GPU adds them, so
+        the raster of a network with heterogeneous weights is the same on every run, grid
+        and number of GPUs.  Uses the kernel of ``exchange='p2p'`` also on one GPU.
+    slack : with ``exchange='p2p'`` and both delays at least ``slack`` steps, spikes are
+        consumed ``slack`` steps after they were sent, which takes the NVLink latency off
+        the critical path.  Default: ``min(delay_e, delay_i)``.
+    conn : ``(conn_e, conn_i)`` of an ``EINet`` of the same network and shard: the projections
+        are shared instead of drawn again (a second network over the same synapses).
+    shard_kernel : on one GPU, ``True`` runs the kernel of ``exchange='p2p'`` (increment rows,
+        one grid-wide barrier per step whatever the delays) instead of the spike-list kernels.
     """
 
     def __init__(self, n_exc: int, n_inh: int, conn_num, w_e, w_i, *, seed_e: int, seed_i: int,
                  V0, params: Optional[LIFParams] = None, device=None, group=None, delay_e: int = 0,
-                 delay_i: int = 0, exchange: str = 'nccl'):
+                 delay_i: int = 0, exchange: str = 'p2p', deterministic: bool = False,
+                 slack: Optional[int] = None, shard_kernel: Optional[bool] = None, conn=None):
         if exchange not in ('nccl', 'p2p'):
             raise ValueError("exchange must be 'nccl' or 'p2p'")
         self.exchange = exchange
-        self._p2p = None
+        self.deterministic = bool(deterministic)
+        self._links = None
+        self._seq = 0
         self.delay_e, self.delay_i = int(delay_e), int(delay_i)
         self.ring = max(self.delay_e, self.delay_i) + 2
         self.n_exc, self.n_inh = int(n_exc), int(n_inh)
@@ -225,7 +244,11 @@ class EINet:
         self.conn_num = K
         dev = self.dev
         hetero = isinstance(w_e, Lognormal) or isinstance(w_i, Lognormal)
-        if self.world == 1 and not hetero and self.n * K < (1 << 31):
+        if conn is not None:
+            self.conn_e, self.conn_i = conn
+            if self.conn_e.shape != (self.n_exc, self.n_local) or self.conn_i.shape != (self.n_inh, self.n_local):
+                raise ValueError('conn: projections of another network or shard')
+        elif self.world == 1 and not hetero and self.n * K < (1 << 31):
             self.E = EventFixedProb(self.n_exc, self.n, K, float(w_e), seed=seed_e, device=dev)
             self.I = EventFixedProb(self.n_inh, self.n, K, float(w_i), seed=seed_i, device=dev)
             self.conn_e, self.conn_i = self.E.conn, self.I.conn
@@ -242,12 +265,31 @@ class EINet:
         self.words = (self.n + 31) // 32
         self.wpr = words_per_rank(self.n, self.world)
         self.bits = torch.zeros(self.wpr * self.world, dtype=torch.int32, device=dev)
-        self.lists = torch.zeros((self.ring, self.n + 1), dtype=torch.int32, device=dev)
         self.step_count = 0
         self._graphs = {}
         self._warmed = False
         self._pstruct = self.params.struct()
-        self._net = self._make_struct()
+        # which kernel family runs the steps: the shard kernel (state: ring of increment rows)
+        # or the spike-list kernels (state: ring of spike lists)
+        self.shard_kernel = (self.world > 1 and exchange == 'p2p') or self.deterministic
+        if shard_kernel is not None and self.world == 1 and not self.deterministic:
+            self.shard_kernel = bool(shard_kernel)       # one GPU: either family can run the network
+        if self.world > 1 and self.deterministic and exchange != 'p2p':
+            raise ValueError("deterministic=True on several GPUs needs exchange='p2p'")
+        dmin = min(self.delay_e, self.delay_i)
+        self.slack = dmin if slack is None else int(slack)
+        if not 0 <= self.slack <= dmin:
+            raise ValueError(f'slack must lie in [0, min(delay_e, delay_i)] = [0, {dmin}]')
+        if self.shard_kernel:
+            acc = torch.int64 if self.deterministic else torch.float32
+            self.incr_e = torch.zeros((self.ring, self.n_local), dtype=acc, device=dev)
+            self.incr_i = torch.zeros((self.ring, self.n_local), dtype=acc, device=dev)
+            self.lists = None
+            self._shard = self._make_shard_struct()
+            self._net = None
+        else:
+            self.lists = torch.zeros((self.ring, self.n + 1), dtype=torch.int32, device=dev)
+            self._net = self._make_struct()
 
     def _make_struct(self) -> BsxNet:
         s = BsxNet()
@@ -261,13 +303,25 @@ class EINet:
         s.ring, s.delay_e, s.delay_i = self.ring, self.delay_e, self.delay_i
         return s
 
+    def _make_shard_struct(self) -> BsxNetShard:
+        s = BsxNetShard()
+        s.n_global, s.n_exc, s.first, s.n_local = self.n, self.n_exc, self.first, self.n_local
+        self._se, self._si = self.conn_e._struct(), self.conn_i._struct()
+        s.exc, s.inh = self._se, self._si
+        s.V, s.g_e, s.g_i, s.ref = self.V.data_ptr(), self.g_e.data_ptr(), self.g_i.data_ptr(), self.ref.data_ptr()
+        s.incr_e, s.incr_i = self.incr_e.data_ptr(), self.incr_i.data_ptr()
+        s.bits = self.bits.data_ptr() + 4 * self.rank * self.wpr
+        s.ring, s.delay_e, s.delay_i = self.ring, self.delay_e, self.delay_i
+        s.fixed_point = int(self.deterministic)
+        return s
+
     # ------------------------------------------------------------------
     def run(self, steps: int, record: bool = True, blocks: int = 0):
         """Advances ``steps`` steps.  Returns ``(raster, counts)``: the packed spike
         words ``(steps, ceil(n/32))`` int32 (``None`` without ``record``) and the
         number of spikes of every step ``(steps,)`` int32."""
-        if self.world > 1 and self.exchange == 'p2p':
-            return self._run_p2p(steps, record, blocks)
+        if self.shard_kernel:
+            return self._run_shard_kernel(steps, record)
         if self.world > 1:
             return self._run_sharded(steps, record)
         dev = self.dev
@@ -306,6 +360,11 @@ class EINet:
         counts = torch.zeros(steps, dtype=torch.int32, device=dev)
         t = 0
         S = graph_steps - (graph_steps % self.ring)      # a whole number of turns of the list ring
+        # A captured launch carries its step number by value.  Replays are right only where the
+        # step enters through ``step % ring`` alone: no background drive (hashed from the step),
+        # and every delayed list already exists (the step - 1 - delay >= 0 tests are past).
+        if S >= self.ring and self.params.ext_threshold != 0:
+            raise ValueError('CUDA-graph replay of the sharded step is not available with a background drive')
         if S >= self.ring and steps >= 2 * S:
             if not self._warmed:       # NCCL and lazy module loading must have run before a capture
                 c0 = torch.zeros(2, dtype=torch.int32, device=dev)
@@ -318,6 +377,14 @@ class EINet:
                 t = 2
                 self._warmed = True
                 torch.cuda.synchronize()
+            while self.step_count <= max(self.delay_e, self.delay_i) + 1 and t < steps:   # eager until every list exists
+                c0 = torch.zeros(1, dtype=torch.int32, device=dev)
+                r0 = torch.empty((1, self.words), dtype=torch.int32, device=dev) if record else None
+                self._sharded_step(0, c0, r0)
+                counts[t:t + 1].copy_(c0)
+                if record:
+                    raster[t:t + 1].copy_(r0)
+                t += 1
             key = (S, record, self.step_count % self.ring)
             if key not in self._graphs:
                 gc = torch.zeros(S, dtype=torch.int32, device=dev)
@@ -358,102 +425,194 @@ class EINet:
         b = np.unpackbits(w.view(np.uint8), bitorder='little')[:self.n].astype(bool)
         return torch.from_numpy(b)
 
-    # -- exchange inside the kernel (peer stores over NVLink) ---------------------
-    def _setup_p2p(self):
-        """Allocates this rank's exchange buffer and progress counters, exports them to
-        the other ranks of the node and maps theirs (CUDA IPC; one-time)."""
-        import torch.distributed as dist
-        from ._lib import BsxNetPeers
+    # -- shard kernel: exchange inside the step kernel (peer stores over NVLink) --------
+    def _setup_links(self):
+        """Launch geometry, the two synchronisation words and — with more than one rank — this
+        rank's inbox, exported to the other ranks of the node and theirs mapped (CUDA IPC;
+        one-time)."""
         l = lib()
-        words = self.wpr * self.world
-        bits_bytes = 2 * words * 4
-        flags_off = (bits_bytes + 255) // 256 * 256
-        total = flags_off + 256 + 256                     # counters (world x int64), status word
-        base = C.c_void_p()
-        handle = C.create_string_buffer(64)
-        check(l.bsx_ipc_alloc(total, C.byref(base), handle))
-        handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(handle.raw), group=self.group)
-        ptrs, opened = [], []
-        for r in range(self.world):
-            if r == self.rank:
-                ptrs.append(base.value)
-            else:
-                q = C.c_void_p()
-                check(l.bsx_ipc_open(C.create_string_buffer(handles[r], 64), C.byref(q)))
-                ptrs.append(q.value)
-                opened.append(q.value)
-        peers = BsxNetPeers()
-        peers.world, peers.rank, peers.words_per_rank, peers.spin_limit = self.world, self.rank, self.wpr, 0
-        for r in range(self.world):
-            peers.bits[r] = ptrs[r]
-            peers.flags[r] = ptrs[r] + flags_off
-        peers.status = base.value + flags_off + 256
-        self._p2p = {'peers': peers, 'base': base.value, 'opened': opened, 'status_ptr': base.value + flags_off + 256}
-        dist.barrier(group=self.group)                    # every rank has mapped every buffer
+        blocks, wpb = C.c_int32(0), C.c_int32(0)
+        check(l.bsx_net_shard_geometry(self.wpr, C.byref(blocks), C.byref(wpb)))
+        links = BsxNetLinks()
+        links.world, links.rank = self.world, self.rank
+        links.blocks, links.words_per_block, links.words_per_rank = blocks.value, wpb.value, self.wpr
+        links.slack, links.slots = (self.slack if self.world > 1 else 0), 2 * self.slack + 2
+        links.spin_limit = 0
+        sync = torch.zeros(2, dtype=torch.int32, device=self.dev)
+        links.sync = sync.data_ptr()
+        state = {'links': links, 'sync': sync, 'base': None, 'opened': []}
+        if self.world > 1:
+            import torch.distributed as dist
+            nbytes = l.bsx_net_inbox_bytes(self.world, blocks.value, wpb.value, links.slots)
+            base = C.c_void_p()
+            handle = C.create_string_buffer(64)
+            check(l.bsx_ipc_alloc(nbytes, C.byref(base), handle))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle.raw), group=self.group)
+            for r in range(self.world):
+                if r == self.rank:
+                    links.inbox[r] = base.value
+                else:
+                    q = C.c_void_p()
+                    check(l.bsx_ipc_open(C.create_string_buffer(handles[r], 64), C.byref(q)))
+                    links.inbox[r] = q.value
+                    state['opened'].append(q.value)
+            state['base'] = base.value
+            dist.barrier(group=self.group)                # every rank has mapped every inbox
+        self._links = state
+        self._seq = 0
 
-    def _run_p2p(self, steps: int, record: bool, blocks: int = 0):
-        """All steps of all ranks in one cooperative launch per GPU; the spike words
-        travel by peer stores inside the kernel."""
-        import torch.distributed as dist
-        if self._p2p is None:
-            self._setup_p2p()
-        # the kernels of all ranks wait for one another with a bounded patience (about a
-        # second): line the hosts up first so that none of them launches much later
-        dist.barrier(group=self.group)
+    def _run_shard_kernel(self, steps: int, record: bool):
+        """All steps in one cooperative launch per GPU; the spike ids travel by peer stores
+        inside the kernel.  The raster of the whole network is assembled from the ranks'
+        words after the launch."""
+        if self._links is None:
+            self._setup_links()
         dev = self.dev
-        raster = torch.empty((steps, self.words), dtype=torch.int32, device=dev) if record else None
+        if self.world > 1:
+            import torch.distributed as dist
+            # the kernels of all ranks wait for one another with a bounded patience (about a
+            # second): line the hosts up first so that none of them launches much later
+            dist.barrier(group=self.group)
+        words_local = (self.n_local + 31) // 32
+        mine = torch.empty((steps, words_local), dtype=torch.int32, device=dev) if record else None
         counts = torch.empty(steps, dtype=torch.int32, device=dev)
-        check(lib().bsx_net_run_p2p(C.byref(self._net), C.byref(self._pstruct), C.byref(self._p2p['peers']), steps,
-                                    self.step_count, _lib.ptr(raster), counts.data_ptr(), blocks,
-                                    _lib.current_stream()))
+        links = self._links['links']
+        links.seq0 = self._seq
+        check(lib().bsx_net_run_sharded(C.byref(self._shard), C.byref(self._pstruct), C.byref(links), steps,
+                                        self.step_count, _lib.ptr(mine), counts.data_ptr(), _lib.current_stream()))
         host = C.c_int32(0)
-        check(lib().bsx_read_status(self._p2p['status_ptr'], C.byref(host), _lib.current_stream()))
+        check(lib().bsx_read_status(self._links['sync'].data_ptr(), C.byref(host), _lib.current_stream()))
         if host.value != 0:
+            self._drop_links()
             raise RuntimeError('the multi-GPU step kernel gave up waiting for a peer '
-                               f'({lib().bsx_status_name(host.value).decode()}); the run stopped early')
+                               f'({lib().bsx_status_name(host.value).decode()}); the run stopped early and '
+                               'the exchange buffers were dropped')
         self.step_count += steps
+        self._seq += steps
+        if self.world == 1:
+            return mine, counts
+        import torch.distributed as dist
+        mine_bits = self.bits[self.rank * self.wpr:(self.rank + 1) * self.wpr]
+        dist.all_gather_into_tensor(self.bits, mine_bits.clone(), group=self.group)   # latest step, whole network
+        raster = None
+        if record:
+            padded = torch.zeros((steps, self.wpr), dtype=torch.int32, device=dev)
+            padded[:, :words_local] = mine
+            parts = torch.empty((self.world, steps, self.wpr), dtype=torch.int32, device=dev)
+            dist.all_gather_into_tensor(parts, padded, group=self.group)
+            raster = parts.permute(1, 0, 2).reshape(steps, self.world * self.wpr)[:, :self.words].contiguous()
         return raster, counts
+
+    def _drop_links(self):
+        if self._links is None:
+            return
+        for q in self._links['opened']:
+            lib().bsx_ipc_close(q)
+        if self._links['base'] is not None:
+            lib().bsx_ipc_free(self._links['base'])
+        self._links = None
 
     def close(self):
         """Drops the captured CUDA graphs and the peer mappings.  Call it before the
         process group is destroyed: a live graph that holds captured collectives keeps
         the communicator busy and the teardown waits for it."""
-        if self._p2p is not None:
+        if self._links is not None and self.world > 1:
             import torch.distributed as dist
             torch.cuda.synchronize()
             dist.barrier(group=self.group)                # nobody still writes into a buffer about to go
-            for q in self._p2p['opened']:
+            for q in self._links['opened']:
                 lib().bsx_ipc_close(q)
+            self._links['opened'] = []
             dist.barrier(group=self.group)
-            lib().bsx_ipc_free(self._p2p['base'])
-            self._p2p = None
+        self._drop_links()
         self._graphs.clear()
         import gc
         gc.collect()
         torch.cuda.synchronize()
 
     # -- checkpoint / resume --------------------------------------------------
+    _STATE = ('V', 'g_e', 'g_i', 'ref', 'delta_e', 'delta_i', 'bits', 'lists', 'incr_e', 'incr_i')
+
+    def _meta(self) -> dict:
+        return {'n_exc': self.n_exc, 'n_inh': self.n_inh, 'conn_num': self.conn_num, 'ring': self.ring,
+                'first': self.first, 'n_local': self.n_local, 'shard_kernel': self.shard_kernel,
+                'deterministic': self.deterministic}
+
     def state_dict(self) -> dict:
         """Everything a resumed run needs that cannot be regenerated: the rank's neuron
-        state, the pending spike lists and the step counter.  The connectivity is not
-        stored; like the reference (whose index arrays are plain attributes, not
-        states, ``brainstate/nn/_event_fixedprob.py:181``) it is rebuilt from the seeds."""
-        return {'V': self.V.clone(), 'g_e': self.g_e.clone(), 'g_i': self.g_i.clone(), 'ref': self.ref.clone(),
-                'delta_e': self.delta_e.clone(), 'delta_i': self.delta_i.clone(), 'bits': self.bits.clone(),
-                'lists': self.lists.clone(), 'step': self.step_count,
-                'meta': {'n_exc': self.n_exc, 'n_inh': self.n_inh, 'conn_num': self.conn_num, 'ring': self.ring,
-                         'first': self.first, 'n_local': self.n_local}}
+        state, the pending synaptic input (spike lists, or increment rows with the shard
+        kernel) and the step counter.  The connectivity is not stored; like the reference
+        (whose index arrays are plain attributes, not states,
+        ``brainstate/nn/_event_fixedprob.py:181``) it is rebuilt from the seeds."""
+        sd = {k: getattr(self, k).clone() for k in self._STATE if getattr(self, k, None) is not None}
+        sd['step'] = self.step_count
+        sd['meta'] = self._meta()
+        return sd
 
     def load_state_dict(self, sd: dict):
-        m = sd['meta']
-        mine = {'n_exc': self.n_exc, 'n_inh': self.n_inh, 'conn_num': self.conn_num, 'ring': self.ring,
-                'first': self.first, 'n_local': self.n_local}
-        if m != mine:
-            raise ValueError(f'checkpoint of a different network or shard: {m} vs {mine}')
-        for k in ('V', 'g_e', 'g_i', 'ref', 'delta_e', 'delta_i', 'bits', 'lists'):
-            getattr(self, k).copy_(sd[k])
+        """Restores a checkpoint of the same network, shard and kernel family.  The exchange
+        sequence number of the inboxes is NOT rewound: it counts what went through them, not
+        the simulation step."""
+        if sd['meta'] != self._meta():
+            raise ValueError(f"checkpoint of a different network or shard: {sd['meta']} vs {self._meta()}")
+        for k in self._STATE:
+            if getattr(self, k, None) is not None:
+                getattr(self, k).copy_(sd[k])
         self.step_count = int(sd['step'])
+
+
+# Constant bias current of the 'coba' preset (same unit as a conductance times a potential:
+# with R = 0.1 the membrane sees R * I = 16.6 mV above rest).  Chosen so that the mean rate
+# over the 1000 steps (100 ms) from the seeded start is 10 Hz: the CPU restatement gives
+# 10.03 Hz on a 100 000-neuron copy of the network (9.6 Hz at 160, 10.3 Hz at 172).
+COBA_BIAS = 166.0
+
+
+def preset(name: str) -> dict:
+    """The three network recipes, as keyword material for :class:`EINet`:
+
+    cuba   4 000 current-based LIF neurons, p = 0.02 (80 targets), weights +1.62 / -9 mV,
+           V_rest -49 mV above V_th -50 mV (self-active), V0 ~ U(-60, -50), seeds 100-102
+           (``examples/400_CUBA_2005_bpu.py:36-58`` with its constants)
+    coba   1 000 000 conductance-based LIF neurons (800k E / 200k I), 100 targets per neuron,
+           g 0.6 / 6.7, E_e 0, E_i -80 mV, V_rest -60 mV, constant bias ``COBA_BIAS`` giving
+           about 10 Hz, V0 ~ U(-60, -50), seeds 300-302
+    large  8 000 000 LIF neurons, 1000 targets per neuron (8e9 synapses), lognormal(-2, 0.5)
+           weights signed by population (inhibition x6), hashed background drive giving
+           about 5 Hz, seeds 400-405
+    """
+    if name == 'cuba':
+        return dict(n_exc=3200, n_inh=800, conn_num=80, w_e=1.62, w_i=-9.0, params=LIFParams(), seed_e=100,
+                    seed_i=101, seed_v=102, v0=(-60., -50.))
+    if name == 'coba':
+        return dict(n_exc=800000, n_inh=200000, conn_num=100, w_e=0.6, w_i=6.7,
+                    params=LIFParams(coba=True, R=0.1, V_rest=-60., E_e=0., E_i=-80., tau_e=5., tau_i=10.,
+                                     I_ext=COBA_BIAS),
+                    seed_e=300, seed_i=301, seed_v=302, v0=(-60., -50.))
+    if name == 'large':
+        return dict(n_exc=6400000, n_inh=1600000, conn_num=1000, w_e=Lognormal(-2.0, 0.5, 402, 1.0),
+                    w_i=Lognormal(-2.0, 0.5, 403, -6.0),
+                    params=LIFParams(V_rest=-60., ext_rate_hz=9000., ext_weight=0.3, ext_seed=405),
+                    seed_e=400, seed_i=401, seed_v=404, v0=(-65., -52.))
+    raise ValueError(f'unknown preset {name!r}')
+
+
+def from_preset(name: str, device=None, group=None, scale: float = 1.0, **kw) -> 'EINet':
+    """Builds the network of :func:`preset` (``scale`` shrinks both populations)."""
+    p = preset(name)
+    n_exc, n_inh = int(p['n_exc'] * scale), int(p['n_inh'] * scale)
+    V0 = np.random.RandomState(p['seed_v']).uniform(p['v0'][0], p['v0'][1], n_exc + n_inh).astype(np.float32)
+    return EINet(n_exc, n_inh, p['conn_num'], p['w_e'], p['w_i'], seed_e=p['seed_e'], seed_i=p['seed_i'], V0=V0,
+                 params=p['params'], device=device, group=group, **kw)
+
+
+def population_rates(counts_or_raster, n_exc: int, n_inh: int, dt_ms: float):
+    """Mean firing rates in Hz of the excitatory and the inhibitory population from a packed
+    raster ``(steps, words)`` (ids below ``n_exc`` are excitatory)."""
+    r = unpack_raster(counts_or_raster, n_exc + n_inh)
+    seconds = r.shape[0] * dt_ms * 1e-3
+    return float(r[:, :n_exc].sum() / max(n_exc, 1) / seconds), float(r[:, n_exc:].sum() / max(n_inh, 1) / seconds)
 
 
 def unpack_raster(raster: torch.Tensor, n: int) -> np.ndarray:

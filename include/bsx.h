@@ -174,23 +174,15 @@ size_t bsx_event_vecmat_workspace_bytes(int64_t batch, int64_t n_pre);
 int bsx_event_vecmat(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                      float* out, int accumulate, void* workspace, size_t workspace_bytes,
                      bsx_stream_t stream);
-/* Same, with explicit launch geometry for tuning: entries per work item of a
- * fixed-number row, and resident blocks per SM of the global-atomic kernel.
- * blocks_per_sm = -1 asks for the variant that accumulates output slices of
- * 32768 columns in shared memory wherever it applies (batch >= 16, n_post <=
- * 131072).  With both at 0 (what bsx_event_vecmat passes) the library chooses:
- * the shared-memory variant when batch * slices is at least 3/4 of the SM count
- * and n_post <= 65536, the global-atomic kernel otherwise.  Any positive value
- * keeps the global-atomic kernel. */
-int bsx_event_vecmat_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
-                           float* out, int accumulate, void* workspace, size_t workspace_bytes,
-                           int chunk, int blocks_per_sm, bsx_stream_t stream);
 /* Which kernel bsx_event_vecmat runs for this connectivity, spike format and batch:
  * BSX_VECMAT_GLOBAL_ATOMICS (compaction launch + scatter launch, uses the workspace) or
  * BSX_VECMAT_SHARED_SLICES (one launch, workspace untouched).  Negative on invalid input. */
 #define BSX_VECMAT_GLOBAL_ATOMICS 0
 #define BSX_VECMAT_SHARED_SLICES 1
 int bsx_event_vecmat_variant(const bsx_conn_t* conn, int spike_format, int64_t batch);
+/* Kernel launches one bsx_event_vecmat call of this shape enqueues (a diagnostic for
+ * callers that budget launch latency, e.g. one spike vector per simulation step). */
+int bsx_event_vecmat_launches(const bsx_conn_t* conn, int spike_format, int64_t batch);
 
 /*
  * Sliced layout for the shared-memory variant.  No counterpart in the reference: a
@@ -260,16 +252,6 @@ int bsx_float_vecmat(const bsx_conn_t* conn, const float* x, int64_t batch, floa
 size_t bsx_event_matvec_workspace_bytes(int64_t batch, int64_t n_post);
 int bsx_event_matvec(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                      float* out, void* workspace, size_t workspace_bytes, bsx_stream_t stream);
-/* Same, with explicit launch geometry for tuning (0 = default).  mask_mode: 1 spike
- * words staged in shared memory by a bulk-async (TMA) copy, 2 staged by ordinary
- * loads, 3 read from global memory, 4 one pass per vector even when batched;
- * batched passes only: 5 stream heterogeneous weights with the indices, 6 fetch
- * them per hit (default: chosen on the device from the spike density).
- * unroll: 128-bit index loads in flight per lane (1, 2, 4 or 6). */
-int bsx_event_matvec_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
-                           float* out, void* workspace, size_t workspace_bytes, int blocks_per_sm,
-                           int mask_mode, int unroll, bsx_stream_t stream);
-
 /*
  * y = conn @ v for float v: y[b,i] = sum_k w[i,k] * v[b, idx[i,k]].
  * This is the input cotangent of the vecmat (transpose product used by jax.grad,
@@ -381,34 +363,90 @@ int bsx_net_update(const bsx_net_t* net, const bsx_lif_params_t* params, int64_t
                    bsx_stream_t stream);
 int bsx_net_list_from_bits(const bsx_net_t* net, int64_t step, bsx_stream_t stream);
 /*
- * Many steps on many GPUs with the exchange inside the kernel: each rank (one
- * process per GPU) launches this cooperative kernel on its part of the network.
- * After the neuron update a rank stores its packed spike words into every peer's
- * exchange buffer with plain stores over NVLink, fences at system scope and raises
- * its progress counter on every peer; it then waits (bounded) for all counters and
- * compacts the complete words into the spike list.  No collective library call and
- * no host round trip per step.  There is no counterpart in the reference, which
- * runs on one device.
- *   bits[r]   rank r's exchange buffer: 2 * world * words_per_rank uint32 (two
- *             step parities), zero before the first step
- *   flags[r]  rank r's progress counters: `world` int64, zero before the first step
- *   status    local int32, zero on entry; BSX_ERR_TIMEOUT after a wait of more than
- *             spin_limit polls (0 = default, about a second), in which case the
- *             kernel has stopped early at a step boundary
- * Rank r owns neurons [32*r*words_per_rank, ...) as in bsx_net_t.  All ranks must
- * call with the same steps and step0.
+ * One rank's shard of an E/I network for bsx_net_run_sharded.  Neurons and projections
+ * as in bsx_net_t (the rank owns neurons [first, first + n_local) and the synapses that
+ * target them; on one GPU first = 0 and n_local = n_global).  The pending synaptic input
+ * is kept as a ring of increment rows instead of a ring of spike lists:
+ *   incr_e, incr_i  (ring, n_local); row (s % ring) holds what step s will add to g_e /
+ *                   g_i and is cleared by that step.  A spike of step s from a projection
+ *                   with delay d lands in row (s + 1 + d) % ring.  This is the delay ring
+ *                   buffer of brainstate/nn/_delay.py:768-958 applied to the summed
+ *                   synaptic input.  Zero before step 0; part of the state afterwards.
+ *   fixed_point     0: float32 rows, atomic float adds (the last bit of a heterogeneous
+ *                   sum depends on the arrival order).  1: int64 rows holding
+ *                   round(w * 2^32) sums — integer addition is associative, so currents
+ *                   and rasters are identical for any grid, arrival order and number of
+ *                   GPUs; needs |sum of weights per neuron and step| < 2^31.
+ *   bits            (ceil(n_local/32)) the rank's spike words of the launch's last step; may be NULL
  */
-typedef struct bsx_net_peers {
+typedef struct bsx_net_shard {
+  int64_t n_global, n_exc, first, n_local;
+  bsx_conn_t exc, inh;
+  float* V;
+  float* g_e;
+  float* g_i;
+  int32_t* ref;
+  void* incr_e;
+  void* incr_i;
+  uint32_t* bits;
+  int32_t ring;        /* >= max(delay_e, delay_i) + 2 */
+  int32_t delay_e;
+  int32_t delay_i;
+  int32_t fixed_point;
+} bsx_net_shard_t;
+
+/*
+ * How the ranks of one node reach each other.  No counterpart in the reference, which
+ * runs on one device.  Every rank launches the same grid (bsx_net_shard_geometry, from
+ * words_per_rank): block b of rank r owns spike words [b * words_per_block, ...) of the
+ * rank.  After its update, block b pushes the ids of its neurons that spiked into every
+ * peer's inbox with plain 64-bit stores over NVLink (peer memory mapped by CUDA IPC);
+ * each word is (tag << 32 | payload) with tag = low 32 bits of (exchange sequence number
+ * + 1), the first word of a list carrying the count, so a reader knows a word is current
+ * by its tag alone: no fence, no separate flag, no collective call and no host round
+ * trip per step.
+ *   inbox[r]   rank r's inbox as addressable from THIS rank (inbox[rank] is local):
+ *              bsx_net_inbox_bytes() bytes, zero at set-up, laid out
+ *              [slot][source rank][source block][1 + 32 * words_per_block] uint64
+ *   slots      inbox ring depth, at least 2 * slack + 2
+ *   slack      0 <= slack <= min(delay_e, delay_i): a block consumes at step s the lists
+ *              of step s - slack, so with delayed synapses the NVLink latency is off the
+ *              critical path; the last `slack` lists are drained before the launch ends
+ *   seq0       exchange sequence number of the launch's first step: the number of steps
+ *              exchanged through these inboxes so far.  It only grows (restoring an
+ *              earlier simulation step does not rewind it); equal on all ranks
+ *   sync       two local int32: [0] status word, zero on entry, BSX_ERR_TIMEOUT after a
+ *              wait of more than spin_limit polls (0 = default, about a second) — the
+ *              launch then stops at a step boundary and the inboxes must be set up again;
+ *              [1] barrier counter, managed by the call
+ * With world = 1 no inbox is read.  All ranks must call with the same steps, step0, seq0.
+ */
+typedef struct bsx_net_links {
   int32_t world, rank;
+  int32_t blocks, words_per_block;
   int64_t words_per_rank;
+  int32_t slots, slack;
   int64_t spin_limit;
-  uint32_t* bits[16];
-  int64_t* flags[16];
-  int32_t* status;
-} bsx_net_peers_t;
-int bsx_net_run_p2p(const bsx_net_t* net, const bsx_lif_params_t* params, const bsx_net_peers_t* peers,
-                    int32_t steps, int64_t step0, uint32_t* raster, int32_t* spike_counts, int32_t blocks,
-                    bsx_stream_t stream);
+  int64_t seq0;
+  uint64_t* inbox[16];
+  int32_t* sync;
+} bsx_net_links_t;
+/* Grid every rank must launch for shards of words_per_rank spike words (one block per SM
+ * at most, at least one word per warp). */
+int bsx_net_shard_geometry(int64_t words_per_rank, int32_t* blocks, int32_t* words_per_block);
+size_t bsx_net_inbox_bytes(int32_t world, int32_t blocks, int32_t words_per_block, int32_t slots);
+/*
+ * Runs steps [step0, step0 + steps) of the shard in ONE cooperative launch: neuron state
+ * resident in shared memory (shards of up to about two million neurons; in global memory
+ * beyond), one grid-wide barrier per step whatever the delays, the exchange inside the
+ * kernel.  Fuses what the reference runs as separate operators per step
+ * (examples/400_CUBA_2005_bpu.py:60-66).  raster (may be NULL): (steps, ceil(n_local/32))
+ * the RANK's spike words; spike_counts (may be NULL): (steps) spikes of the WHOLE network
+ * per step (own count plus the counts of the received lists), overwritten.
+ */
+int bsx_net_run_sharded(const bsx_net_shard_t* net, const bsx_lif_params_t* params, const bsx_net_links_t* links,
+                        int32_t steps, int64_t step0, uint32_t* raster, int32_t* spike_counts,
+                        bsx_stream_t stream);
 /* Set-up helpers for the buffers above (the only allocating entry points; never on
  * the hot path): allocate zeroed device memory with a 64-byte handle another process
  * on the node can open; open / close a peer's handle; free. */

@@ -30,6 +30,7 @@
  */
 #include <stdint.h>
 #include <stddef.h>
+#include <stdlib.h>
 #include <string.h>
 #ifdef _OPENMP
 #include <omp.h>
@@ -136,22 +137,92 @@ void orc_float_vecmat(const float* x, int64_t batch, int64_t n_pre, int64_t n_po
     }
 }
 
+/* With at least as many vectors as threads (and for small matrices) each thread takes whole
+ * vectors and sums sequentially in (row, k) order.  With fewer vectors of a large matrix the
+ * active rows of one vector are split over the threads, every thread adding into a private
+ * copy of the output that is then summed column-wise in thread order, so that all cores
+ * work on a single vector too (sums then differ from the sequential order within float32
+ * rounding). */
 void orc_event_vecmat_u8(const uint8_t* spk, int64_t batch, int64_t n_pre, int64_t n_post, int64_t K,
                          const int64_t* indptr, const int32_t* idx, const float* w, int hetero,
                          float* y) {
+    int nt = 1;
+#ifdef _OPENMP
+    nt = omp_get_max_threads();
+#endif
+    const int64_t nnz_all = indptr ? indptr[n_pre] : n_pre * K;
+    if (batch >= nt || nt == 1 || nnz_all < ((int64_t)1 << 22)) {
 #pragma omp parallel for schedule(dynamic, 1)
+        for (int64_t b = 0; b < batch; ++b) {
+            float* yb = y + b * n_post;
+            memset(yb, 0, (size_t)n_post * sizeof(float));
+            const uint8_t* sb = spk + b * n_pre;
+            for (int64_t i = 0; i < n_pre; ++i) {
+                if (!sb[i]) continue;
+                int64_t s, e;
+                row_range(indptr, K, i, &s, &e);
+                if (hetero) for (int64_t p = s; p < e; ++p) yb[idx[p]] += w[p];
+                else { float v = w[0]; for (int64_t p = s; p < e; ++p) yb[idx[p]] += v; }
+            }
+        }
+        return;
+    }
+    float* priv = (float*)malloc((size_t)nt * (size_t)n_post * sizeof(float));
+    int32_t* act = (int32_t*)malloc((size_t)(n_pre > 0 ? n_pre : 1) * sizeof(int32_t));
     for (int64_t b = 0; b < batch; ++b) {
-        float* yb = y + b * n_post;
-        memset(yb, 0, (size_t)n_post * sizeof(float));
         const uint8_t* sb = spk + b * n_pre;
-        for (int64_t i = 0; i < n_pre; ++i) {
-            if (!sb[i]) continue;
-            int64_t s, e;
-            row_range(indptr, K, i, &s, &e);
-            if (hetero) for (int64_t p = s; p < e; ++p) yb[idx[p]] += w[p];
-            else { float v = w[0]; for (int64_t p = s; p < e; ++p) yb[idx[p]] += v; }
+        float* yb = y + b * n_post;
+        int64_t na = 0;
+        for (int64_t i = 0; i < n_pre; ++i) if (sb[i]) act[na++] = (int32_t)i;
+#pragma omp parallel num_threads(nt)
+        {
+            int t = 0;
+#ifdef _OPENMP
+            t = omp_get_thread_num();
+#endif
+            float* mine = priv + (size_t)t * n_post;
+            memset(mine, 0, (size_t)n_post * sizeof(float));
+#pragma omp for schedule(static)
+            for (int64_t q = 0; q < na; ++q) {
+                int64_t s, e;
+                row_range(indptr, K, act[q], &s, &e);
+                if (hetero) for (int64_t p = s; p < e; ++p) mine[idx[p]] += w[p];
+                else { float v = w[0]; for (int64_t p = s; p < e; ++p) mine[idx[p]] += v; }
+            }
+#pragma omp for schedule(static)
+            for (int64_t j = 0; j < n_post; ++j) {
+                float acc = 0.0f;
+                for (int u = 0; u < nt; ++u) acc += priv[(size_t)u * n_post + j];
+                yb[j] = acc;
+            }
         }
     }
+    free(priv);
+    free(act);
+}
+
+/* Transposed (column-major) copy of a connectivity by counting sort: for every column j
+ * the rows that target it in ascending (row, k) order; t_perm[p] = position of the entry in
+ * the original arrays.  One-time, like the device's transposed copy; W @ spike is then the
+ * event-driven scatter orc_event_vecmat_u8 over (t_indptr, t_rows, w[t_perm]). */
+void orc_transpose(int64_t n_pre, int64_t n_post, int64_t K, const int64_t* indptr, const int32_t* idx,
+                   int64_t* t_indptr, int32_t* t_rows, int64_t* t_perm) {
+    int64_t nnz = indptr ? indptr[n_pre] : n_pre * K;
+    memset(t_indptr, 0, (size_t)(n_post + 1) * sizeof(int64_t));
+    for (int64_t p = 0; p < nnz; ++p) t_indptr[idx[p] + 1]++;
+    for (int64_t j = 0; j < n_post; ++j) t_indptr[j + 1] += t_indptr[j];
+    int64_t* fill = (int64_t*)malloc((size_t)(n_post > 0 ? n_post : 1) * sizeof(int64_t));
+    memcpy(fill, t_indptr, (size_t)n_post * sizeof(int64_t));
+    for (int64_t i = 0; i < n_pre; ++i) {
+        int64_t s, e;
+        row_range(indptr, K, i, &s, &e);
+        for (int64_t p = s; p < e; ++p) {
+            int64_t q = fill[idx[p]]++;
+            t_rows[q] = (int32_t)i;
+            t_perm[q] = p;
+        }
+    }
+    free(fill);
 }
 
 /* y[b,i] = sum_k w[i,k] * a[b, idx[i,k]];  a = v or [v != 0]. */

@@ -125,6 +125,19 @@ def event_matvec_u8(spk, idx, w, n_pre, indptr=None):
     return y.reshape(spk.shape[:-1] + (n_pre,))
 
 
+def transpose(idx, n_pre, n_post, indptr=None):
+    """Column-major copy: ``(t_indptr int64 (n_post+1,), t_rows int32 (nnz,), t_perm int64 (nnz,))``."""
+    idx = np.ascontiguousarray(idx, np.int32)
+    K = idx.size // max(n_pre, 1) if indptr is None else 0
+    ip = None if indptr is None else np.ascontiguousarray(indptr, np.int64)
+    t_indptr = np.empty(n_post + 1, np.int64)
+    t_rows = np.empty(idx.size, np.int32)
+    t_perm = np.empty(idx.size, np.int64)
+    lib().orc_transpose(C.c_int64(n_pre), C.c_int64(n_post), C.c_int64(K), _p(ip, C.c_int64), _p(idx, C.c_int32),
+                        _p(t_indptr, C.c_int64), _p(t_rows, C.c_int32), _p(t_perm, C.c_int64))
+    return t_indptr, t_rows, t_perm
+
+
 def vecmat_dw(x, ct, idx, n_pre, n_post, indptr=None, event=False):
     x = np.ascontiguousarray(x, np.float32).reshape(-1, n_pre)
     ct = np.ascontiguousarray(ct, np.float32).reshape(-1, n_post)

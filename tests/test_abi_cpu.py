@@ -23,7 +23,8 @@ def test_every_declared_symbol_is_exported_and_bound(bsx):
     for name in names:
         assert hasattr(bsx, name), f'{name} declared in include/bsx.h but not exported'
         assert name in _lib.SIGNATURES, f'{name} has no ctypes signature'
-    assert set(_lib.SIGNATURES) <= set(names)
+    assert set(_lib.SIGNATURES) - set(_lib.INTERNAL) <= set(names)
+    assert not set(_lib.INTERNAL) & set(names), 'tuning hooks do not belong in the public header'
     assert bsx.bsx_version() == 100
 
 
@@ -137,3 +138,37 @@ def test_product_path_does_not_import_the_oracle():
             if f.endswith(('.py', '.cu', '.cuh', '.h')):
                 text = open(os.path.join(dirpath, f)).read()
                 assert 'oracle' not in text.replace('c_oracle', 'oracle') or f == 'never', (dirpath, f)
+
+
+def test_shard_kernel_entry_point_validates_on_the_host(bsx):
+    """bsx_net_run_sharded rejects inconsistent descriptions before anything is launched
+    (no device is needed for these paths)."""
+    from brainstate_b200._lib import BsxNetShard, BsxNetLinks, BsxLifParams, BSX_ERR_INVALID_ARG
+    net, links, par = BsxNetShard(), BsxNetLinks(), BsxLifParams()
+    call = lambda: bsx.bsx_net_run_sharded(C.byref(net), C.byref(par), C.byref(links), 10, 0, None, None, None)
+    assert bsx.bsx_net_run_sharded(None, C.byref(par), C.byref(links), 1, 0, None, None, None) == BSX_ERR_INVALID_ARG
+    assert call() == BSX_ERR_INVALID_ARG and b'sizes' in bsx.bsx_last_error_string()
+    net.n_global, net.n_exc, net.first, net.n_local = 640, 512, 0, 640
+    net.exc.n_pre, net.exc.n_post, net.inh.n_pre, net.inh.n_post = 512, 640, 128, 640
+    buf = (C.c_float * 4)()
+    for f in ('V', 'g_e', 'g_i', 'ref', 'incr_e', 'incr_i'):
+        setattr(net, f, C.addressof(buf))
+    net.ring, net.delay_e, net.delay_i = 2, 3, 1
+    assert call() == BSX_ERR_INVALID_ARG and b'increment ring' in bsx.bsx_last_error_string()
+    net.ring = 5
+    links.world, links.rank = 17, 0
+    assert call() == BSX_ERR_INVALID_ARG and b'world' in bsx.bsx_last_error_string()
+    links.world, links.rank = 2, 0
+    assert call() == BSX_ERR_INVALID_ARG and b'sync' in bsx.bsx_last_error_string()
+    links.sync = C.addressof(buf)
+    links.blocks, links.words_per_block, links.words_per_rank = 1, 8, 20
+    assert call() == BSX_ERR_INVALID_ARG and b'words_per_block' in bsx.bsx_last_error_string()
+    links.blocks, links.words_per_block = 1, 32
+    links.slack = 2                                           # above min(delay) = 1
+    assert call() == BSX_ERR_INVALID_ARG and b'slack' in bsx.bsx_last_error_string()
+    links.slack, links.slots = 1, 3                           # needs 2 * slack + 2
+    assert call() == BSX_ERR_INVALID_ARG and b'slots' in bsx.bsx_last_error_string()
+    links.slots = 4
+    assert call() == BSX_ERR_INVALID_ARG and b'inbox' in bsx.bsx_last_error_string()
+    assert bsx.bsx_net_inbox_bytes(2, 3, 32, 4) == 4 * 2 * 3 * (1 + 32 * 32) * 8
+    assert bsx.bsx_net_inbox_bytes(0, 3, 32, 4) == 0

@@ -514,9 +514,9 @@ def test_transposed_weights_follow_the_weight_tensor(cuda):
     spk = np.random.RandomState(44).random_sample(n_post) < 0.2
     ts = torch.from_numpy(spk).to(cuda)
     close(event_matvec(conn, ts, method='scatter'), eo.event_matvec(spk, idx, w, n_pre))
-    kept = conn._t_weights[1]
+    kept = conn._derived['w_t'][1]
     event_matvec(conn, ts, method='scatter')
-    assert conn._t_weights[1] is kept                                   # no second permutation
+    assert conn._derived['w_t'][1] is kept                                   # no second permutation
     conn.data.mul_(2.0)                                                 # optimiser-style in-place step
     close(event_matvec(conn, ts, method='scatter'), eo.event_matvec(spk, idx, 2 * w, n_pre))
     w3 = (3 * w).astype(np.float32)
@@ -661,9 +661,36 @@ def test_large_batches_take_the_sliced_copy(cuda):
     assert _lib.lib().bsx_event_vecmat_variant(C.byref(st), _lib.SPK_BOOL8, B) == _lib.VECMAT_SHARED_SLICES
     assert _lib.lib().bsx_event_vecmat_variant(C.byref(st), _lib.SPK_BOOL8, 8) == _lib.VECMAT_GLOBAL_ATOMICS
     y = EventArray(ts) @ conn
-    assert conn._sliced is not None
+    assert 'sliced' in conn._derived
     close(y, eo.event_vecmat(spk, idx, w, n))
     close(y[:8], (EventArray(ts[:8]) @ conn).cpu().numpy())
     z = event_matvec(conn, ts, method='scatter')
-    assert conn._t_groups is not None
+    assert 't_groups' in conn._derived
     close(z, eo.event_matvec(spk, idx, w, n))
+
+
+def test_layer_calls_build_the_derived_layouts_once(cuda):
+    """``FixedNumConn.update`` goes through ``conn.with_data(weight)`` on every call
+    (``brainstate/nn/_event_fixedprob.py:204``): the views share the derived layouts of the
+    layer's connectivity, so the transposed and the sliced copy — and the permuted weights,
+    as long as the weight tensor is unchanged — are built by the first call only."""
+    from brainstate_b200.nn import EventFixedProb
+    n, K, B = 3000, 41, 160
+    w = np.random.RandomState(71).uniform(0.05, 0.15, (n, K)).astype(np.float32)
+    layer = EventFixedProb(n, n, K, w, seed=70)
+    idx = layer.conn.indices.cpu().numpy()
+    spk = np.random.RandomState(72).random_sample((B, n)) < 0.03
+    ts = torch.from_numpy(spk).to(cuda)
+    ref = eo.event_vecmat(spk, idx, w, n)
+    close(layer(ts), ref)                                   # batch fills the GPU: sliced copy
+    sliced, w_s = layer.conn._derived['sliced'], layer.conn._derived['w_s'][1]
+    close(layer(ts), ref)
+    assert layer.conn._derived['sliced'] is sliced and layer.conn._derived['w_s'][1] is w_s
+    layer.method = 'gather'                                 # deterministic form: transposed copy
+    close(layer(ts[:3]), ref[:3])
+    t, w_t = layer.conn._derived['transposed'], layer.conn._derived['w_t'][1]
+    close(layer(ts[:3]), ref[:3])
+    assert layer.conn._derived['transposed'] is t and layer.conn._derived['w_t'][1] is w_t
+    layer.weight.value.mul_(2.0)                            # an in-place update refreshes the weights only
+    close(layer(ts[:3]), 2 * ref[:3])
+    assert layer.conn._derived['transposed'] is t and layer.conn._derived['w_t'][1] is not w_t

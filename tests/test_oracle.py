@@ -168,3 +168,47 @@ def test_network_oracle_is_self_active_and_deterministic():
     for nid in np.unique(i)[:20]:
         ts = t[i == nid]
         assert np.all(np.diff(ts) > 50)
+
+
+def test_exprel_f32_is_within_one_ulp_of_float64():
+    """The exponential factor of the conductance-based step: the float32 Horner polynomial
+    used for |z| <= 0.125 (on the device and in the oracle, operation for operation) and the
+    float64 branch beyond stay within one float32 ulp of expm1(z)/z."""
+    pieces = [np.linspace(-0.125, 0.125, 400001), np.linspace(-0.5, -0.125, 50001), np.linspace(0.125, 0.5, 50001),
+              np.linspace(-30, 30, 20001), np.array([1e-8, -1e-8, 1e-4, -1e-4, 0.125, -0.125, 0.12500001, -0.12500001])]
+    z = np.concatenate(pieces).astype(np.float32)
+    z = z[z != 0]
+    got = eo.exprel_f32(z).astype(np.float64)
+    z64 = z.astype(np.float64)
+    ref = np.expm1(z64) / z64
+    ulp = np.spacing(ref.astype(np.float32)).astype(np.float64)
+    err = np.abs(got - ref) / ulp
+    assert err.max() <= 1.0, (err.max(), z[err.argmax()])
+    inside = np.abs(z) <= np.float32(0.125)
+    assert err[inside].max() <= 0.75            # measured 0.57
+    assert err[~inside].max() <= 0.5 + 1e-9     # one rounding of the float64 value
+    assert eo.exprel_f32(np.float32(0.0)) == np.float32(1.0)
+
+
+@pytest.mark.parametrize('hetero', [False, True])
+def test_event_vecmat_over_active_rows_equals_the_full_walk(hetero):
+    """``event_vecmat_rows`` (active rows only; what the network oracle uses at 10^6 neurons)
+    gives the bits of ``event_vecmat``, for both layouts; its fixed-point form agrees within
+    half a float32 ulp of the sum and does not depend on the order of the entries."""
+    rs = np.random.RandomState(5)
+    n_pre, n_post, K = 400, 150, 21
+    idx = rs.randint(0, n_post, (n_pre, K)).astype(np.int32)
+    w = rs.normal(0.1, 0.3, (n_pre, K)).astype(np.float32) if hetero else np.float32(-0.7)
+    spk = rs.random_sample(n_pre) < 0.15
+    assert np.array_equal(eo.event_vecmat_rows(spk, idx, w, n_post), eo.event_vecmat(spk, idx, w, n_post))
+    flat, indptr, _ = eo.afferent_csr(9, n_pre, n_post, K, 0.5)
+    wf = rs.normal(0.1, 0.3, flat.shape).astype(np.float32) if hetero else w
+    assert np.array_equal(eo.event_vecmat_rows(spk, flat, wf, n_post, indptr), eo.event_vecmat(spk, flat, wf, n_post, indptr))
+    fx = eo.event_vecmat_rows(spk, idx, w, n_post, fixed_point=True)
+    act = np.nonzero(spk)[0]
+    ref = np.zeros(n_post, np.float64)
+    np.add.at(ref, idx[act].reshape(-1), (w[act].reshape(-1) if hetero else np.full(act.size * K, w)).astype(np.float64))
+    np.testing.assert_allclose(fx, ref, rtol=1e-6, atol=1e-7)
+    perm = rs.permutation(K)                     # another order inside every row: same integers, same sum
+    w2 = w[:, perm] if hetero else w
+    assert np.array_equal(eo.event_vecmat_rows(spk, idx[:, perm], w2, n_post, fixed_point=True), fx)
