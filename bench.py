@@ -163,12 +163,12 @@ class CpuPath:
             self.reverse = 'scatter over the column-major copy'
 
     def vecmat(self, spk):
-        return self.co.event_vecmat_u8(spk, self.idx, self.w, self.n)
+        return self.co.event_vecmat_u8(spk, self.idx, self.w, self.n, split_rows=True)
 
     def matvec(self, spk):
         if self.reverse == 'row gather':
             return self.co.event_matvec_u8(spk, self.idx, self.w, self.n)
-        return self.co.event_vecmat_u8(spk, self.t_rows, self.t_w, self.n, self.t_indptr)
+        return self.co.event_vecmat_u8(spk, self.t_rows, self.t_w, self.n, self.t_indptr, split_rows=True)
 
     def run(self, spk):
         self.vecmat(spk)

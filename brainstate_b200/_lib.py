@@ -21,6 +21,7 @@ BSX_ERR_UNSUPPORTED = -5
 BSX_ERR_TIMEOUT = -6
 
 VECMAT_GLOBAL_ATOMICS, VECMAT_SHARED_SLICES = 0, 1
+LINK_EARLY_PUSH, LINK_FETCH_AHEAD, LINK_DEFAULT = 1, 2, 3
 SPK_BOOL8, SPK_F32, SPK_BITS32, SPK_LIST = 0, 1, 2, 3
 
 
@@ -79,7 +80,7 @@ class BsxNetLinks(C.Structure):
     """Mirror of ``bsx_net_links_t``."""
     _fields_ = [('world', C.c_int32), ('rank', C.c_int32), ('blocks', C.c_int32), ('words_per_block', C.c_int32),
                 ('words_per_rank', C.c_int64), ('slots', C.c_int32), ('slack', C.c_int32),
-                ('spin_limit', C.c_int64), ('seq0', C.c_int64), ('inbox', C.c_void_p * 16), ('sync', C.c_void_p)]
+                ('spin_limit', C.c_int64), ('seq0', C.c_int64), ('inbox', C.c_void_p * 16), ('sync', C.c_void_p), ('flags', C.c_int32)]
 
 
 _i64, _i32, _vp, _sz, _f32 = C.c_int64, C.c_int, C.c_void_p, C.c_size_t, C.c_float

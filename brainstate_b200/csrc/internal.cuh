@@ -26,6 +26,12 @@ bool scatter_smem_preferred(const bsx_conn_t* conn, int format, int64_t batch);
 int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, const float* x, int64_t batch,
                         float* out, int accumulate, cudaStream_t st, int row_mul = 0);   // row_mul >= 1: sliced layout with that many slices
 
+// One-kernel event vecmat for a few spike vectors (scatter_fused.cu): memset node + list-and-scatter kernel.
+bool scatter_fused_applies(const bsx_conn_t* conn, const void* spikes, int format, int64_t batch);
+bool scatter_fused_fits(const bsx_conn_t* conn, int format, int64_t batch);
+int launch_scatter_fused(const bsx_conn_t* conn, const void* spikes, int format, const float* x, int64_t batch,
+                         float* out, int accumulate, cudaStream_t st);
+
 // Batched event matvec, 16 spike vectors per pass over the indices (gather_batched.cu).
 size_t b16_mask_bytes(int64_t batch, int64_t n_post);
 bool b16_fits(int64_t n_post);

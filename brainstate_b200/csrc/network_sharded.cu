@@ -72,6 +72,7 @@ struct LinkDev {
   int32_t* sync;                  // [0] status word, [1] barrier counter
   int64_t spin_limit;
   int64_t seq0;
+  int flags;                      // bit 0: push ids as soon as a warp has them; bit 1: fetch header and first ids together
 };
 
 // ---- increments: float (atomic order decides the last bit) or 2^-32 fixed point ----
@@ -149,8 +150,10 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
 
 // Barrier over the blocks of this launch (all co-resident: cooperative launch).  The
 // counter only grows; `target` is blocks * (barriers so far + 1).  Bounded: a block that
-// waits too long records the timeout and goes on.
-__device__ __forceinline__ void grid_barrier(int32_t* sync, unsigned target, int64_t spin_limit) {
+// waits too long records the timeout and goes on.  Returns the status word as thread 0 read
+// it after the wait — the same value for every thread of the block, so the block can leave
+// the step loop as one.
+__device__ __forceinline__ int grid_barrier(int32_t* sync, unsigned target, int64_t spin_limit, int* s_status) {
   __syncthreads();
   if (threadIdx.x == 0) {
     unsigned* counter = reinterpret_cast<unsigned*>(sync + 1);
@@ -162,8 +165,10 @@ __device__ __forceinline__ void grid_barrier(int32_t* sync, unsigned target, int
         break;
       }
     }
+    *s_status = *reinterpret_cast<volatile int32_t*>(sync);
   }
   __syncthreads();
+  return *s_status;
 }
 
 // The block's own-spike list -> inbox of `peer`, list (source rank, source block) of slot seq % slots.
@@ -172,7 +177,8 @@ __device__ __forceinline__ void push_list(const LinkDev& L, int peer, int64_t se
   unsigned long long* base = L.inbox[peer] + (seq % L.slots) * L.slot_stride +
                              ((int64_t)L.rank * gridDim.x + blockIdx.x) * (1 + L.cap);
   const unsigned long long tag = (unsigned long long)(uint32_t)(seq + 1) << 32;
-  for (int k = lane; k < count; k += 32) st_relaxed_sys(base + 1 + k, tag | (uint32_t)(gid0 + mine[k]));
+  if (!(L.flags & 1))                      // otherwise the ids went out while the update was running
+    for (int k = lane; k < count; k += 32) st_relaxed_sys(base + 1 + k, tag | (uint32_t)(gid0 + mine[k]));
   if (lane == 0) st_relaxed_sys(base, tag | (uint32_t)count);
 }
 
@@ -202,31 +208,69 @@ __device__ __forceinline__ int recv_list(const ShardDev& a, const LinkDev& L, in
   const unsigned long long* base = L.inbox[L.rank] + (seq % L.slots) * L.slot_stride +
                                    ((int64_t)src * gridDim.x + blockIdx.x) * (1 + L.cap);
   const uint32_t tag = (uint32_t)(seq + 1);
-  uint32_t count = 0;
-  int ok = 1;
-  if (lane == 0) ok = wait_word(base, tag, L.spin_limit, L.sync, &count) ? 1 : 0;
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  count = __shfl_sync(0xffffffffu, count, 0);
-  if (!ok || (int64_t)count > L.cap) return -1;
-  for (uint32_t k0 = 0; k0 < count; k0 += 32) {
-    const uint32_t k = k0 + lane;
-    uint32_t id = 0;
+  uint32_t count = 0, id = 0;
+  uint32_t k0 = 0;
+  bool have_first = false;                // ids 0..30 already fetched by lanes 1..31
+  if (L.flags & 2) {
+    // header (lane 0) and the first 31 id words (lanes 1..31) in the same round trip: the
+    // sender stores the ids before the header, so they are usually there with it
+    int64_t spins = 0;
+    unsigned long long v;
+    for (;;) {
+      v = ld_relaxed_sys(base + lane);
+      const unsigned long long h = __shfl_sync(0xffffffffu, v, 0);
+      if ((uint32_t)(h >> 32) == tag) {
+        count = (uint32_t)h;
+        break;
+      }
+      if (++spins > L.spin_limit) return -1;
+      if ((spins & 1023) == 0 && *reinterpret_cast<const volatile int32_t*>(L.sync) != 0) return -1;
+    }
+    if ((int64_t)count > L.cap) return -1;
     int good = 1;
-    if (k < count) good = wait_word(base + 1 + k, tag, L.spin_limit, L.sync, &id) ? 1 : 0;
+    if (lane >= 1 && (uint32_t)lane <= count) {
+      if ((uint32_t)(v >> 32) == tag) id = (uint32_t)v;
+      else good = wait_word(base + lane, tag, L.spin_limit, L.sync, &id) ? 1 : 0;
+    }
     if (!__all_sync(0xffffffffu, good)) return -1;
-    const int n = (int)(count - k0 < 32u ? count - k0 : 32u);
+    have_first = true;
+  } else {
+    int ok = 1;
+    if (lane == 0) ok = wait_word(base, tag, L.spin_limit, L.sync, &count) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    count = __shfl_sync(0xffffffffu, count, 0);
+    if (!ok || (int64_t)count > L.cap) return -1;
+  }
+  while (k0 < count) {
+    int n;                                 // ids of this batch; lane `first + j` holds id k0 + j
+    int first;
+    if (have_first) {
+      n = (int)(count < 31u ? count : 31u);
+      first = 1;
+      have_first = false;
+    } else {
+      const uint32_t k = k0 + lane;
+      int good = 1;
+      if (k < count) good = wait_word(base + 1 + k, tag, L.spin_limit, L.sync, &id) ? 1 : 0;
+      if (!__all_sync(0xffffffffu, good)) return -1;
+      n = (int)(count - k0 < 32u ? count - k0 : 32u);
+      first = 0;
+    }
+    const int j0 = lane - first;           // position inside the batch
     int pos = 0;
     if (lane == 0) pos = atomicAdd(queue_count, n);
     pos = __shfl_sync(0xffffffffu, pos, 0);
-    const bool staged = lane < n && pos + lane < kShQueue;
-    if (staged) queue[pos + lane] = (int32_t)id;
-    uint32_t direct = __ballot_sync(0xffffffffu, lane < n && !staged);
+    const bool in_batch = j0 >= 0 && j0 < n;
+    const bool staged = in_batch && pos + j0 < kShQueue;
+    if (staged) queue[pos + j0] = (int32_t)id;
+    uint32_t direct = __ballot_sync(0xffffffffu, in_batch && !staged);
     while (direct) {
       const int j = __ffs(direct) - 1;
       direct &= direct - 1;
       const int64_t idj = (int64_t)__shfl_sync(0xffffffffu, id, j);
       for (int c = 0; c < cpr; ++c) scatter_spike<FIXED>(a, idj, c, fired, lane);
     }
+    k0 += n;
   }
   return (int)count;
 }
@@ -239,8 +283,9 @@ net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t
   using T = typename I::T;
   constexpr int WPW = RESIDENT ? 8 : 4;                 // words a warp has in flight at once
   extern __shared__ __align__(16) unsigned char sh_raw[];
-  __shared__ int s_spikes, s_queue_count;
+  __shared__ int s_spikes, s_queue_count, s_status;
   __shared__ int32_t s_queue[kShQueue];
+  __shared__ unsigned long long* s_out[kShMaxPeers];      // this step's list in every peer's inbox
   const int cap = L.words_per_block * 32;
   float* sV = reinterpret_cast<float*>(sh_raw);
   float* sge = sV + (RESIDENT ? cap : 0);
@@ -267,7 +312,9 @@ net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t
     }
   }
   __syncthreads();
+  __syncthreads();
   unsigned barriers = 0;
+  int status = 0;
   for (int t = 0; t < steps; ++t) {
     const int64_t step = step0 + t;
     const int64_t seq = L.seq0 + t;
@@ -277,7 +324,12 @@ net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t
       s_spikes = 0;
       s_queue_count = 0;
     }
+    if (tid < links)
+      s_out[tid] = L.inbox[(L.rank + 1 + tid) % L.world] + (seq % L.slots) * L.slot_stride +
+                   ((int64_t)L.rank * gridDim.x + blockIdx.x) * (1 + L.cap);
     __syncthreads();
+    const bool early = links > 0 && (L.flags & 1);
+    const unsigned long long push_tag = (unsigned long long)(uint32_t)(seq + 1) << 32;
     // ---- 1. neuron update ----
     for (int64_t wl0 = wid; wl0 < my_words; wl0 += kShWarps * WPW) {
       T de[WPW], di[WPW];
@@ -333,7 +385,12 @@ net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t
           int base = 0;
           if (lane == 0) base = atomicAdd(&s_spikes, __popc(m));
           base = __shfl_sync(0xffffffffu, base, 0);
-          if (spk) smine[base + __popc(m & ((1u << lane) - 1u))] = (uint16_t)li;
+          if (spk) {
+            const int pos = base + __popc(m & ((1u << lane) - 1u));
+            smine[pos] = (uint16_t)li;
+            if (early)       // the id is on its way to every peer before the rest of the block has finished
+              for (int p = 0; p < links; ++p) st_relaxed_sys(s_out[p] + 1 + pos, push_tag | (uint32_t)(a.first + i));
+          }
         }
       }
     }
@@ -358,9 +415,9 @@ net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t
       }
     }
     if (tid == 0 && mine && spike_counts) atomicAdd(spike_counts + t, mine);
-    __syncthreads();
     // ---- 4. received spikes, all warps ----
-    {
+    if (links > 0) {
+      __syncthreads();
       const int staged = s_queue_count < kShQueue ? s_queue_count : kShQueue;
       const int items = staged * cpr;
       for (int it = wid; it < items; it += kShWarps) {
@@ -370,11 +427,11 @@ net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t
     }
     // ---- 5. every increment of the next step is in place once all blocks are here ----
     ++barriers;
-    grid_barrier(L.sync, barriers * gridDim.x, L.spin_limit);
-    if (*reinterpret_cast<volatile int32_t*>(L.sync) != 0) break;
+    status = grid_barrier(L.sync, barriers * gridDim.x, L.spin_limit, &s_status);
+    if (status != 0) break;                              // uniform across the block
   }
   // lists still in the inbox (the last `slack` steps): consume them before the launch ends
-  if (links > 0 && L.slack > 0 && *reinterpret_cast<volatile int32_t*>(L.sync) == 0) {
+  if (links > 0 && L.slack > 0 && status == 0) {
     for (int t = steps - L.slack < 0 ? 0 : steps - L.slack; t < steps; ++t) {
       __syncthreads();
       if (tid == 0) s_queue_count = 0;
@@ -510,6 +567,7 @@ int bsx_net_run_sharded(const bsx_net_shard_t* net, const bsx_lif_params_t* para
   L.sync = links->sync;
   L.spin_limit = links->spin_limit > 0 ? links->spin_limit : (int64_t)1 << 21;
   L.seq0 = links->seq0;
+  L.flags = links->flags;
   cudaStream_t st = as_stream(stream);
   if (spike_counts && steps > 0) BSX_CUDA(cudaMemsetAsync(spike_counts, 0, sizeof(int32_t) * (size_t)steps, st));
   if (steps == 0) return BSX_OK;

@@ -120,6 +120,18 @@ int vecmat_common(const bsx_conn_t* conn, const void* in, int format, const floa
       return launch_scatter_smem(conn, in, format, x, batch, out, accumulate, st);
     blocks_per_sm = 0;
   }
+  // A few spike vectors (the per-step call of a simulation): a memset node and ONE kernel that
+  // lists the active rows in shared memory and scatters them; the workspace stays untouched
+  // (it is still checked, so that a caller's sizing error shows at any input size).  Explicit
+  // tuning arguments keep the queue + scatter launches.
+  if (blocks_per_sm == 0 && chunk == 0 && scatter_fused_applies(conn, in, format, batch)) {
+    if (format != BSX_SPK_LIST) {
+      if (!ws || (reinterpret_cast<uintptr_t>(ws) & 15)) return fail(BSX_ERR_WORKSPACE, "workspace NULL or not 16-byte aligned");
+      if (ws_bytes < queue_bytes(batch, conn->n_pre))
+        return fail(BSX_ERR_WORKSPACE, "workspace too small: %zu < %zu", ws_bytes, queue_bytes(batch, conn->n_pre));
+    }
+    return launch_scatter_fused(conn, in, format, x, batch, out, accumulate, st);
+  }
   if (format == BSX_SPK_LIST) {
     if (batch != 1) return fail(BSX_ERR_UNSUPPORTED, "an index list describes one spike vector (batch 1)");
     if (!accumulate) {
@@ -175,7 +187,8 @@ int bsx_event_vecmat_launches(const bsx_conn_t* conn, int spike_format, int64_t 
   const int v = bsx_event_vecmat_variant(conn, spike_format, batch);
   if (v < 0) return v;
   if (v == BSX_VECMAT_SHARED_SLICES) return 1;
-  return spike_format == BSX_SPK_LIST ? 2 : 2;      // (clear | compaction + clear) and scatter
+  if (scatter_fused_fits(conn, spike_format, batch)) return 1;   // given 16-byte aligned buffers
+  return 2;                                                      // (clear | compaction + clear) and scatter
 }
 
 int bsx_event_vecmat(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,

@@ -6,11 +6,11 @@
 // with a = x or the event indicator [x != 0].
 //
 // The cotangent is first transposed to batch-minor order (n_post, Bp) so that one
-// index fetches the values of 64 batch lanes as two coalesced 128-byte loads.  A
-// warp owns a row; lane l holds batch lanes l and l + 32.  Indices and weights are
-// loaded 32 at a time (coalesced) and broadcast by shuffles.  The weight cotangent
-// only touches the batch lanes where the row was active (a handful at the firing
-// rates of interest), found by ballot.  No atomics; fixed summation order.
+// index fetches the values of 64 batch lanes as one contiguous 256-byte stretch.  The input
+// cotangent and the weight cotangent are separate launches: dx walks every synapse for every
+// batch lane (lane = batch lane), dw only touches the batch lanes where the row was active —
+// a handful at the firing rates of interest, found by ballot — with lane = synapse.  No
+// atomics; fixed summation order.
 #include "common.cuh"
 #include "internal.cuh"
 
@@ -41,41 +41,24 @@ __device__ __forceinline__ float act_at(const void* x, int64_t pos, bool event) 
   return a;
 }
 
-// One chunk of up to 64 batch lanes starting at b0.  first_chunk: dw is written,
-// later chunks add to it.
-template <bool HETERO, int XFORMAT>
+// Input cotangent for one chunk of up to 64 batch lanes starting at b0: a warp owns a row,
+// lane l holds batch lanes l and l + 32; every index fetches its 64 cotangent values as one
+// 256-byte stretch of the batch-minor copy (one 8-byte load per lane).
+template <bool HETERO>
 __global__ void __launch_bounds__(256)
-vjp_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
-                   const void* __restrict__ x, bool event, const float* __restrict__ ctT, int64_t Bp,
-                   int64_t B, int64_t b0, int64_t n_pre, float* __restrict__ dx, float* __restrict__ dw,
-                   bool first_chunk) {
-  __shared__ float block_part[8];
+vjp_dx_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
+                      const float* __restrict__ ctT, int64_t Bp, int64_t B, int64_t b0, int64_t n_pre,
+                      float* __restrict__ dx) {
   const int lane = threadIdx.x & 31;
   const float w0 = HETERO ? 0.f : __ldg(w);
-  const int64_t blo = b0 + lane, bhi = b0 + 32 + lane;
-  const bool has_lo = blo < B, has_hi = bhi < B;
-  float homo_acc = 0.f;
+  // lane l reads the pair (2l, 2l + 1) of the 64 lanes: one float2 per lane covers the stretch
+  const int64_t be = b0 + 2 * lane, bo = be + 1;
+  const bool pair = b0 + 64 <= Bp;                       // a full 64-lane stretch exists
   const int64_t wstep = (int64_t)gridDim.x * (blockDim.x >> 5);
   for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < n_pre; row += wstep) {
-    float a_lo = 0.f, a_hi = 0.f;
-    if (dw) {
-      if (has_lo) a_lo = act_at<XFORMAT>(x, blo * n_pre + row, event);
-      if (has_hi) a_hi = act_at<XFORMAT>(x, bhi * n_pre + row, event);
-    }
-    const uint32_t act_lo = __ballot_sync(0xffffffffu, a_lo != 0.f);
-    const uint32_t act_hi = __ballot_sync(0xffffffffu, a_hi != 0.f);
-    const bool any_act = (act_lo | act_hi) != 0;
-    if (!dx && !any_act) {
-      if (dw && HETERO && first_chunk) {  // this row contributes nothing: clear its slice
-        int64_t s, e;
-        rm.range(row, s, e);
-        for (int64_t p = s + lane; p < e; p += 32) dw[p] = 0.f;
-      }
-      continue;
-    }
     int64_t s, e;
     rm.range(row, s, e);
-    float dx_lo = 0.f, dx_hi = 0.f;
+    float acc_e = 0.f, acc_o = 0.f;
     for (int64_t pb = s; pb < e; pb += 32) {
       const int64_t p = pb + lane;
       int32_t j_l = 0;
@@ -85,44 +68,107 @@ vjp_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __re
         w_l = HETERO ? __ldg(w + p) : 1.f;
       }
       const int cnt = (int)((e - pb) < 32 ? (e - pb) : 32);
-      float dw_l = 0.f;
+#pragma unroll 4
       for (int t = 0; t < cnt; ++t) {
         const int32_t j = __shfl_sync(0xffffffffu, j_l, t);
         const float ww = __shfl_sync(0xffffffffu, w_l, t);
         const float* __restrict__ crow = ctT + (int64_t)j * Bp + b0;
-        const float c_lo = __ldg(crow + lane);          // padded columns are zero
-        const float c_hi = (b0 + 32 < Bp) ? __ldg(crow + 32 + lane) : 0.f;
-        dx_lo = fmaf(ww, c_lo, dx_lo);
-        dx_hi = fmaf(ww, c_hi, dx_hi);
-        if (any_act) {
-          float sacc = 0.f;  // sum over the active batch lanes, ascending b
-          uint32_t m = act_lo;
-          while (m) {
-            const int src = __ffs(m) - 1;
-            m &= m - 1;
-            sacc = fmaf(__shfl_sync(0xffffffffu, a_lo, src), __shfl_sync(0xffffffffu, c_lo, src), sacc);
+        float2 c;
+        if (pair) c = __ldg(reinterpret_cast<const float2*>(crow) + lane);
+        else c = make_float2(lane < 16 ? __ldg(crow + 2 * lane) : 0.f, lane < 16 ? __ldg(crow + 2 * lane + 1) : 0.f);
+        acc_e = fmaf(ww, c.x, acc_e);
+        acc_o = fmaf(ww, c.y, acc_o);
+      }
+    }
+    if (!HETERO) { acc_e *= w0; acc_o *= w0; }
+    if (be < B) dx[be * n_pre + row] = acc_e;
+    if (bo < B) dx[bo * n_pre + row] = acc_o;
+  }
+}
+
+// Weight cotangent for one chunk of up to 64 batch lanes starting at b0: a warp owns a row
+// and first finds the batch lanes where the row was active (ballot).  With few of them (the
+// event case: a handful at the firing rates of interest) lane = synapse: every lane gathers
+// the cotangent of its own target for each active batch lane, in ascending batch order.  With
+// many (a dense float input) lane = batch lane over the batch-minor copy and a warp sum per
+// synapse.  No atomics, fixed summation order.  first_chunk: dw is written, later chunks add.
+template <bool HETERO, int XFORMAT>
+__global__ void __launch_bounds__(256)
+vjp_dw_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const void* __restrict__ x, bool event,
+                      const float* __restrict__ ct, const float* __restrict__ ctT, int64_t Bp, int64_t B, int64_t b0,
+                      int64_t n_pre, int64_t n_post, float* __restrict__ dw, bool first_chunk) {
+  __shared__ float block_part[8];
+  const int lane = threadIdx.x & 31;
+  const int64_t blo = b0 + lane, bhi = b0 + 32 + lane;
+  const bool has_lo = blo < B, has_hi = bhi < B;
+  float homo_acc = 0.f;
+  const int64_t wstep = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < n_pre; row += wstep) {
+    const float a_lo = has_lo ? act_at<XFORMAT>(x, blo * n_pre + row, event) : 0.f;
+    const float a_hi = has_hi ? act_at<XFORMAT>(x, bhi * n_pre + row, event) : 0.f;
+    const uint32_t act_lo = __ballot_sync(0xffffffffu, a_lo != 0.f);
+    const uint32_t act_hi = __ballot_sync(0xffffffffu, a_hi != 0.f);
+    int64_t s, e;
+    rm.range(row, s, e);
+    const int n_act = __popc(act_lo) + __popc(act_hi);
+    if (n_act == 0) {
+      if (HETERO && first_chunk)                           // this row contributes nothing: clear its slice
+        for (int64_t p = s + lane; p < e; p += 32) dw[p] = 0.f;
+      continue;
+    }
+    if (n_act <= 16) {
+      for (int64_t pb = s; pb < e; pb += 32) {
+        const int64_t p = pb + lane;
+        const bool ok = p < e;
+        const int64_t j = ok ? (int64_t)__ldg(idx + p) : 0;
+        float acc = 0.f;
+        uint32_t m = act_lo;
+        while (m) {                                        // uniform across the warp
+          const int src = __ffs(m) - 1;
+          m &= m - 1;
+          const float a = __shfl_sync(0xffffffffu, a_lo, src);
+          if (ok) acc = fmaf(a, __ldg(ct + (b0 + src) * n_post + j), acc);
+        }
+        m = act_hi;
+        while (m) {
+          const int src = __ffs(m) - 1;
+          m &= m - 1;
+          const float a = __shfl_sync(0xffffffffu, a_hi, src);
+          if (ok) acc = fmaf(a, __ldg(ct + (b0 + 32 + src) * n_post + j), acc);
+        }
+        if (ok) {
+          if (HETERO) {
+            if (first_chunk) dw[p] = acc; else dw[p] += acc;
+          } else {
+            homo_acc += acc;
           }
-          m = act_hi;
-          while (m) {
-            const int src = __ffs(m) - 1;
-            m &= m - 1;
-            sacc = fmaf(__shfl_sync(0xffffffffu, a_hi, src), __shfl_sync(0xffffffffu, c_hi, src), sacc);
-          }
-          if (lane == t) dw_l = sacc;
         }
       }
-      if (dw && HETERO && p < e) {
-        if (first_chunk) dw[p] = dw_l; else dw[p] += dw_l;
+    } else {
+      for (int64_t pb = s; pb < e; pb += 32) {
+        const int64_t p = pb + lane;
+        const int32_t j_l = p < e ? __ldg(idx + p) : 0;
+        const int cnt = (int)((e - pb) < 32 ? (e - pb) : 32);
+        float dw_l = 0.f;
+        for (int t = 0; t < cnt; ++t) {
+          const int32_t j = __shfl_sync(0xffffffffu, j_l, t);
+          const float* __restrict__ crow = ctT + (int64_t)j * Bp + b0;
+          float v = a_lo * __ldg(crow + lane);             // padded batch columns are zero
+          if (b0 + 32 < Bp) v = fmaf(a_hi, __ldg(crow + 32 + lane), v);
+          v = warp_sum(v);
+          if (lane == t) dw_l = v;
+        }
+        if (p < e) {
+          if (HETERO) {
+            if (first_chunk) dw[p] = dw_l; else dw[p] += dw_l;
+          } else {
+            homo_acc += dw_l;
+          }
+        }
       }
-      if (dw && !HETERO && p < e) homo_acc += dw_l;
-    }
-    if (dx) {
-      if (!HETERO) { dx_lo *= w0; dx_hi *= w0; }
-      if (has_lo) dx[blo * n_pre + row] = dx_lo;
-      if (has_hi) dx[bhi * n_pre + row] = dx_hi;
     }
   }
-  if (dw && !HETERO) {
+  if (!HETERO) {
     homo_acc = warp_sum(homo_acc);
     if (lane == 0) block_part[threadIdx.x >> 5] = homo_acc;
     __syncthreads();
@@ -191,16 +237,27 @@ int bsx_vecmat_vjp_batched(const bsx_conn_t* conn, const void* x, int x_format, 
   const bool ev = event != 0;
   for (int64_t b0 = 0; b0 < batch; b0 += 64) {
     const bool first = b0 == 0;
-#define BSX_VJPB(H, F)                                                                                    \
-  vjp_batched_kernel<H, F><<<(unsigned)blocks, 256, 0, st>>>(rm, conn->indices, conn->weights, x, ev, ctT, Bp, \
-                                                             batch, b0, conn->n_pre, dx, dw, first)
-    if (conn->hetero) {
-      if (x_format == BSX_SPK_BOOL8) BSX_VJPB(true, BSX_SPK_BOOL8); else BSX_VJPB(true, BSX_SPK_F32);
-    } else {
-      if (x_format == BSX_SPK_BOOL8) BSX_VJPB(false, BSX_SPK_BOOL8); else BSX_VJPB(false, BSX_SPK_F32);
+    if (dx) {
+      if (conn->hetero)
+        vjp_dx_batched_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(rm, conn->indices, conn->weights, ctT, Bp, batch,
+                                                                     b0, conn->n_pre, dx);
+      else
+        vjp_dx_batched_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(rm, conn->indices, conn->weights, ctT, Bp, batch,
+                                                                      b0, conn->n_pre, dx);
+      BSX_LAUNCH_CHECK("vjp_dx_batched_kernel");
     }
-#undef BSX_VJPB
-    BSX_LAUNCH_CHECK("vjp_batched_kernel");
+    if (dw) {
+#define BSX_VJPW(H, F)                                                                                        \
+  vjp_dw_batched_kernel<H, F><<<(unsigned)blocks, 256, 0, st>>>(rm, conn->indices, x, ev, ct, ctT, Bp, batch, b0, \
+                                                                conn->n_pre, conn->n_post, dw, first)
+      if (conn->hetero) {
+        if (x_format == BSX_SPK_BOOL8) BSX_VJPW(true, BSX_SPK_BOOL8); else BSX_VJPW(true, BSX_SPK_F32);
+      } else {
+        if (x_format == BSX_SPK_BOOL8) BSX_VJPW(false, BSX_SPK_BOOL8); else BSX_VJPW(false, BSX_SPK_F32);
+      }
+#undef BSX_VJPW
+      BSX_LAUNCH_CHECK("vjp_dw_batched_kernel");
+    }
   }
   return BSX_OK;
 }

@@ -227,6 +227,7 @@ class EINet:
         self.deterministic = bool(deterministic)
         self._links = None
         self._seq = 0
+        self.link_flags = _lib.LINK_DEFAULT
         self.delay_e, self.delay_i = int(delay_e), int(delay_i)
         self.ring = max(self.delay_e, self.delay_i) + 2
         self.n_exc, self.n_inh = int(n_exc), int(n_inh)
@@ -438,6 +439,7 @@ class EINet:
         links.blocks, links.words_per_block, links.words_per_rank = blocks.value, wpb.value, self.wpr
         links.slack, links.slots = (self.slack if self.world > 1 else 0), 2 * self.slack + 2
         links.spin_limit = 0
+        links.flags = self.link_flags
         sync = torch.zeros(2, dtype=torch.int32, device=self.dev)
         links.sync = sync.data_ptr()
         state = {'links': links, 'sync': sync, 'base': None, 'opened': []}
@@ -563,10 +565,11 @@ class EINet:
 
 
 # Constant bias current of the 'coba' preset (same unit as a conductance times a potential:
-# with R = 0.1 the membrane sees R * I = 16.6 mV above rest).  Chosen so that the mean rate
-# over the 1000 steps (100 ms) from the seeded start is 10 Hz: the CPU restatement gives
-# 10.03 Hz on a 100 000-neuron copy of the network (9.6 Hz at 160, 10.3 Hz at 172).
-COBA_BIAS = 166.0
+# with R = 0.1 the membrane sees R * I = 16.8 mV above rest).  Found by bisection on the full
+# 10^6-neuron network on a B200: mean rate over the configuration's 1000 steps (100 ms) from
+# the seeded start 10.02 Hz (9.92 Hz at 166, 10.26 Hz at 172); 9.1 Hz once the initial
+# transient of the first 200 steps is left out.
+COBA_BIAS = 168.0
 
 
 def preset(name: str) -> dict:

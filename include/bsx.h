@@ -167,6 +167,9 @@ int bsx_permute_f32(const float* src, const int32_t* perm, int64_t n, float* dst
  *   y[b, idx[i,k]] += w[i,k]  for every i with spk[b,i] != 0   (pre-centric scatter)
  * spikes: (batch, n_pre) in `spike_format`; out: (batch, n_post) float32.
  * accumulate == 0 zeroes `out` first.  Workspace: bsx_event_vecmat_workspace_bytes.
+ * Spike inputs of up to 128 KB (one bool vector of 131 072 neurons) in a 16-byte aligned
+ * buffer run as a memset node plus ONE kernel (active-row list in shared memory + scatter),
+ * which leaves the workspace untouched.
  * Duplicate targets accumulate (brainstate/nn/_event_fixedprob_test.py:256-259).
  * Summation order of heterogeneous weights is not fixed between runs (atomic adds).
  */
@@ -430,7 +433,12 @@ typedef struct bsx_net_links {
   int64_t seq0;
   uint64_t* inbox[16];
   int32_t* sync;
+  int32_t flags;       /* BSX_LINK_* below; 0 = plainest form (ids pushed after the block's update, header
+                          and ids fetched one after the other) */
 } bsx_net_links_t;
+#define BSX_LINK_EARLY_PUSH 1   /* a warp pushes the ids of its spikes as soon as it has them */
+#define BSX_LINK_FETCH_AHEAD 2  /* the receiver fetches a list's header and first 31 ids in one round trip */
+#define BSX_LINK_DEFAULT 3
 /* Grid every rank must launch for shards of words_per_rank spike words (one block per SM
  * at most, at least one word per warp). */
 int bsx_net_shard_geometry(int64_t words_per_rank, int32_t* blocks, int32_t* words_per_block);

@@ -137,34 +137,38 @@ void orc_float_vecmat(const float* x, int64_t batch, int64_t n_pre, int64_t n_po
     }
 }
 
-/* With at least as many vectors as threads (and for small matrices) each thread takes whole
- * vectors and sums sequentially in (row, k) order.  With fewer vectors of a large matrix the
- * active rows of one vector are split over the threads, every thread adding into a private
- * copy of the output that is then summed column-wise in thread order, so that all cores
- * work on a single vector too (sums then differ from the sequential order within float32
- * rounding). */
 void orc_event_vecmat_u8(const uint8_t* spk, int64_t batch, int64_t n_pre, int64_t n_post, int64_t K,
                          const int64_t* indptr, const int32_t* idx, const float* w, int hetero,
                          float* y) {
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t b = 0; b < batch; ++b) {
+        float* yb = y + b * n_post;
+        memset(yb, 0, (size_t)n_post * sizeof(float));
+        const uint8_t* sb = spk + b * n_pre;
+        for (int64_t i = 0; i < n_pre; ++i) {
+            if (!sb[i]) continue;
+            int64_t s, e;
+            row_range(indptr, K, i, &s, &e);
+            if (hetero) for (int64_t p = s; p < e; ++p) yb[idx[p]] += w[p];
+            else { float v = w[0]; for (int64_t p = s; p < e; ++p) yb[idx[p]] += v; }
+        }
+    }
+}
+
+/* The same product for timing on many cores with FEWER vectors than threads: the active
+ * rows of one vector are split over the threads, every thread adding into a private copy of
+ * the output that is then summed column-wise in thread order, so that all cores work on a
+ * single vector too.  The sums differ from the sequential (row, k) order within float32
+ * rounding, so parity tests use orc_event_vecmat_u8. */
+void orc_event_vecmat_u8_par(const uint8_t* spk, int64_t batch, int64_t n_pre, int64_t n_post, int64_t K,
+                             const int64_t* indptr, const int32_t* idx, const float* w, int hetero,
+                             float* y) {
     int nt = 1;
 #ifdef _OPENMP
     nt = omp_get_max_threads();
 #endif
-    const int64_t nnz_all = indptr ? indptr[n_pre] : n_pre * K;
-    if (batch >= nt || nt == 1 || nnz_all < ((int64_t)1 << 22)) {
-#pragma omp parallel for schedule(dynamic, 1)
-        for (int64_t b = 0; b < batch; ++b) {
-            float* yb = y + b * n_post;
-            memset(yb, 0, (size_t)n_post * sizeof(float));
-            const uint8_t* sb = spk + b * n_pre;
-            for (int64_t i = 0; i < n_pre; ++i) {
-                if (!sb[i]) continue;
-                int64_t s, e;
-                row_range(indptr, K, i, &s, &e);
-                if (hetero) for (int64_t p = s; p < e; ++p) yb[idx[p]] += w[p];
-                else { float v = w[0]; for (int64_t p = s; p < e; ++p) yb[idx[p]] += v; }
-            }
-        }
+    if (batch >= nt || nt == 1) {
+        orc_event_vecmat_u8(spk, batch, n_pre, n_post, K, indptr, idx, w, hetero, y);
         return;
     }
     float* priv = (float*)malloc((size_t)nt * (size_t)n_post * sizeof(float));

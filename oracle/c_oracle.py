@@ -77,13 +77,16 @@ def _conn_args(idx, w, indptr, n_pre):
     return idx, w, hetero, K, ip
 
 
-def event_vecmat_u8(spk, idx, w, n_post, indptr=None):
+def event_vecmat_u8(spk, idx, w, n_post, indptr=None, split_rows=False):
+    """``split_rows``: for timing on many cores with few vectors — the active rows of a vector are
+    divided among the threads (sums then differ from the sequential order within rounding)."""
     spk = np.ascontiguousarray(spk, np.uint8)
     n_pre = spk.shape[-1]
     sb = spk.reshape(-1, n_pre)
     idx, w, hetero, K, ip = _conn_args(idx, w, indptr, n_pre)
     y = np.empty((sb.shape[0], n_post), np.float32)
-    lib().orc_event_vecmat_u8(_p(sb, C.c_uint8), C.c_int64(sb.shape[0]), C.c_int64(n_pre), C.c_int64(n_post),
+    fn = lib().orc_event_vecmat_u8_par if split_rows else lib().orc_event_vecmat_u8
+    fn(_p(sb, C.c_uint8), C.c_int64(sb.shape[0]), C.c_int64(n_pre), C.c_int64(n_post),
                               C.c_int64(K), _p(ip, C.c_int64), _p(idx, C.c_int32), _p(w, C.c_float),
                               C.c_int(hetero), _p(y, C.c_float))
     return y.reshape(spk.shape[:-1] + (n_post,))
