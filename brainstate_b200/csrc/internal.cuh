@@ -32,6 +32,9 @@ bool scatter_fused_fits(const bsx_conn_t* conn, int format, int64_t batch);
 int launch_scatter_fused(const bsx_conn_t* conn, const void* spikes, int format, const float* x, int64_t batch,
                          float* out, int accumulate, cudaStream_t st);
 
+// (B, n) row-major -> (n, Bp) row-major, zero padded to Bp (a multiple of 32) columns (vjp_batched.cu).
+int launch_transpose_pad(const float* src, int64_t B, int64_t n, int64_t Bp, float* dst, cudaStream_t st);
+
 // Batched event matvec, 16 spike vectors per pass over the indices (gather_batched.cu).
 size_t b16_mask_bytes(int64_t batch, int64_t n_post);
 bool b16_fits(int64_t n_post);

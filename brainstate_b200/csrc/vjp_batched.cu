@@ -33,6 +33,14 @@ transpose_pad_kernel(const float* __restrict__ src, int64_t B, int64_t n, int64_
   }
 }
 
+int launch_transpose_pad(const float* src, int64_t B, int64_t n, int64_t Bp, float* dst, cudaStream_t st) {
+  if (Bp % 32 || Bp / 32 > 65535) return fail(BSX_ERR_UNSUPPORTED, "batch too large");
+  dim3 grid((unsigned)((n + 31) / 32), (unsigned)(Bp / 32), 1);
+  transpose_pad_kernel<<<grid, 256, 0, st>>>(src, B, n, Bp, dst);
+  BSX_LAUNCH_CHECK("transpose_pad_kernel");
+  return BSX_OK;
+}
+
 template <int XFORMAT>
 __device__ __forceinline__ float act_at(const void* x, int64_t pos, bool event) {
   float a = (XFORMAT == BSX_SPK_BOOL8) ? (float)(static_cast<const uint8_t*>(x)[pos] != 0)
@@ -225,11 +233,8 @@ int bsx_vecmat_vjp_batched(const bsx_conn_t* conn, const void* x, int x_format, 
   const int64_t Bp = (batch + 31) & ~int64_t(31);
   if (Bp / 32 > 65535) return fail(BSX_ERR_UNSUPPORTED, "batch too large");
   float* ctT = static_cast<float*>(workspace);
-  {
-    dim3 grid((unsigned)((conn->n_post + 31) / 32), (unsigned)(Bp / 32), 1);
-    transpose_pad_kernel<<<grid, 256, 0, st>>>(ct, batch, conn->n_post, Bp, ctT);
-    BSX_LAUNCH_CHECK("transpose_pad_kernel");
-  }
+  rc = launch_transpose_pad(ct, batch, conn->n_post, Bp, ctT, st);
+  if (rc) return rc;
   int64_t blocks = (conn->n_pre + 7) / 8;
   if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
   if (blocks < 1) blocks = 1;

@@ -3,6 +3,7 @@ validates its arguments on the host and refuses to compute without a GPU."""
 import ctypes as C
 import os
 import re
+import sys
 
 import numpy as np
 import pytest
@@ -172,3 +173,37 @@ def test_shard_kernel_entry_point_validates_on_the_host(bsx):
     assert call() == BSX_ERR_INVALID_ARG and b'inbox' in bsx.bsx_last_error_string()
     assert bsx.bsx_net_inbox_bytes(2, 3, 32, 4) == 4 * 2 * 3 * (1 + 32 * 32) * 8
     assert bsx.bsx_net_inbox_bytes(0, 3, 32, 4) == 0
+
+
+def test_xla_ffi_shim_type_checks_against_a_stub_header():
+    """ffi/bsx_ffi.cc compiles only where jaxlib's FFI headers exist.  Against a
+    declarations-only stand-in (tests/stubs) the translation unit must parse and every
+    handler's signature must match its binding (the stand-in's macro asserts it)."""
+    import shutil
+    import subprocess
+    gxx = shutil.which('g++')
+    if gxx is None:
+        pytest.skip('no g++')
+    cuda_inc = '/usr/local/cuda/include'
+    if not os.path.exists(os.path.join(cuda_inc, 'cuda_runtime_api.h')):
+        pytest.skip('no CUDA headers')
+    r = subprocess.run([gxx, '-std=c++17', '-fsyntax-only', '-I', os.path.join(ROOT, 'include'),
+                        '-I', os.path.join(ROOT, 'tests', 'stubs'), '-I', cuda_inc,
+                        os.path.join(ROOT, 'ffi', 'bsx_ffi.cc')], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    text = open(os.path.join(ROOT, 'ffi', 'bsx_ffi.cc')).read()
+    for target in ('bsx_ffi_vecmat', 'bsx_ffi_matvec', 'bsx_ffi_vecmat_vjp', 'bsx_ffi_dense_event_vecmat'):
+        assert f'XLA_FFI_DEFINE_HANDLER_SYMBOL({target},' in text
+
+
+def test_jax_binding_is_import_guarded():
+    """The JAX registration module must not be pulled in by the package, and without jax it
+    fails with a message that says what is missing."""
+    import importlib
+    import brainstate_b200
+    assert 'brainstate_b200.jax_binding' not in sys.modules
+    try:
+        import jax  # noqa: F401
+    except ImportError:
+        with pytest.raises(ImportError, match='needs jax'):
+            importlib.import_module('brainstate_b200.jax_binding')
