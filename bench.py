@@ -580,6 +580,7 @@ def run_network(torch, dist, dev, world, rank, name, steps, warm):
     build_s = time.perf_counter() - t0
 
     def timed(net):
+        net.prepare()                           # inboxes and peer mappings: set-up, not part of a step
         pre = net.run(warm, record=False)[1] if warm else None
         torch.cuda.synchronize()
         if world > 1:

@@ -12,7 +12,11 @@
 // With n_post = 65 536 two blocks share a batch row and each reads every active row;
 // the two are neighbours in launch order, so the second read is served by L2.  Beyond
 // four slices the re-reading outweighs any gain.  Like every atomic scatter, the
-// summation order of heterogeneous weights is not fixed.
+// summation order of heterogeneous weights is not fixed.  With homogeneous weights and
+// an event input every event adds the same value, so the slice holds integer hit counts
+// (native integer atomics, no compare-and-swap loop) and every output is count * weight,
+// rounded once: exact in the count, and within an ulp of — not bit-equal to — a sequential
+// float sum of `count` copies of the weight.
 //
 // One block per SM: the kernel needs batch * slices >= the number of SMs to fill the
 // GPU, which is what the automatic choice in vecmat_common checks.
@@ -28,8 +32,19 @@ constexpr int kSsList = 2048;     // active rows listed per round (row, start, l
 constexpr int kSsUnroll = 3;      // 128-bit loads in flight per lane and array
 constexpr int kSsDeal = 12;       // 32-entry stretches in flight per warp over the sliced layout
 
-__device__ __forceinline__ void smem_add(float* p, float v) {
+__device__ __forceinline__ void smem_add_f32(float* p, float v) {
   asm volatile("red.shared.add.f32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "f"(v) : "memory");
+}
+__device__ __forceinline__ void smem_count(float* p) {   // the slot holds a uint32 hit count
+  asm volatile("red.shared.add.u32 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)) : "memory");
+}
+// COUNT (homogeneous weights, event input): the slice holds integer hit counts, added with the
+// native shared-memory integer atomic (the float add is a load + compare-and-swap loop), and
+// is multiplied by the weight once when it is written out.
+template <bool COUNT>
+__device__ __forceinline__ void smem_add(float* p, float v) {
+  if (COUNT) smem_count(p);
+  else smem_add_f32(p, v);
 }
 
 // Active spikes among the positions [i0, i1) of batch row b; their positions go to dst
@@ -74,14 +89,14 @@ __device__ __forceinline__ int list_span(const void* __restrict__ spikes, int64_
   return c;
 }
 
-template <bool HETERO>
+template <bool HETERO, bool COUNT>
 __device__ __forceinline__ void add_four(float* acc, int32_t col0, uint32_t ncol, const int4 j, const float4 t, float v) {
   const uint32_t c0 = (uint32_t)(j.x - col0), c1 = (uint32_t)(j.y - col0), c2 = (uint32_t)(j.z - col0),
                  c3 = (uint32_t)(j.w - col0);
-  if (c0 < ncol) smem_add(acc + c0, HETERO ? __fmul_rn(v, t.x) : v);
-  if (c1 < ncol) smem_add(acc + c1, HETERO ? __fmul_rn(v, t.y) : v);
-  if (c2 < ncol) smem_add(acc + c2, HETERO ? __fmul_rn(v, t.z) : v);
-  if (c3 < ncol) smem_add(acc + c3, HETERO ? __fmul_rn(v, t.w) : v);
+  if (c0 < ncol) smem_add<COUNT>(acc + c0, HETERO ? __fmul_rn(v, t.x) : v);
+  if (c1 < ncol) smem_add<COUNT>(acc + c1, HETERO ? __fmul_rn(v, t.y) : v);
+  if (c2 < ncol) smem_add<COUNT>(acc + c2, HETERO ? __fmul_rn(v, t.z) : v);
+  if (c3 < ncol) smem_add<COUNT>(acc + c3, HETERO ? __fmul_rn(v, t.w) : v);
 }
 
 template <bool HETERO, bool HAS_X, int FORMAT, bool SLICED>
@@ -89,6 +104,7 @@ __global__ void __launch_bounds__(kSsThreads, 1)
 scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
                     const void* __restrict__ spikes, const float* __restrict__ x, int64_t n_pre,
                     int64_t n_post, float* __restrict__ out, int accumulate, bool vec_ok, int row_mul) {
+  constexpr bool COUNT = !HETERO && !HAS_X;     // every event adds the same value: count, multiply once
   extern __shared__ __align__(16) unsigned char ss_raw[];
   float* acc = reinterpret_cast<float*>(ss_raw);
   // per listed row: where its entries start, how many there are, and which row it is
@@ -213,7 +229,7 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
 #pragma unroll
           for (int u = 0; u < kSsDeal; ++u) {
             const uint32_t cc = (uint32_t)(j[u] - col0);
-            if (cc < ncol) smem_add(acc + cc, HETERO ? __fmul_rn(v, t[u]) : v);
+            if (cc < ncol) smem_add<COUNT>(acc + cc, HETERO ? __fmul_rn(v, t[u]) : v);
           }
         }
         continue;
@@ -248,28 +264,30 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
           else t4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
-        for (int u = 0; u < kSsUnroll; ++u) add_four<HETERO>(acc, col0, ncol, j[u], t4[u], v);
+        for (int u = 0; u < kSsUnroll; ++u) add_four<HETERO, COUNT>(acc, col0, ncol, j[u], t4[u], v);
       }
       if (vec_ok) {
         const uint32_t cc = (uint32_t)(hj - col0);
-        if (cc < ncol) smem_add(acc + cc, HETERO ? __fmul_rn(v, hw) : v);
+        if (cc < ncol) smem_add<COUNT>(acc + cc, HETERO ? __fmul_rn(v, hw) : v);
       } else {
         for (int64_t p = s + lane; p < e; p += 32) {
           const uint32_t cc = (uint32_t)(__ldg(idx + p) - col0);
-          if (cc < ncol) smem_add(acc + cc, HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
+          if (cc < ncol) smem_add<COUNT>(acc + cc, HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
         }
       }
     }
     __syncthreads();
     lo = hi;
   }
-  // ---- write the slice
+  // ---- write the slice (hit counts become count * weight here, rounded once)
   float* __restrict__ ob = out + b * n_post + col0;
+  auto value = [&](float slot) { return COUNT ? __fmul_rn(__uint2float_rn(__float_as_uint(slot)), w0) : slot; };
   if (((reinterpret_cast<uintptr_t>(ob) & 15) == 0) && (ncol % 4 == 0)) {
     float4* o4 = reinterpret_cast<float4*>(ob);
     const float4* a4 = reinterpret_cast<const float4*>(acc);
     for (int i = tid; i < (int)(ncol / 4); i += kSsThreads) {
       float4 r = a4[i];
+      r.x = value(r.x); r.y = value(r.y); r.z = value(r.z); r.w = value(r.w);
       if (accumulate) {
         const float4 old = o4[i];
         r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
@@ -277,7 +295,7 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
       o4[i] = r;
     }
   } else {
-    for (int i = tid; i < (int)ncol; i += kSsThreads) ob[i] = accumulate ? ob[i] + acc[i] : acc[i];
+    for (int i = tid; i < (int)ncol; i += kSsThreads) ob[i] = accumulate ? ob[i] + value(acc[i]) : value(acc[i]);
   }
 }
 

@@ -464,6 +464,13 @@ class EINet:
         self._links = state
         self._seq = 0
 
+    def prepare(self):
+        """One-time set-up that would otherwise happen inside the first ``run``: the launch
+        geometry and, with several ranks, the inboxes and their peer mappings (collective)."""
+        if self.shard_kernel and self._links is None:
+            self._setup_links()
+        return self
+
     def _run_shard_kernel(self, steps: int, record: bool):
         """All steps in one cooperative launch per GPU; the spike ids travel by peer stores
         inside the kernel.  The raster of the whole network is assembled from the ranks'
