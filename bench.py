@@ -394,6 +394,20 @@ def run_ours(args):
     events_all = float(ev_all.item())
     value = events_all * args.steps / (ms_total_max * 1e-3)
 
+    if args.only:             # one leg, for the profiler
+        peak, _ = measured_hbm_peak()
+        if args.only == 'training':
+            out = run_training_step(torch, dev, dp, peak)
+        elif args.only == 'single':
+            out = run_single_vector(torch, dev, dp, peak, calls=8)
+        else:
+            out = [c for c in run_cases(torch, dev, dp, peak, rates=(0.01,)) if c['weights'] == 'homogeneous']
+        if rank == 0:
+            print(json.dumps({'only': args.only, 'result': out}))
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
     if args.profile:          # device loop only: what the profiler captures
         if rank == 0:
             print(json.dumps({'profile_run': True, 'value': value, 'ms_per_step': ms_total_max / args.steps}))
@@ -650,7 +664,7 @@ def _time(torch, fn, reps=5, warm=3):
     return a.elapsed_time(b) * 1e-3 / reps
 
 
-def run_cases(torch, dev, dp, peak):
+def run_cases(torch, dev, dp, peak, rates=(0.001, 0.01, 0.1)):
     """The microbenchmark grid: firing rates 0.1 / 1 / 10 %, homogeneous (0.1) and
     heterogeneous weights, both products — ``spike@W`` as the batched scatter, ``W@spike``
     both event-driven (scatter over the transposed copy) and as the deterministic gather
@@ -663,7 +677,8 @@ def run_cases(torch, dev, dp, peak):
     homo = FixedPostNumConn((0.1, dp.ti), shape=(n, n))
     homo._derived = dp.conn._derived           # same connectivity: share the derived layouts
     out = []
-    for r_id, rate in enumerate((0.001, 0.01, 0.1)):
+    for rate in rates:
+        r_id = (0.001, 0.01, 0.1).index(rate)
         spk = np.random.RandomState(210 + r_id).random_sample((T, n)) < rate
         sd = torch.from_numpy(spk).to(dev)
         events = float(spk.sum()) * K
@@ -684,8 +699,21 @@ def run_cases(torch, dev, dp, peak):
                 _lib.check(lib.bsx_event_matvec(C.byref(st), sd.data_ptr(), _lib.SPK_BOOL8, T, dp.y_matvec.data_ptr(),
                                                 dp.mv_ws.data_ptr(), dp.mv_ws_bytes, stream))
 
+            scale_s, scale_ts = conn._fixed_scale('s', st_s, conn.data), conn._fixed_scale('ts', st_ts, conn.data)
+
+            def vecmat_fixed():
+                _lib.check(lib.bsx_event_vecmat_sliced_fixed(C.byref(st_s), sd.data_ptr(), _lib.SPK_BOOL8, T,
+                                                             dp.y_vecmat.data_ptr(), 0, scale_s, stream))
+
+            def matvec_fixed():
+                _lib.check(lib.bsx_event_vecmat_sliced_fixed(C.byref(st_ts), sd.data_ptr(), _lib.SPK_BOOL8, T,
+                                                             dp.y_matvec.data_ptr(), 0, scale_ts, stream))
+
             scatter_bytes = events * (4 + 4 * h) + T * (n + 4 * n)
-            for prod, fn, alg in (('spike@W, scatter (output slices in shared memory)', vecmat_sliced, scatter_bytes),
+            fixed = (('spike@W, fixed-point scatter (deterministic)', vecmat_fixed, scatter_bytes),
+                     ('W@spike, fixed-point scatter over the transposed copy (deterministic)', matvec_fixed,
+                      scatter_bytes)) if h else ()
+            for prod, fn, alg in fixed + (('spike@W, scatter (output slices in shared memory)', vecmat_sliced, scatter_bytes),
                                   ('W@spike, event-driven scatter over the transposed copy', matvec_sliced, scatter_bytes),
                                   ('W@spike, deterministic gather (16 vectors per pass)', matvec_b16,
                                    dp.passes * (n * K * 4 + 2 * n) + T * 4 * n + events * 4 * h)):
@@ -805,7 +833,12 @@ def main():
                     help='one GPU: write the per-step spike counts of the network runs to gpurun_out/network_counts.npz')
     ap.add_argument('--profile', action='store_true',
                     help='run only the device-resident loop (for ncu); prints no bench line')
+    ap.add_argument('--only', default=None, choices=['training', 'single', 'homogeneous'],
+                    help='for ncu: build the workload, run that one leg (training step; single-vector calls; the '
+                         'batched scatter with homogeneous weights) and exit')
     args = ap.parse_args()
+    if args.only:
+        args.profile = True           # no long warm-up, no gather loop: only what the profiler should see
     if args.impl == 'reference':
         return run_reference_arm(args)
     return run_ours(args)

@@ -19,6 +19,7 @@ BSX_ERR_INDEX_RANGE = -3
 BSX_ERR_WORKSPACE = -4
 BSX_ERR_UNSUPPORTED = -5
 BSX_ERR_TIMEOUT = -6
+BSX_ERR_NONFINITE = -7
 
 VECMAT_GLOBAL_ATOMICS, VECMAT_SHARED_SLICES = 0, 1
 LINK_EARLY_PUSH, LINK_FETCH_AHEAD, LINK_DEFAULT = 1, 2, 3
@@ -116,6 +117,9 @@ SIGNATURES = {
     'bsx_sliced_slices': (_i64, [_i64]),
     'bsx_sliced_build': (_i32, [_connp, _vp, _vp, _vp, _vp]),
     'bsx_event_vecmat_sliced': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp]),
+    'bsx_fixed_scale_workspace_bytes': (_sz, [_i64]),
+    'bsx_fixed_scale_log2': (_i32, [_connp, _vp, _sz, C.POINTER(C.c_int32), _vp]),
+    'bsx_event_vecmat_sliced_fixed': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
     'bsx_event_vecmat_static': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _vp]),
     'bsx_float_vecmat': (_i32, [_connp, _vp, _i64, _vp, _i32, _vp, _sz, _vp]),
     'bsx_event_matvec_workspace_bytes': (_sz, [_i64, _i64]),

@@ -101,6 +101,7 @@ const char* bsx_status_name(int status) {
     case BSX_ERR_WORKSPACE: return "BSX_ERR_WORKSPACE";
     case BSX_ERR_UNSUPPORTED: return "BSX_ERR_UNSUPPORTED";
     case BSX_ERR_TIMEOUT: return "BSX_ERR_TIMEOUT";
+    case BSX_ERR_NONFINITE: return "BSX_ERR_NONFINITE";
     default: return "BSX_ERR_UNKNOWN";
   }
 }

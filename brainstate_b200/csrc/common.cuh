@@ -10,7 +10,21 @@
 #error "bsx is written for sm_100a (B200) only"
 #endif
 
+#include <nvtx3/nvToolsExt.h>
+
 namespace bsx {
+
+// Names the enclosing scope for timeline tools (an NVTX range; a no-op costing a few nanoseconds
+// when no tool is attached).  Placed at the top of every compute entry point, so that a trace
+// shows which C-ABI call each kernel belongs to — the counterpart of the named scopes the
+// reference gets from jax.named_scope around its operators.
+struct NvtxScope {
+  explicit NvtxScope(const char* name) { nvtxRangePushA(name); }
+  ~NvtxScope() { nvtxRangePop(); }
+  NvtxScope(const NvtxScope&) = delete;
+  NvtxScope& operator=(const NvtxScope&) = delete;
+};
+#define BSX_TRACE(name) ::bsx::NvtxScope bsx_nvtx_scope_(name)
 
 // ---- host-side error plumbing (thread-local message, integer codes) --------
 int fail(int status, const char* fmt, ...);

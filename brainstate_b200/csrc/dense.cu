@@ -86,6 +86,7 @@ using namespace bsx;
 extern "C" int bsx_dense_event_vecmat(const void* spikes, int spike_format, const float* weight,
                                       int64_t batch, int64_t n_pre, int64_t n_post, float* out,
                                       bsx_stream_t stream) {
+  BSX_TRACE("bsx_dense_event_vecmat");
   if (batch < 0 || n_pre < 0 || n_post < 0) return fail(BSX_ERR_INVALID_ARG, "negative size");
   if (batch == 0 || n_post == 0) return BSX_OK;
   if (!out) return fail(BSX_ERR_INVALID_ARG, "out is NULL");

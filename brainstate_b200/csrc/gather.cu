@@ -262,6 +262,7 @@ size_t bsx_event_matvec_workspace_bytes(int64_t batch, int64_t n_post) {
 int bsx_event_matvec_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                            float* out, void* workspace, size_t workspace_bytes, int blocks_per_sm,
                            int mask_mode, int unroll, bsx_stream_t stream) {
+  BSX_TRACE("bsx_event_matvec_tuned");
   int rc = check_conn(conn);
   if (rc) return rc;
   if (batch < 0) return fail(BSX_ERR_INVALID_ARG, "negative batch");
@@ -348,6 +349,7 @@ int bsx_event_matvec(const bsx_conn_t* conn, const void* spikes, int spike_forma
 }
 
 int bsx_float_matvec(const bsx_conn_t* conn, const float* v, int64_t batch, float* out, bsx_stream_t stream) {
+  BSX_TRACE("bsx_float_matvec");
   int rc = check_conn(conn);
   if (rc) return rc;
   if (batch < 0) return fail(BSX_ERR_INVALID_ARG, "negative batch");
@@ -374,6 +376,7 @@ int bsx_float_matvec(const bsx_conn_t* conn, const float* v, int64_t batch, floa
 
 int bsx_vecmat_vjp(const bsx_conn_t* conn, const void* x, int x_format, int event, const float* ct,
                    int64_t batch, float* dx, float* dw, bsx_stream_t stream) {
+  BSX_TRACE("bsx_vecmat_vjp");
   int rc = check_conn(conn);
   if (rc) return rc;
   if (batch < 0) return fail(BSX_ERR_INVALID_ARG, "negative batch");

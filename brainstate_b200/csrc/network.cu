@@ -598,6 +598,7 @@ extern "C" {
 
 int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t steps, int64_t step0,
                 uint32_t* raster, int32_t* spike_counts, int32_t blocks, bsx_stream_t stream) {
+  BSX_TRACE("bsx_net_run");
   if (!params) return fail(BSX_ERR_INVALID_ARG, "params is NULL");
   if (steps < 0 || step0 < 0) return fail(BSX_ERR_INVALID_ARG, "bad step range");
   NetDev a;
@@ -648,6 +649,7 @@ int bsx_net_run(const bsx_net_t* net, const bsx_lif_params_t* params, int32_t st
 }
 
 int bsx_net_scatter(const bsx_net_t* net, int64_t step, bsx_stream_t stream) {
+  BSX_TRACE("bsx_net_scatter");
   if (step < 0) return fail(BSX_ERR_INVALID_ARG, "negative step");
   NetDev a;
   int rc = make_net(net, nullptr, &a);
@@ -661,6 +663,7 @@ int bsx_net_scatter(const bsx_net_t* net, int64_t step, bsx_stream_t stream) {
 
 int bsx_net_update(const bsx_net_t* net, const bsx_lif_params_t* params, int64_t step, int32_t* local_count,
                    bsx_stream_t stream) {
+  BSX_TRACE("bsx_net_update");
   if (!params) return fail(BSX_ERR_INVALID_ARG, "params is NULL");
   if (step < 0) return fail(BSX_ERR_INVALID_ARG, "negative step");
   NetDev a;
@@ -677,6 +680,7 @@ int bsx_net_update(const bsx_net_t* net, const bsx_lif_params_t* params, int64_t
 }
 
 int bsx_net_list_from_bits(const bsx_net_t* net, int64_t step, bsx_stream_t stream) {
+  BSX_TRACE("bsx_net_list_from_bits");
   if (step < 0) return fail(BSX_ERR_INVALID_ARG, "negative step");
   NetDev a;
   int rc = make_net(net, nullptr, &a);

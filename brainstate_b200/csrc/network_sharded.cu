@@ -375,6 +375,8 @@ net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t
             if (o.r != r) a.ref[i] = o.r;
           }
           spk = o.spk;
+          // NaN or infinity in the membrane potential or a synaptic variable (they propagate through the sum)
+          if (!(fabsf(o.V) + fabsf(o.ge) + fabsf(o.gi) <= 3.0e38f)) atomicCAS(L.sync, 0, (int32_t)BSX_ERR_NONFINITE);
         }
         const uint32_t m = __ballot_sync(0xffffffffu, spk);
         if (lane == 0) {
@@ -495,6 +497,7 @@ size_t bsx_net_inbox_bytes(int32_t world, int32_t blocks, int32_t words_per_bloc
 int bsx_net_run_sharded(const bsx_net_shard_t* net, const bsx_lif_params_t* params, const bsx_net_links_t* links,
                         int32_t steps, int64_t step0, uint32_t* raster, int32_t* spike_counts,
                         bsx_stream_t stream) {
+  BSX_TRACE("bsx_net_run_sharded");
   if (!net || !params || !links) return fail(BSX_ERR_INVALID_ARG, "net, params or links is NULL");
   if (steps < 0 || step0 < 0 || links->seq0 < 0) return fail(BSX_ERR_INVALID_ARG, "bad step range");
   if (steps > (1 << 24)) return fail(BSX_ERR_UNSUPPORTED, "at most 2^24 steps per launch");

@@ -168,6 +168,7 @@ size_t bsx_event_vecmat_workspace_bytes(int64_t batch, int64_t n_pre) {
 int bsx_event_vecmat_tuned(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
                            float* out, int accumulate, void* workspace, size_t workspace_bytes,
                            int chunk, int blocks_per_sm, bsx_stream_t stream) {
+  BSX_TRACE("bsx_event_vecmat_tuned");
   if (spike_format < BSX_SPK_BOOL8 || spike_format > BSX_SPK_LIST)
     return fail(BSX_ERR_INVALID_ARG, "unknown spike format %d", spike_format);
   return vecmat_common(conn, spikes, spike_format, nullptr, batch, out, accumulate, workspace,
@@ -200,6 +201,7 @@ int bsx_event_vecmat(const bsx_conn_t* conn, const void* spikes, int spike_forma
 
 int bsx_float_vecmat(const bsx_conn_t* conn, const float* x, int64_t batch, float* out, int accumulate,
                      void* workspace, size_t workspace_bytes, bsx_stream_t stream) {
+  BSX_TRACE("bsx_float_vecmat");
   return vecmat_common(conn, x, BSX_SPK_F32, x, batch, out, accumulate, workspace, workspace_bytes, 0, 0,
                        as_stream(stream));
 }

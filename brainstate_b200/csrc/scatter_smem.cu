@@ -41,10 +41,18 @@ __device__ __forceinline__ void smem_count(float* p) {   // the slot holds a uin
 // COUNT (homogeneous weights, event input): the slice holds integer hit counts, added with the
 // native shared-memory integer atomic (the float add is a load + compare-and-swap loop), and
 // is multiplied by the weight once when it is written out.
-template <bool COUNT>
+// FIXED: the slot holds a signed 32-bit fixed-point sum; v arrives already scaled by 2^s.  Integer
+// addition is associative, so the result does not depend on the order of the adds.
+template <bool COUNT, bool FIXED = false>
 __device__ __forceinline__ void smem_add(float* p, float v) {
-  if (COUNT) smem_count(p);
-  else smem_add_f32(p, v);
+  if (COUNT) {
+    smem_count(p);
+  } else if (FIXED) {
+    const int q = __float2int_rn(v);
+    asm volatile("red.shared.add.s32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "r"(q) : "memory");
+  } else {
+    smem_add_f32(p, v);
+  }
 }
 
 // Active spikes among the positions [i0, i1) of batch row b; their positions go to dst
@@ -99,11 +107,12 @@ __device__ __forceinline__ void add_four(float* acc, int32_t col0, uint32_t ncol
   if (c3 < ncol) smem_add<COUNT>(acc + c3, HETERO ? __fmul_rn(v, t.w) : v);
 }
 
-template <bool HETERO, bool HAS_X, int FORMAT, bool SLICED>
+template <bool HETERO, bool HAS_X, int FORMAT, bool SLICED, bool FIXED = false>
 __global__ void __launch_bounds__(kSsThreads, 1)
 scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
                     const void* __restrict__ spikes, const float* __restrict__ x, int64_t n_pre,
-                    int64_t n_post, float* __restrict__ out, int accumulate, bool vec_ok, int row_mul) {
+                    int64_t n_post, float* __restrict__ out, int accumulate, bool vec_ok, int row_mul,
+                    float scale = 1.0f, float inv_scale = 1.0f) {
   constexpr bool COUNT = !HETERO && !HAS_X;     // every event adds the same value: count, multiply once
   extern __shared__ __align__(16) unsigned char ss_raw[];
   float* acc = reinterpret_cast<float*>(ss_raw);
@@ -214,6 +223,7 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
       const int64_t s = row_start[t], e = s + row_len[t];
       float v = HAS_X ? __ldg(x + b * n_pre + row) : 1.0f;
       if (!HETERO) v = __fmul_rn(v, w0);
+      if (FIXED) v = __fmul_rn(v, scale);            // a power of two: exact
       if (SLICED) {
         // the group is laid out in 32-entry stretches whose entries fall into distinct banks:
         // one coalesced 4-byte load per lane and stretch, all issued before the first add
@@ -229,7 +239,7 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
 #pragma unroll
           for (int u = 0; u < kSsDeal; ++u) {
             const uint32_t cc = (uint32_t)(j[u] - col0);
-            if (cc < ncol) smem_add<COUNT>(acc + cc, HETERO ? __fmul_rn(v, t[u]) : v);
+            if (cc < ncol) smem_add<COUNT, FIXED>(acc + cc, HETERO ? __fmul_rn(v, t[u]) : v);
           }
         }
         continue;
@@ -281,7 +291,11 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
   }
   // ---- write the slice (hit counts become count * weight here, rounded once)
   float* __restrict__ ob = out + b * n_post + col0;
-  auto value = [&](float slot) { return COUNT ? __fmul_rn(__uint2float_rn(__float_as_uint(slot)), w0) : slot; };
+  auto value = [&](float slot) {
+    if (COUNT) return __fmul_rn(__uint2float_rn(__float_as_uint(slot)), w0);
+    if (FIXED) return __fmul_rn(__int2float_rn(__float_as_int(slot)), inv_scale);
+    return slot;
+  };
   if (((reinterpret_cast<uintptr_t>(ob) & 15) == 0) && (ncol % 4 == 0)) {
     float4* o4 = reinterpret_cast<float4*>(ob);
     const float4* a4 = reinterpret_cast<const float4*>(acc);
@@ -411,6 +425,55 @@ bool scatter_smem_preferred(const bsx_conn_t* conn, int format, int64_t batch) {
   return sms > 0 && slices <= 2 && batch * slices * 4 >= (int64_t)sms * 3;
 }
 
+// Deterministic form over the sliced layout: heterogeneous weights summed in 2^-scale_log2 fixed point.
+static int launch_scatter_smem_fixed(const bsx_conn_t* conn, const void* spikes, int format, int64_t batch, float* out,
+                                     int accumulate, cudaStream_t st, int row_mul, int scale_log2) {
+  if (sm_count() <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  const int64_t slices = (conn->n_post + kSsSlice - 1) / kSsSlice;
+  const dim3 grid((unsigned)slices, (unsigned)batch, 1);
+  const size_t smem = sizeof(float) * kSsSlice + (sizeof(int64_t) + 2 * sizeof(int32_t)) * kSsList;
+  const bool vec_ok = aligned16(conn->indices) && aligned16(conn->weights);
+  const RowMap rm = make_rowmap(conn);
+  const float scale = ldexpf(1.0f, scale_log2), inv_scale = ldexpf(1.0f, -scale_log2);
+#define BSX_SSF(F)                                                                                                   \
+  do {                                                                                                               \
+    BSX_CUDA(cudaFuncSetAttribute(scatter_smem_kernel<true, false, F, true, true>,                                   \
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                          \
+    scatter_smem_kernel<true, false, F, true, true><<<grid, kSsThreads, smem, st>>>(                                 \
+        rm, conn->indices, conn->weights, spikes, nullptr, conn->n_pre, conn->n_post, out, accumulate, vec_ok, row_mul, \
+        scale, inv_scale);                                                                                           \
+  } while (0)
+  if (format == BSX_SPK_BOOL8) BSX_SSF(BSX_SPK_BOOL8);
+  else if (format == BSX_SPK_F32) BSX_SSF(BSX_SPK_F32);
+  else BSX_SSF(BSX_SPK_BITS32);
+#undef BSX_SSF
+  BSX_LAUNCH_CHECK("scatter_smem_kernel<fixed>");
+  return BSX_OK;
+}
+
+// |w| summed per output column as 2^-32 fixed point (order-free), then the largest column.
+__global__ void __launch_bounds__(256)
+abs_sum_kernel(const int32_t* __restrict__ idx, const float* __restrict__ w, int64_t nnz,
+               unsigned long long* __restrict__ col_sum) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < nnz; p += stride) {
+    const unsigned long long q = (unsigned long long)__float2ll_rn(fabsf(__ldg(w + p)) * 4294967296.0f);
+    atomicAdd(col_sum + __ldg(idx + p), q);
+  }
+}
+__global__ void __launch_bounds__(256)
+max_u64_kernel(const unsigned long long* __restrict__ v, int64_t n, unsigned long long* __restrict__ out) {
+  unsigned long long m = 0;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) m = v[i] > m ? v[i] : m;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long t = __shfl_xor_sync(0xffffffffu, m, o);
+    m = t > m ? t : m;
+  }
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+}
+
 int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, const float* x, int64_t batch,
                         float* out, int accumulate, cudaStream_t st, int row_mul) {
   if (sm_count() <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
@@ -460,6 +523,7 @@ int64_t bsx_sliced_slices(int64_t n_post) { return n_post <= 0 ? 0 : (n_post + k
 
 int bsx_sliced_build(const bsx_conn_t* conn, int64_t* s_indptr, int32_t* s_indices, int32_t* s_perm,
                      bsx_stream_t stream) {
+  BSX_TRACE("bsx_sliced_build");
   const int rc = check_conn(conn);
   if (rc) return rc;
   const int64_t S = bsx_sliced_slices(conn->n_post);
@@ -481,6 +545,7 @@ int bsx_sliced_build(const bsx_conn_t* conn, int64_t* s_indptr, int32_t* s_indic
 
 int bsx_event_vecmat_sliced(const bsx_conn_t* sliced, const void* spikes, int spike_format, int64_t batch,
                             float* out, int accumulate, bsx_stream_t stream) {
+  BSX_TRACE("bsx_event_vecmat_sliced");
   const int rc = check_conn(sliced);
   if (rc) return rc;
   if (!sliced->indptr || !sliced->indptr_is_64)
@@ -495,6 +560,68 @@ int bsx_event_vecmat_sliced(const bsx_conn_t* sliced, const void* spikes, int sp
   const int64_t S = bsx_sliced_slices(sliced->n_post);
   if (S > 4 || batch > 65535) return fail(BSX_ERR_UNSUPPORTED, "the sliced scatter covers up to 131072 columns and 65535 vectors");
   return launch_scatter_smem(sliced, spikes, spike_format, nullptr, batch, out, accumulate, as_stream(stream), (int)S);
+}
+
+size_t bsx_fixed_scale_workspace_bytes(int64_t n_post) {
+  return n_post < 0 ? 0 : ((size_t)(n_post + 1) * sizeof(unsigned long long) + 255) & ~size_t(255);
+}
+
+int bsx_fixed_scale_log2(const bsx_conn_t* conn, void* workspace, size_t workspace_bytes, int32_t* host_scale_log2,
+                         bsx_stream_t stream) {
+  BSX_TRACE("bsx_fixed_scale_log2");
+  const int rc = check_conn(conn);
+  if (rc) return rc;
+  if (!host_scale_log2) return fail(BSX_ERR_INVALID_ARG, "host_scale_log2 is NULL");
+  *host_scale_log2 = 0;
+  if (!conn->hetero || conn->nnz == 0 || conn->n_post == 0) return BSX_OK;     // counted, not summed: nothing to scale
+  const size_t need = bsx_fixed_scale_workspace_bytes(conn->n_post);
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < need)
+    return fail(BSX_ERR_WORKSPACE, "bsx_fixed_scale_log2 needs %zu workspace bytes", need);
+  const int sms = sm_count();
+  if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  cudaStream_t st = as_stream(stream);
+  unsigned long long* col = static_cast<unsigned long long*>(workspace);
+  BSX_CUDA(cudaMemsetAsync(col, 0, need, st));
+  abs_sum_kernel<<<(unsigned)(sms * 8), 256, 0, st>>>(conn->indices, conn->weights, conn->nnz, col);
+  BSX_LAUNCH_CHECK("abs_sum_kernel");
+  max_u64_kernel<<<(unsigned)(sms * 2), 256, 0, st>>>(col, conn->n_post, col + conn->n_post);
+  BSX_LAUNCH_CHECK("max_u64_kernel");
+  unsigned long long host_max = 0;
+  BSX_CUDA(cudaMemcpyAsync(&host_max, col + conn->n_post, sizeof(host_max), cudaMemcpyDeviceToHost, st));
+  BSX_CUDA(cudaStreamSynchronize(st));
+  // the largest |sum| any output can reach is host_max * 2^-32; keep it below 2^30 after scaling
+  double bound = (double)host_max / 4294967296.0;
+  int s = 30;
+  if (bound > 0.0) {
+    s = (int)floor(log2(1073741824.0 / bound));
+    if (s > 30) s = 30;
+    if (s < -60) s = -60;
+  }
+  *host_scale_log2 = s;
+  return BSX_OK;
+}
+
+int bsx_event_vecmat_sliced_fixed(const bsx_conn_t* sliced, const void* spikes, int spike_format, int64_t batch,
+                                  float* out, int accumulate, int32_t scale_log2, bsx_stream_t stream) {
+  BSX_TRACE("bsx_event_vecmat_sliced_fixed");
+  const int rc = check_conn(sliced);
+  if (rc) return rc;
+  if (!sliced->hetero)        // homogeneous weights are counted as integers already: order-free as it is
+    return bsx_event_vecmat_sliced(sliced, spikes, spike_format, batch, out, accumulate, stream);
+  if (!sliced->indptr || !sliced->indptr_is_64)
+    return fail(BSX_ERR_INVALID_ARG, "the sliced layout has 64-bit group offsets in indptr");
+  if (batch < 0) return fail(BSX_ERR_INVALID_ARG, "negative batch");
+  if (scale_log2 < -60 || scale_log2 > 30) return fail(BSX_ERR_INVALID_ARG, "scale_log2 out of range (see bsx_fixed_scale_log2)");
+  if (batch == 0 || sliced->n_post == 0) return BSX_OK;
+  if (!out) return fail(BSX_ERR_INVALID_ARG, "out is NULL");
+  if (sliced->n_pre == 0) return accumulate ? BSX_OK : launch_zero(out, batch * sliced->n_post, as_stream(stream));
+  if (!spikes) return fail(BSX_ERR_INVALID_ARG, "input vector is NULL");
+  if (spike_format != BSX_SPK_BOOL8 && spike_format != BSX_SPK_F32 && spike_format != BSX_SPK_BITS32)
+    return fail(BSX_ERR_UNSUPPORTED, "the sliced scatter takes byte, float or packed spikes");
+  const int64_t S = bsx_sliced_slices(sliced->n_post);
+  if (S > 4 || batch > 65535) return fail(BSX_ERR_UNSUPPORTED, "the sliced scatter covers up to 131072 columns and 65535 vectors");
+  return launch_scatter_smem_fixed(sliced, spikes, spike_format, batch, out, accumulate, as_stream(stream), (int)S,
+                                   scale_log2);
 }
 
 }  // extern "C"

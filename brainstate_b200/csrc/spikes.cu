@@ -203,6 +203,7 @@ using namespace bsx;
 
 extern "C" int bsx_pack_spikes(const void* spikes, int spike_format, int64_t batch, int64_t n,
                                uint32_t* bits, bsx_stream_t stream) {
+  BSX_TRACE("bsx_pack_spikes");
   if (batch < 0 || n < 0) return fail(BSX_ERR_INVALID_ARG, "bsx_pack_spikes: negative size");
   if (batch == 0 || n == 0) return BSX_OK;
   if (!spikes || !bits) return fail(BSX_ERR_INVALID_ARG, "bsx_pack_spikes: NULL buffer");

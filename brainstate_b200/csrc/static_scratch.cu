@@ -47,6 +47,7 @@ using namespace bsx;
 
 extern "C" int bsx_event_vecmat_static(const bsx_conn_t* conn, const void* spikes, int spike_format,
                                        int64_t batch, float* out, int accumulate, bsx_stream_t stream) {
+  BSX_TRACE("bsx_event_vecmat_static");
   if (spike_format < BSX_SPK_BOOL8 || spike_format > BSX_SPK_LIST)
     return fail(BSX_ERR_INVALID_ARG, "unknown spike format %d", spike_format);
   if (!conn) return fail(BSX_ERR_INVALID_ARG, "conn is NULL");

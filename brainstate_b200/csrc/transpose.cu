@@ -153,6 +153,7 @@ using namespace bsx;
 extern "C" {
 
 int bsx_validate_conn(const bsx_conn_t* conn, int32_t* status_word, bsx_stream_t stream) {
+  BSX_TRACE("bsx_validate_conn");
   int rc = check_conn(conn);
   if (rc) return rc;
   if (!status_word) return fail(BSX_ERR_INVALID_ARG, "status word is NULL");
@@ -175,6 +176,7 @@ size_t bsx_transpose_workspace_bytes(int64_t n_pre, int64_t n_post, int64_t nnz)
 
 int bsx_transpose_build(const bsx_conn_t* conn, int64_t nnz, int64_t* t_indptr, int32_t* t_indices,
                         int32_t* t_perm, void* workspace, size_t workspace_bytes, bsx_stream_t stream) {
+  BSX_TRACE("bsx_transpose_build");
   int rc = check_conn(conn);
   if (rc) return rc;
   if (nnz != conn->nnz) return fail(BSX_ERR_INVALID_ARG, "nnz argument differs from conn->nnz");

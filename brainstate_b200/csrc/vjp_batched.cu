@@ -207,6 +207,7 @@ size_t bsx_vecmat_vjp_batched_workspace_bytes(int64_t batch, int64_t n_post) {
 int bsx_vecmat_vjp_batched(const bsx_conn_t* conn, const void* x, int x_format, int event, const float* ct,
                            int64_t batch, float* dx, float* dw, void* workspace, size_t workspace_bytes,
                            bsx_stream_t stream) {
+  BSX_TRACE("bsx_vecmat_vjp_batched");
   int rc = check_conn(conn);
   if (rc) return rc;
   if (batch < 0) return fail(BSX_ERR_INVALID_ARG, "negative batch");

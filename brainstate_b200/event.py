@@ -269,6 +269,29 @@ class _SparseConn:
         s._keep = (wt, s_indptr, s_indices)
         return s
 
+    def _fixed_scale(self, layout: str, st: BsxConn, weights: torch.Tensor) -> int:
+        """Scale (log2) of the fixed-point scatter over a derived layout: the largest that cannot
+        overflow, from the largest column sum of ``|w|``.  Kept until the weight tensor changes."""
+        if not self.hetero:
+            return 0
+        wsrc = weights.contiguous()
+        key = (wsrc.data_ptr(), wsrc._version, wsrc.numel())
+        cached = self._derived.get('scale_' + layout)
+        if cached is not None and cached[0] == key:
+            return cached[1]
+        nbytes = lib().bsx_fixed_scale_workspace_bytes(st.n_post)
+        ws = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=self.indices.device)
+        s = C.c_int32(0)
+        check(lib().bsx_fixed_scale_log2(C.byref(st), ptr(ws), nbytes, C.byref(s), _lib.current_stream()))
+        self._derived['scale_' + layout] = (key, int(s.value))
+        return int(s.value)
+
+    @staticmethod
+    def _fixed_applies(n_out: int, batch: int) -> bool:
+        """The fixed-point scatter keeps output slices in shared memory: batches of 16 and more
+        over at most 131 072 outputs."""
+        return 16 <= batch <= 65535 and n_out <= 131072
+
     # -- products ------------------------------------------------------------------
     def _vecmat(self, x, event: bool, method: str = 'scatter'):
         return _VecMat.apply(x, self.data, self, event, method)
@@ -334,6 +357,15 @@ def _raw_vecmat(conn: _SparseConn, x: torch.Tensor, weights: torch.Tensor, event
         out = torch.empty((batch, n_post), dtype=torch.float32, device=x.device)
         accumulate = False
     stream = _lib.current_stream()
+    if method == 'fixed':
+        # order-free sums: the fixed-point scatter where it applies, the order-fixing gather elsewhere
+        if event and conn._fixed_applies(n_post, batch):
+            st_s = conn._sliced_struct(weights)
+            scale = conn._fixed_scale('s', st_s, weights)
+            check(lib().bsx_event_vecmat_sliced_fixed(C.byref(st_s), ptr(xb), spike_format_of(xb), batch, ptr(out),
+                                                      int(accumulate), scale, stream))
+            return out.reshape(lead + (n_post,))
+        method = 'gather' if event else 'scatter'
     if event and method == 'gather':
         # deterministic post-centric form: event matvec over the transposed copy
         st = conn._transposed_struct(weights)
@@ -348,7 +380,7 @@ def _raw_vecmat(conn: _SparseConn, x: torch.Tensor, weights: torch.Tensor, event
             check(lib().bsx_event_matvec(C.byref(st), ptr(xb), fmt, batch, ptr(out), ptr(ws), ws_bytes, stream))
         return out.reshape(lead + (n_post,))
     if method not in ('scatter', 'gather'):
-        raise ValueError(f"method must be 'scatter' or 'gather', got {method!r}")
+        raise ValueError(f"method must be 'scatter', 'gather' or 'fixed', got {method!r}")
     st = conn._struct(weights)
     if event and lib().bsx_event_vecmat_variant(C.byref(st), spike_format_of(xb), batch) == _lib.VECMAT_SHARED_SLICES:
         # a batch that fills the GPU: one launch over the copy whose rows are grouped by output slice
@@ -388,10 +420,13 @@ def event_matvec(conn: _SparseConn, spk: torch.Tensor, bits: bool = False, metho
         active postsynaptic neurons scatter along the transposed copy (built once), cost
         proportional to the events — about twice as fast at 1 % firing, slower above ≈ 3 %;
         heterogeneous sums then depend on the order of the atomic adds (last-bit differences).
+        ``'fixed'`` is the event-driven form with the sums in fixed point (batches of 16 and
+        more; the gather otherwise): as fast as ``'scatter'`` and as reproducible as ``'gather'``,
+        every addend rounded to ``2^-scale`` (``bsx_fixed_scale_log2``).
     """
     _require_cuda(spk, 'spikes')
-    if method not in ('gather', 'scatter'):
-        raise ValueError(f"method must be 'gather' or 'scatter', got {method!r}")
+    if method not in ('gather', 'scatter', 'fixed'):
+        raise ValueError(f"method must be 'gather', 'scatter' or 'fixed', got {method!r}")
     n_pre, n_post = conn.shape
     if bits:
         words = (n_post + 31) // 32
@@ -402,6 +437,14 @@ def event_matvec(conn: _SparseConn, spk: torch.Tensor, bits: bool = False, metho
         fmt = spike_format_of(xb)
     batch = xb.shape[0]
     out = torch.empty((batch, n_pre), dtype=torch.float32, device=spk.device)
+    if method == 'fixed':
+        if conn._fixed_applies(n_pre, batch):
+            st_ts = conn._transposed_sliced_struct(conn.data)
+            scale = conn._fixed_scale('ts', st_ts, conn.data)
+            check(lib().bsx_event_vecmat_sliced_fixed(C.byref(st_ts), ptr(xb), fmt, batch, ptr(out), 0, scale,
+                                                      _lib.current_stream()))
+            return out.reshape(lead + (n_pre,))
+        method = 'gather'
     if method == 'scatter':
         st = conn._transposed_struct(conn.data)
         if lib().bsx_event_vecmat_variant(C.byref(st), fmt, batch) == _lib.VECMAT_SHARED_SLICES:

@@ -145,7 +145,7 @@ class FixedNumConn(Module):
         self.conn_num = conn_num
         self.seed = seed
         self.allow_multi_conn = allow_multi_conn
-        self.method = 'scatter'        # 'gather' = deterministic post-centric forward
+        self.method = 'scatter'        # 'gather' = deterministic post-centric forward; 'fixed' = order-free fixed-point scatter
 
         dev = _device(device)
         if self.conn_num >= 1:

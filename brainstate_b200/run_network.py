@@ -33,6 +33,8 @@ def main():
     ap.add_argument('--steps', type=int, default=1000)
     ap.add_argument('--warmup', type=int, default=100)
     ap.add_argument('--exchange', default='p2p', choices=['p2p', 'nccl'])
+    ap.add_argument('--shard-kernel', action='store_true',
+                    help='one GPU: run the kernel the sharded runs use (increment rows, one barrier per step)')
     ap.add_argument('--deterministic', action='store_true', help='fixed-point synaptic sums: order-free rasters')
     ap.add_argument('--record', action='store_true', help='keep the bit-packed raster (memory: steps * n / 8 bytes)')
     args = ap.parse_args()
@@ -60,7 +62,7 @@ def main():
     t0 = time.perf_counter()
     net = EINet(n_exc, n_inh, K, p['w_e'], p['w_i'], seed_e=p['seed_e'], seed_i=p['seed_i'], V0=V0, params=params,
                 device=dev, group=dist.group.WORLD if world > 1 else None, exchange=args.exchange,
-                deterministic=args.deterministic)
+                deterministic=args.deterministic, shard_kernel=True if args.shard_kernel else None)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
     mem_gb = torch.cuda.max_memory_allocated(dev) / 1e9

@@ -492,6 +492,10 @@ class EINet:
                                         self.step_count, _lib.ptr(mine), counts.data_ptr(), _lib.current_stream()))
         host = C.c_int32(0)
         check(lib().bsx_read_status(self._links['sync'].data_ptr(), C.byref(host), _lib.current_stream()))
+        if host.value == _lib.BSX_ERR_NONFINITE:
+            self._links['sync'].zero_()
+            raise FloatingPointError('a neuron state became NaN or infinite; the run stopped at the end of '
+                                     'that step (BSX_ERR_NONFINITE)')
         if host.value != 0:
             self._drop_links()
             raise RuntimeError('the multi-GPU step kernel gave up waiting for a peer '

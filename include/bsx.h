@@ -44,7 +44,8 @@ typedef enum {
   BSX_ERR_INDEX_RANGE = -3, /* a connectivity index lies outside [0, n_post) */
   BSX_ERR_WORKSPACE = -4,   /* workspace pointer null, misaligned or too small */
   BSX_ERR_UNSUPPORTED = -5, /* a size beyond what the kernels address */
-  BSX_ERR_TIMEOUT = -6      /* a bounded device-side wait ran out */
+  BSX_ERR_TIMEOUT = -6,     /* a bounded device-side wait ran out */
+  BSX_ERR_NONFINITE = -7    /* a neuron's potential or synaptic variable became NaN or infinite (network step) */
 } bsx_status_t;
 
 /* How a spike vector is stored. */
@@ -214,6 +215,26 @@ int bsx_sliced_build(const bsx_conn_t* conn, int64_t* s_indptr, int32_t* s_indic
                      bsx_stream_t stream);
 int bsx_event_vecmat_sliced(const bsx_conn_t* sliced, const void* spikes, int spike_format, int64_t batch,
                             float* out, int accumulate, bsx_stream_t stream);
+
+/*
+ * Deterministic form of the sliced scatter.  No counterpart in the reference.  Heterogeneous
+ * weights are summed in 2^-scale_log2 fixed point (signed 32-bit, native shared-memory integer
+ * atomics), so the result does not depend on the order in which the GPU adds: identical on
+ * every run, and a drop-in for the order-fixing gather at the speed of the scatter.  The
+ * price is absolute precision: every addend is rounded to 2^-scale_log2, so an output is
+ * within (number of its events) * 2^-(scale_log2+1) of the exact sum.  bsx_fixed_scale_log2
+ * picks the largest scale that cannot overflow: it sums |w| per output column (order-free
+ * itself), takes the largest column B and returns floor(log2(2^30 / B)) in *host_scale_log2
+ * (it synchronises the stream; call it once per weight array, not per product).  For the
+ * 65 536 x 655 matrix with weights ~ N(0.1, 0.01), B = 73 and the scale is 2^-23: an output of
+ * 7 events is within 4e-7 of the exact sum.  Homogeneous weights need no scale (events are
+ * counted); the sliced entry point is then called as it is.
+ */
+size_t bsx_fixed_scale_workspace_bytes(int64_t n_post);
+int bsx_fixed_scale_log2(const bsx_conn_t* conn, void* workspace, size_t workspace_bytes, int32_t* host_scale_log2,
+                         bsx_stream_t stream);
+int bsx_event_vecmat_sliced_fixed(const bsx_conn_t* sliced, const void* spikes, int spike_format, int64_t batch,
+                                  float* out, int accumulate, int32_t scale_log2, bsx_stream_t stream);
 
 /*
  * Event vecmat without a workspace argument.  No counterpart in the reference:
@@ -420,7 +441,10 @@ typedef struct bsx_net_shard {
  *              earlier simulation step does not rewind it); equal on all ranks
  *   sync       two local int32: [0] status word, zero on entry, BSX_ERR_TIMEOUT after a
  *              wait of more than spin_limit polls (0 = default, about a second) — the
- *              launch then stops at a step boundary and the inboxes must be set up again;
+ *              launch then stops at a step boundary and the inboxes must be set up again —
+ *              or BSX_ERR_NONFINITE when a neuron's state left the finite range (the
+ *              launch stops at the end of that step; the counterpart of the reference's
+ *              NaN check, brainstate/transform/_debug.py:282-430, at one compare per neuron);
  *              [1] barrier counter, managed by the call
  * With world = 1 no inbox is read.  All ranks must call with the same steps, step0, seq0.
  */

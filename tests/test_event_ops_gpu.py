@@ -694,3 +694,51 @@ def test_layer_calls_build_the_derived_layouts_once(cuda):
     layer.weight.value.mul_(2.0)                            # an in-place update refreshes the weights only
     close(layer(ts[:3]), 2 * ref[:3])
     assert layer.conn._derived['transposed'] is t and layer.conn._derived['w_t'][1] is not w_t
+
+
+@pytest.mark.parametrize('layout', ['fixed', 'csr'])
+def test_fixed_point_scatter_is_deterministic_and_close(layout, bsx, cuda):
+    """``method='fixed'``: the batched scatter with heterogeneous weights summed in 2^-s fixed
+    point (s from ``bsx_fixed_scale_log2``: the largest scale the largest column sum of |w|
+    cannot overflow).  Order-free, so two runs agree bit for bit; every output within
+    (its events) * 2^-(s+1) of the float64 sum, which here is well inside rtol 1e-5 / atol 1e-6;
+    both products; mixed-sign weights; all-active input (the overflow bound is reached)."""
+    from brainstate_b200 import _lib, EventArray
+    from brainstate_b200.event import event_matvec, event_vecmat
+    n, K, B = 3000, 41, 160
+    conn, idx, indptr, w = make(n, n, K, 57, True, cuda, csr_ratio=0.6 if layout == 'csr' else None)
+    w = (w * np.random.RandomState(58).choice([-1.0, 1.0], size=w.shape)).astype(np.float32)
+    conn = conn.with_data(torch.from_numpy(w).to(cuda))
+    spk = np.random.RandomState(59).random_sample((B, n)) < 0.05
+    spk[3] = True                                           # every presynaptic neuron fires in this vector
+    ts = torch.from_numpy(spk).to(cuda)
+    y1 = event_vecmat(conn, ts, method='fixed')
+    y2 = event_vecmat(conn, ts, method='fixed')
+    assert torch.equal(y1, y2)
+    st_s = conn._sliced_struct(conn.data)
+    s = conn._fixed_scale('s', st_s, conn.data)
+    col_abs = np.zeros(n)
+    np.add.at(col_abs, idx.reshape(-1), np.abs(w.reshape(-1)).astype(np.float64))
+    assert s == min(30, int(np.floor(np.log2(2.0 ** 30 / col_abs.max()))))
+    exact = np.zeros((B, n))
+    starts = np.arange(n + 1) * K if indptr is None else indptr.astype(np.int64)
+    for b in range(B):
+        for i in np.nonzero(spk[b])[0]:
+            np.add.at(exact[b], idx.reshape(-1)[starts[i]:starts[i + 1]], w.reshape(-1)[starts[i]:starts[i + 1]].astype(np.float64))
+    events = np.zeros((B, n))
+    for b in range(B):
+        for i in np.nonzero(spk[b])[0]:
+            np.add.at(events[b], idx.reshape(-1)[starts[i]:starts[i + 1]], 1.0)
+    err = np.abs(y1.cpu().numpy().astype(np.float64) - exact)
+    assert np.all(err <= events * 2.0 ** -(s + 1) + np.abs(exact) * 2.0 ** -23 + 1e-12)
+    np.testing.assert_allclose(y1.cpu().numpy(), exact, rtol=RTOL, atol=ATOL)
+    z1 = event_matvec(conn, ts, method='fixed')
+    assert torch.equal(z1, event_matvec(conn, ts, method='fixed'))
+    close(z1, eo.event_matvec(spk, idx, w, n, indptr), scale=3)
+    # below 16 vectors the order-fixing gather serves the request
+    close(event_vecmat(conn, ts[:3], method='fixed'), exact[:3].astype(np.float32), scale=3)
+    # homogeneous weights are counted, which is order-free as it is
+    hom, idx_h, _, _ = make(n, n, K, 57, False, cuda)
+    yh = event_vecmat(hom, ts, method='fixed')
+    counts = eo.event_vecmat(spk, idx_h, np.float32(1.0), n)
+    assert np.array_equal(yh.cpu().numpy(), (counts * np.float32(0.1)).astype(np.float32))

@@ -304,6 +304,18 @@ def test_wait_for_a_silent_peer_runs_out_and_reports(bsx, cuda):
     assert float((x + 1).sum()) == 16.0
 
 
+def test_non_finite_state_stops_the_run_and_is_reported(cuda):
+    """A weight of infinity drives the first target's potential out of the finite range: the
+    kernel records BSX_ERR_NONFINITE, stops at the end of that step and the driver raises."""
+    from brainstate_b200.sim import EINet
+    V0 = np.random.RandomState(102).uniform(-60, -50, 416).astype(np.float32)
+    net = EINet(320, 96, 12, float('inf'), -9.0, seed_e=100, seed_i=101, V0=V0, device=cuda, shard_kernel=True)
+    with pytest.raises(FloatingPointError):
+        net.run(50)
+    ok = EINet(320, 96, 12, 1.62, -9.0, seed_e=100, seed_i=101, V0=V0, device=cuda, shard_kernel=True)
+    assert int(ok.run(50)[1].sum()) > 0                     # the context and the library are fine
+
+
 def test_shard_kernel_checkpoint_and_resume(cuda, tmp_path):
     """Checkpoint of the increment rows: stop after 90 steps, save, rebuild, load, continue."""
     from brainstate_b200.sim import EINet, LIFParams
