@@ -273,17 +273,21 @@ class DevicePass:
         self.scatter_variant = self.lib.bsx_event_vecmat_variant(C.byref(self.st), self._lib.SPK_BOOL8, vectors)
         self.sliced = self.scatter_variant == self._lib.VECMAT_SHARED_SLICES
         per_scatter = 1 if self.sliced else 2
+        self.scale_s = self.scale_t = None
         if self.sliced:       # copies whose rows are grouped by output slice, built once like the matrix
             self.st_s = self.conn._sliced_struct(self.tw)
+            self.scale_s = self.conn._fixed_scale('s', self.st_s, self.tw)       # fixed-point sums: order-free, faster
             if self.matvec_method == 'scatter':
                 self.st_t = self.conn._transposed_sliced_struct(self.tw)
+                self.scale_t = self.conn._fixed_scale('ts', self.st_t, self.tw)
         # for the gather: transpose-pack + one pass per 16 vectors
         self.launches_per_pass = per_scatter + (per_scatter if self.matvec_method == 'scatter' else 1 + self.passes)
 
     def vecmat(self, spk_dev, stream):
         if self.sliced:
-            self._lib.check(self.lib.bsx_event_vecmat_sliced(C.byref(self.st_s), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
-                                                             self.T, self.y_vecmat.data_ptr(), 0, stream))
+            self._lib.check(self.lib.bsx_event_vecmat_sliced_fixed(C.byref(self.st_s), spk_dev.data_ptr(),
+                                                                   self._lib.SPK_BOOL8, self.T, self.y_vecmat.data_ptr(),
+                                                                   0, self.scale_s, stream))
             return
         self._lib.check(self.lib.bsx_event_vecmat(C.byref(self.st), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
                                                   self.T, self.y_vecmat.data_ptr(), 0, self.ws.data_ptr(),
@@ -291,8 +295,9 @@ class DevicePass:
 
     def matvec(self, spk_dev, stream):
         if self.matvec_method == 'scatter' and self.sliced:
-            self._lib.check(self.lib.bsx_event_vecmat_sliced(C.byref(self.st_t), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
-                                                             self.T, self.y_matvec.data_ptr(), 0, stream))
+            self._lib.check(self.lib.bsx_event_vecmat_sliced_fixed(C.byref(self.st_t), spk_dev.data_ptr(),
+                                                                   self._lib.SPK_BOOL8, self.T, self.y_matvec.data_ptr(),
+                                                                   0, self.scale_t, stream))
         elif self.matvec_method == 'scatter':
             self._lib.check(self.lib.bsx_event_vecmat(C.byref(self.st_t), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
                                                       self.T, self.y_matvec.data_ptr(), 0, self.ws.data_ptr(),
@@ -495,10 +500,11 @@ def run_ours(args):
     smem_variant = facts['scatter_variant'] == _lib.VECMAT_SHARED_SLICES
     what = 'spike@W over the rows' + (' and W@spike over the transposed copy' if facts['matvec_method'] == 'scatter' else '')
     if smem_variant:
-        r_s = roof('scatter_smem_kernel<hetero>', s_bytes, s_launch_s, ms_scatter / ms_total,
-                   what + '; one block per (spike vector, 32768-column slice of the output held in shared memory); '
-                   'every active row is read once per slice (the second read from L2); limited by load latency '
-                   'at one block per SM and by the shared-memory atomic rate')
+        r_s = roof('scatter_smem_kernel<hetero, fixed-point>', s_bytes, s_launch_s, ms_scatter / ms_total,
+                   what + '; one block per (spike vector, 32768-column slice of the output held in shared memory) '
+                   'over the copy whose rows are grouped by slice; weights summed as 2^-s fixed point with native '
+                   'shared-memory integer atomics (order-free: deterministic); algorithmic bytes can exceed the DRAM '
+                   'traffic because rows shared between vectors are served by L2')
     else:
         r_s = roof('scatter_queue_kernel<hetero> (+compact)', s_bytes, s_launch_s, ms_scatter / ms_total,
                    what + '; limited by the L2 rate of red.global.add.f32 (about 190 G adds/s in a stand-alone '
@@ -524,7 +530,7 @@ def run_ours(args):
             if smem_variant:
                 # L2 serves rows that several vectors share, so DRAM traffic does not grow in proportion
                 # to the vectors: the capture is of this launch size and is used for no other
-                r_s['traffic'] = float(tr['scatter_smem_kernel_296_vectors']) if T == 296 else None
+                r_s['traffic'] = float(tr.get('scatter_smem_kernel_fixed_296_vectors', tr['scatter_smem_kernel_296_vectors'])) if T == 296 else None
             else:
                 r_s['traffic'] = float(tr['scatter_queue_kernel_per_16_vectors']) * T / 16  # grows with the events
         except Exception:
@@ -549,7 +555,7 @@ def run_ours(args):
         'roofline_other_kernel': roofline_2,
         'cpu_baseline': cpu,
         'events_per_step': events_all,
-        'variants': {'spike@W': 'scatter', 'scatter_kernel': 'shared-memory slices' if smem_variant else 'global atomics', 'W@spike': facts['matvec_method'] + (' over the transposed copy' if facts['matvec_method'] == 'scatter' else ''),
+        'variants': {'spike@W': 'scatter', 'scatter_kernel': 'shared-memory slices, fixed-point sums' if smem_variant else 'global atomics', 'W@spike': facts['matvec_method'] + (' over the transposed copy' if facts['matvec_method'] == 'scatter' else ''),
                      'chosen_for_rate': RATE},
         'cases': cases,
         'single_vector_us': single,

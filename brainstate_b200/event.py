@@ -269,9 +269,12 @@ class _SparseConn:
         s._keep = (wt, s_indptr, s_indices)
         return s
 
-    def _fixed_scale(self, layout: str, st: BsxConn, weights: torch.Tensor) -> int:
+    def _fixed_scale(self, layout: str, st: BsxConn, weights: torch.Tensor, if_settled: bool = False):
         """Scale (log2) of the fixed-point scatter over a derived layout: the largest that cannot
-        overflow, from the largest column sum of ``|w|``.  Kept until the weight tensor changes."""
+        overflow, from the largest column sum of ``|w|`` (one pass over the weights and a stream
+        synchronisation).  Kept until the weight tensor changes.  ``if_settled``: return ``None``
+        instead of recomputing once the weights have changed twice — a training loop, where a
+        pass per step would cost more than the float atomics it avoids."""
         if not self.hetero:
             return 0
         wsrc = weights.contiguous()
@@ -279,11 +282,14 @@ class _SparseConn:
         cached = self._derived.get('scale_' + layout)
         if cached is not None and cached[0] == key:
             return cached[1]
+        misses = 0 if cached is None else cached[2] + 1
+        if if_settled and misses >= 2:
+            return None
         nbytes = lib().bsx_fixed_scale_workspace_bytes(st.n_post)
         ws = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=self.indices.device)
         s = C.c_int32(0)
         check(lib().bsx_fixed_scale_log2(C.byref(st), ptr(ws), nbytes, C.byref(s), _lib.current_stream()))
-        self._derived['scale_' + layout] = (key, int(s.value))
+        self._derived['scale_' + layout] = (key, int(s.value), misses)
         return int(s.value)
 
     @staticmethod
@@ -379,13 +385,21 @@ def _raw_vecmat(conn: _SparseConn, x: torch.Tensor, weights: torch.Tensor, event
         else:
             check(lib().bsx_event_matvec(C.byref(st), ptr(xb), fmt, batch, ptr(out), ptr(ws), ws_bytes, stream))
         return out.reshape(lead + (n_post,))
-    if method not in ('scatter', 'gather'):
-        raise ValueError(f"method must be 'scatter', 'gather' or 'fixed', got {method!r}")
+    if method not in ('scatter', 'gather', 'float'):
+        raise ValueError(f"method must be 'scatter', 'gather', 'fixed' or 'float', got {method!r}")
     st = conn._struct(weights)
     if event and lib().bsx_event_vecmat_variant(C.byref(st), spike_format_of(xb), batch) == _lib.VECMAT_SHARED_SLICES:
-        # a batch that fills the GPU: one launch over the copy whose rows are grouped by output slice
-        check(lib().bsx_event_vecmat_sliced(C.byref(conn._sliced_struct(weights)), ptr(xb), spike_format_of(xb),
-                                            batch, ptr(out), int(accumulate), stream))
+        # a batch that fills the GPU: one launch over the copy whose rows are grouped by output slice.
+        # Heterogeneous weights are summed in fixed point (order-free and faster than float atomics in
+        # shared memory) unless float sums are asked for.
+        st_s = conn._sliced_struct(weights)
+        scale = conn._fixed_scale('s', st_s, weights, if_settled=True) if conn.hetero and method != 'float' else None
+        if scale is not None:
+            check(lib().bsx_event_vecmat_sliced_fixed(C.byref(st_s), ptr(xb), spike_format_of(xb), batch, ptr(out),
+                                                      int(accumulate), scale, stream))
+        else:
+            check(lib().bsx_event_vecmat_sliced(C.byref(st_s), ptr(xb), spike_format_of(xb), batch, ptr(out),
+                                                int(accumulate), stream))
         return out.reshape(lead + (n_post,))
     ws_bytes = lib().bsx_event_vecmat_workspace_bytes(batch, n_pre)
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
@@ -420,13 +434,15 @@ def event_matvec(conn: _SparseConn, spk: torch.Tensor, bits: bool = False, metho
         active postsynaptic neurons scatter along the transposed copy (built once), cost
         proportional to the events — about twice as fast at 1 % firing, slower above ≈ 3 %;
         heterogeneous sums then depend on the order of the atomic adds (last-bit differences).
-        ``'fixed'`` is the event-driven form with the sums in fixed point (batches of 16 and
-        more; the gather otherwise): as fast as ``'scatter'`` and as reproducible as ``'gather'``,
-        every addend rounded to ``2^-scale`` (``bsx_fixed_scale_log2``).
+        Batches that fill the GPU sum heterogeneous weights in fixed point (``bsx_fixed_scale_log2``),
+        which is order-free and faster; ``'float'`` keeps float atomics there.
+        ``'fixed'`` asks for order-free sums at any batch size: the fixed-point scatter for batches
+        of 16 and more, the gather otherwise — as reproducible as ``'gather'``, every addend rounded
+        to ``2^-scale``.
     """
     _require_cuda(spk, 'spikes')
-    if method not in ('gather', 'scatter', 'fixed'):
-        raise ValueError(f"method must be 'gather', 'scatter' or 'fixed', got {method!r}")
+    if method not in ('gather', 'scatter', 'fixed', 'float'):
+        raise ValueError(f"method must be 'gather', 'scatter', 'fixed' or 'float', got {method!r}")
     n_pre, n_post = conn.shape
     if bits:
         words = (n_post + 31) // 32
@@ -445,11 +461,18 @@ def event_matvec(conn: _SparseConn, spk: torch.Tensor, bits: bool = False, metho
                                                       _lib.current_stream()))
             return out.reshape(lead + (n_pre,))
         method = 'gather'
-    if method == 'scatter':
+    if method in ('scatter', 'float'):
         st = conn._transposed_struct(conn.data)
         if lib().bsx_event_vecmat_variant(C.byref(st), fmt, batch) == _lib.VECMAT_SHARED_SLICES:
-            check(lib().bsx_event_vecmat_sliced(C.byref(conn._transposed_sliced_struct(conn.data)), ptr(xb), fmt,
-                                                batch, ptr(out), 0, _lib.current_stream()))
+            st_ts = conn._transposed_sliced_struct(conn.data)
+            scale = (conn._fixed_scale('ts', st_ts, conn.data, if_settled=True)
+                     if conn.hetero and method == 'scatter' else None)
+            if scale is not None:
+                check(lib().bsx_event_vecmat_sliced_fixed(C.byref(st_ts), ptr(xb), fmt, batch, ptr(out), 0, scale,
+                                                          _lib.current_stream()))
+            else:
+                check(lib().bsx_event_vecmat_sliced(C.byref(st_ts), ptr(xb), fmt, batch, ptr(out), 0,
+                                                    _lib.current_stream()))
             return out.reshape(lead + (n_pre,))
         ws_bytes = lib().bsx_event_vecmat_workspace_bytes(batch, n_post)
         ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=spk.device)

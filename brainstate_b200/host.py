@@ -61,10 +61,15 @@ class HostEventProducts:
         self.st = conn._struct()
         # chunks that fill the GPU run the scatter over the copies grouped by output slice
         self.sliced = l.bsx_event_vecmat_variant(C.byref(self.st), _lib.SPK_BOOL8, self.chunk) == _lib.VECMAT_SHARED_SLICES
+        self.scale_f = self.scale_t = None
         if self.sliced:
             self.st_f = conn._sliced_struct(conn.data) if forward else None
             if reverse and reverse_method == 'scatter':
                 self.st_t = conn._transposed_sliced_struct(conn.data)
+            if conn.hetero:     # heterogeneous weights: fixed-point sums (order-free, faster than float atomics)
+                self.scale_f = conn._fixed_scale('s', self.st_f, conn.data) if forward else None
+                self.scale_t = (conn._fixed_scale('ts', self.st_t, conn.data)
+                                if reverse and reverse_method == 'scatter' else None)
 
     def __call__(self, spk_host: torch.Tensor, y_fwd_host: Optional[torch.Tensor] = None,
                  y_rev_host: Optional[torch.Tensor] = None):
@@ -98,14 +103,20 @@ class HostEventProducts:
                 if c >= self.slots:
                     self.s_comp.wait_event(ev_out[c - self.slots])     # the slot's results were downloaded
                 stream = self.s_comp.cuda_stream
-                if self.forward and self.sliced:
+                if self.forward and self.sliced and self.scale_f is not None:
+                    check(l.bsx_event_vecmat_sliced_fixed(C.byref(self.st_f), self.spk[slot].data_ptr(), _lib.SPK_BOOL8,
+                                                          nb, self.y_fwd[slot].data_ptr(), 0, self.scale_f, stream))
+                elif self.forward and self.sliced:
                     check(l.bsx_event_vecmat_sliced(C.byref(self.st_f), self.spk[slot].data_ptr(), _lib.SPK_BOOL8, nb,
                                                     self.y_fwd[slot].data_ptr(), 0, stream))
                 elif self.forward:
                     check(l.bsx_event_vecmat(C.byref(self.st), self.spk[slot].data_ptr(), _lib.SPK_BOOL8, nb,
                                              self.y_fwd[slot].data_ptr(), 0, self.ws_f.data_ptr(), self.ws_f_bytes,
                                              stream))
-                if self.reverse and self.reverse_method == 'scatter' and self.sliced:
+                if self.reverse and self.reverse_method == 'scatter' and self.sliced and self.scale_t is not None:
+                    check(l.bsx_event_vecmat_sliced_fixed(C.byref(self.st_t), self.spk[slot].data_ptr(), _lib.SPK_BOOL8,
+                                                          nb, self.y_rev[slot].data_ptr(), 0, self.scale_t, stream))
+                elif self.reverse and self.reverse_method == 'scatter' and self.sliced:
                     check(l.bsx_event_vecmat_sliced(C.byref(self.st_t), self.spk[slot].data_ptr(), _lib.SPK_BOOL8, nb,
                                                     self.y_rev[slot].data_ptr(), 0, stream))
                 elif self.reverse and self.reverse_method == 'scatter':

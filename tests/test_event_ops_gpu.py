@@ -305,8 +305,10 @@ def test_batched_scatter_with_output_in_shared_memory(n_post, hetero, bsx, cuda)
         y = smem_scatter(ts, _lib.SPK_BOOL8, torch.full((B, n_post), 9.0, device=cuda))
         if hetero:
             close(y, ref)
-        else:
-            assert np.array_equal(y.cpu().numpy(), ref)
+        else:   # homogeneous weights: integer hit counts times the weight, rounded once — exactly
+            counts = eo.event_vecmat(spk, idx, np.float32(1.0), n_post, indptr)
+            assert np.array_equal(y.cpu().numpy(), (counts * np.float32(w)).astype(np.float32))
+            close(y, ref)
         xf = torch.from_numpy((spk * rs.uniform(0.5, 2, spk.shape)).astype(np.float32)).to(cuda)
         close(smem_scatter(xf, _lib.SPK_F32, torch.empty_like(y)), ref)            # float spikes are events
         bits = pack_spikes(ts)
