@@ -64,6 +64,30 @@ __device__ __forceinline__ void chunk_masks(const uint4& v, int64_t chunk, int64
   }
 }
 
+// The thread's kFuLoads chunks (chunk j * kFuThreads + tid), all loads issued before any is used:
+// one round trip to L2 instead of one per chunk.  Whole chunks are plain 128-bit loads; only the
+// last, partial chunk of the input goes through the byte-wise loader.
+__device__ __forceinline__ void load_my_chunks(const unsigned char* __restrict__ spikes, int64_t spike_bytes, int tid,
+                                               uint4 v[kFuLoads]) {
+  const int64_t whole = spike_bytes >> 4;
+  const uint4* __restrict__ p4 = reinterpret_cast<const uint4*>(spikes);
+#pragma unroll
+  for (int j = 0; j < kFuLoads; ++j) {
+    const int64_t c = (int64_t)j * kFuThreads + tid;
+    v[j] = c < whole ? __ldg(p4 + c) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (spike_bytes & 15) {
+    const int64_t c = whole;                                  // the partial chunk
+    const int j = (int)(c / kFuThreads);
+    if (c - (int64_t)j * kFuThreads == tid && j < kFuLoads) {
+      const uint4 t = load_chunk(spikes, c * 16, spike_bytes);
+#pragma unroll
+      for (int k = 0; k < kFuLoads; ++k)
+        if (k == j) v[k] = t;
+    }
+  }
+}
+
 template <bool HETERO, bool HAS_X, int FORMAT>
 __global__ void __launch_bounds__(kFuThreads, 1)
 scatter_fused_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
@@ -87,13 +111,15 @@ scatter_fused_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __
     entries = reinterpret_cast<const uint32_t*>(list + 1);
   } else {
     uint32_t cnt = 0;
+    uint4 v[kFuLoads];
+    load_my_chunks(spikes, spike_bytes, tid, v);
 #pragma unroll
     for (int j = 0; j < kFuLoads; ++j) {
       const int64_t c = (int64_t)j * kFuThreads + tid;
       if (c * 16 < spike_bytes) {
         uint32_t m[4];
         int64_t base[4];
-        chunk_masks<FORMAT>(load_chunk(spikes, c * 16, spike_bytes), c, n_pre, words, m, base);
+        chunk_masks<FORMAT>(v[j], c, n_pre, words, m, base);
         cnt += __popc(m[0]) + __popc(m[1]) + __popc(m[2]) + __popc(m[3]);
       }
     }
@@ -135,13 +161,15 @@ scatter_fused_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __
       r_count = total - lo < (uint32_t)kFuList ? total - lo : (uint32_t)kFuList;
       if (r > 0) __syncthreads();                             // the previous round's list has been consumed
       uint32_t pos = my_off;
+      uint4 v[kFuLoads];
+      load_my_chunks(spikes, spike_bytes, tid, v);              // L1/L2 hits: the count pass just read them
 #pragma unroll
       for (int j = 0; j < kFuLoads; ++j) {
         const int64_t c = (int64_t)j * kFuThreads + tid;
         if (c * 16 < spike_bytes) {
           uint32_t m[4];
           int64_t base[4];
-          chunk_masks<FORMAT>(load_chunk(spikes, c * 16, spike_bytes), c, n_pre, words, m, base);
+          chunk_masks<FORMAT>(v[j], c, n_pre, words, m, base);
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             uint32_t mm = m[u];

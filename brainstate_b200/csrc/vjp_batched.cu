@@ -52,6 +52,8 @@ __device__ __forceinline__ float act_at(const void* x, int64_t pos, bool event) 
 // Input cotangent for one chunk of up to 64 batch lanes starting at b0: a warp owns a row,
 // lane l holds batch lanes l and l + 32; every index fetches its 64 cotangent values as one
 // 256-byte stretch of the batch-minor copy (one 8-byte load per lane).
+constexpr int kDxFlight = 16;   // cotangent stretches a warp has in flight (8: 1.3x slower, 32: 1.1x slower)
+
 template <bool HETERO>
 __global__ void __launch_bounds__(256)
 vjp_dx_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
@@ -76,6 +78,26 @@ vjp_dx_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* _
         w_l = HETERO ? __ldg(w + p) : 1.f;
       }
       const int cnt = (int)((e - pb) < 32 ? (e - pb) : 32);
+      if (pair && cnt == 32) {
+        // the common case: 32 synapses, their 32 stretches requested in groups of kDxFlight loads
+        // before any is used (the kernel is bound by the latency of these L2 gathers)
+#pragma unroll
+        for (int t0 = 0; t0 < 32; t0 += kDxFlight) {
+          float2 c[kDxFlight];
+#pragma unroll
+          for (int u = 0; u < kDxFlight; ++u) {
+            const int32_t j = __shfl_sync(0xffffffffu, j_l, t0 + u);
+            c[u] = __ldg(reinterpret_cast<const float2*>(ctT + (int64_t)j * Bp + b0) + lane);
+          }
+#pragma unroll
+          for (int u = 0; u < kDxFlight; ++u) {
+            const float ww = __shfl_sync(0xffffffffu, w_l, t0 + u);
+            acc_e = fmaf(ww, c[u].x, acc_e);
+            acc_o = fmaf(ww, c[u].y, acc_o);
+          }
+        }
+        continue;
+      }
 #pragma unroll 4
       for (int t = 0; t < cnt; ++t) {
         const int32_t j = __shfl_sync(0xffffffffu, j_l, t);
@@ -125,30 +147,53 @@ vjp_dw_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const void* __
       continue;
     }
     if (n_act <= 16) {
-      for (int64_t pb = s; pb < e; pb += 32) {
-        const int64_t p = pb + lane;
-        const bool ok = p < e;
-        const int64_t j = ok ? (int64_t)__ldg(idx + p) : 0;
-        float acc = 0.f;
+      // four 32-synapse stretches per round: their indices first, then for every active batch lane
+      // four independent gathers per lane (the kernel is bound by the latency of these L2 gathers)
+      constexpr int U = 4;
+      for (int64_t pb = s; pb < e; pb += 32 * U) {
+        int64_t j[U];
+        bool ok[U];
+        float acc[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int64_t p = pb + 32 * u + lane;
+          ok[u] = p < e;
+          j[u] = ok[u] ? (int64_t)__ldg(idx + p) : 0;
+          acc[u] = 0.f;
+        }
         uint32_t m = act_lo;
         while (m) {                                        // uniform across the warp
           const int src = __ffs(m) - 1;
           m &= m - 1;
           const float a = __shfl_sync(0xffffffffu, a_lo, src);
-          if (ok) acc = fmaf(a, __ldg(ct + (b0 + src) * n_post + j), acc);
+          const float* __restrict__ crow = ct + (b0 + src) * n_post;
+          float c[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) c[u] = ok[u] ? __ldg(crow + j[u]) : 0.f;
+#pragma unroll
+          for (int u = 0; u < U; ++u) acc[u] = fmaf(a, c[u], acc[u]);
         }
         m = act_hi;
         while (m) {
           const int src = __ffs(m) - 1;
           m &= m - 1;
           const float a = __shfl_sync(0xffffffffu, a_hi, src);
-          if (ok) acc = fmaf(a, __ldg(ct + (b0 + 32 + src) * n_post + j), acc);
+          const float* __restrict__ crow = ct + (b0 + 32 + src) * n_post;
+          float c[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) c[u] = ok[u] ? __ldg(crow + j[u]) : 0.f;
+#pragma unroll
+          for (int u = 0; u < U; ++u) acc[u] = fmaf(a, c[u], acc[u]);
         }
-        if (ok) {
-          if (HETERO) {
-            if (first_chunk) dw[p] = acc; else dw[p] += acc;
-          } else {
-            homo_acc += acc;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int64_t p = pb + 32 * u + lane;
+          if (ok[u]) {
+            if (HETERO) {
+              if (first_chunk) dw[p] = acc[u]; else dw[p] += acc[u];
+            } else {
+              homo_acc += acc[u];
+            }
           }
         }
       }

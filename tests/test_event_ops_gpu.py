@@ -636,8 +636,9 @@ def test_scatter_over_rows_grouped_by_slice(n_post, hetero, bsx, cuda):
 
         y = sliced(ts, _lib.SPK_BOOL8, torch.full((B, n_post), 9.0, device=cuda))
         close(y, ref)
-        if not hetero:
-            assert np.array_equal(y.cpu().numpy(), ref)
+        if not hetero:      # integer hit counts times the weight, rounded once — exactly
+            counts = eo.event_vecmat(spk, idx, np.float32(1.0), n_post, indptr)
+            assert np.array_equal(y.cpu().numpy(), (counts * np.float32(w)).astype(np.float32))
         xf = torch.from_numpy((spk * rs.uniform(0.5, 2, spk.shape)).astype(np.float32)).to(cuda)
         close(sliced(xf, _lib.SPK_F32, torch.empty_like(y)), ref)
         close(sliced(pack_spikes(ts), _lib.SPK_BITS32, y.clone(), accumulate=1), 2 * ref)
