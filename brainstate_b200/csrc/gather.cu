@@ -52,7 +52,7 @@ __device__ __forceinline__ bool bit_at(const uint32_t* __restrict__ m, int32_t j
 // them.  A 655-entry row is 164 such loads, i.e. 6 per lane: with U = 6 a warp has
 // its whole row in flight at once.
 template <bool HETERO, bool SMEM, int U>
-__global__ void __launch_bounds__(256, (U > 2 ? 4 : 8))
+__global__ void __launch_bounds__(256, (U > 2 ? 4 : (U > 1 ? 6 : 8)))
 event_matvec_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
                     const uint32_t* __restrict__ bits, int64_t words, int64_t n_rows,
                     float* __restrict__ out, bool vec_ok, bool use_tma) {

@@ -52,7 +52,7 @@ __device__ __forceinline__ float act_at(const void* x, int64_t pos, bool event) 
 // Input cotangent for one chunk of up to 64 batch lanes starting at b0: a warp owns a row,
 // lane l holds batch lanes l and l + 32; every index fetches its 64 cotangent values as one
 // 256-byte stretch of the batch-minor copy (one 8-byte load per lane).
-constexpr int kDxFlight = 16;   // cotangent stretches a warp has in flight (8: 1.3x slower, 32: 1.1x slower)
+constexpr int kDxFlight = 8;    // 128-bit loads per lane in flight = 16 cotangent stretches per warp (4: 1.3x slower, 16: 1.2x slower)
 
 template <bool HETERO>
 __global__ void __launch_bounds__(256)
@@ -64,11 +64,13 @@ vjp_dx_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* _
   // lane l reads the pair (2l, 2l + 1) of the 64 lanes: one float2 per lane covers the stretch
   const int64_t be = b0 + 2 * lane, bo = be + 1;
   const bool pair = b0 + 64 <= Bp;                       // a full 64-lane stretch exists
+  const int half = lane >> 4, quad = lane & 15;
   const int64_t wstep = (int64_t)gridDim.x * (blockDim.x >> 5);
   for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < n_pre; row += wstep) {
     int64_t s, e;
     rm.range(row, s, e);
     float acc_e = 0.f, acc_o = 0.f;
+    float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);       // batch lanes 4 * quad .. + 3, this half-warp's synapses
     for (int64_t pb = s; pb < e; pb += 32) {
       const int64_t p = pb + lane;
       int32_t j_l = 0;
@@ -79,21 +81,25 @@ vjp_dx_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* _
       }
       const int cnt = (int)((e - pb) < 32 ? (e - pb) : 32);
       if (pair && cnt == 32) {
-        // the common case: 32 synapses, their 32 stretches requested in groups of kDxFlight loads
-        // before any is used (the kernel is bound by the latency of these L2 gathers)
+        // the common case: 32 synapses.  Each half-warp takes every other synapse, one 128-bit load
+        // per lane (16 lanes x 4 batch lanes = the 256-byte stretch), kDxFlight loads — 2 * kDxFlight
+        // stretches per warp — requested before any is used: the kernel is bound by the latency of
+        // these L2 gathers.
 #pragma unroll
-        for (int t0 = 0; t0 < 32; t0 += kDxFlight) {
-          float2 c[kDxFlight];
+        for (int t0 = 0; t0 < 16; t0 += kDxFlight) {
+          float4 c[kDxFlight];
 #pragma unroll
           for (int u = 0; u < kDxFlight; ++u) {
-            const int32_t j = __shfl_sync(0xffffffffu, j_l, t0 + u);
-            c[u] = __ldg(reinterpret_cast<const float2*>(ctT + (int64_t)j * Bp + b0) + lane);
+            const int32_t j = __shfl_sync(0xffffffffu, j_l, 2 * (t0 + u) + half);
+            c[u] = __ldg(reinterpret_cast<const float4*>(ctT + (int64_t)j * Bp + b0) + quad);
           }
 #pragma unroll
           for (int u = 0; u < kDxFlight; ++u) {
-            const float ww = __shfl_sync(0xffffffffu, w_l, t0 + u);
-            acc_e = fmaf(ww, c[u].x, acc_e);
-            acc_o = fmaf(ww, c[u].y, acc_o);
+            const float ww = __shfl_sync(0xffffffffu, w_l, 2 * (t0 + u) + half);
+            acc4.x = fmaf(ww, c[u].x, acc4.x);
+            acc4.y = fmaf(ww, c[u].y, acc4.y);
+            acc4.z = fmaf(ww, c[u].z, acc4.z);
+            acc4.w = fmaf(ww, c[u].w, acc4.w);
           }
         }
         continue;
@@ -109,6 +115,19 @@ vjp_dx_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* _
         acc_e = fmaf(ww, c.x, acc_e);
         acc_o = fmaf(ww, c.y, acc_o);
       }
+    }
+    // fold the 128-bit path into the pair layout: the two half-warps are summed, then lane l takes
+    // batch lanes 2l and 2l + 1 from lane l / 2 (fixed order: deterministic)
+    acc4.x += __shfl_xor_sync(0xffffffffu, acc4.x, 16);
+    acc4.y += __shfl_xor_sync(0xffffffffu, acc4.y, 16);
+    acc4.z += __shfl_xor_sync(0xffffffffu, acc4.z, 16);
+    acc4.w += __shfl_xor_sync(0xffffffffu, acc4.w, 16);
+    {
+      const int src = lane >> 1;
+      const float lo_a = __shfl_sync(0xffffffffu, acc4.x, src), lo_b = __shfl_sync(0xffffffffu, acc4.y, src);
+      const float hi_a = __shfl_sync(0xffffffffu, acc4.z, src), hi_b = __shfl_sync(0xffffffffu, acc4.w, src);
+      acc_e += (lane & 1) ? hi_a : lo_a;
+      acc_o += (lane & 1) ? hi_b : lo_b;
     }
     if (!HETERO) { acc_e *= w0; acc_o *= w0; }
     if (be < B) dx[be * n_pre + row] = acc_e;
