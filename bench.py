@@ -568,9 +568,8 @@ def run_ours(args):
         if leg:
             records.update(leg.pop('_records'))
     if args.write_fixtures and world == 1 and records:
-        os.makedirs(os.path.join(ROOT, 'gpurun_out'), exist_ok=True)
-        np.savez_compressed(os.path.join(ROOT, 'gpurun_out', 'network_counts.npz'),
-                            **{k: v.astype(np.int32) for k, v in records.items()})
+        os.makedirs(os.path.dirname(os.path.abspath(args.write_fixtures)), exist_ok=True)
+        np.savez_compressed(args.write_fixtures, **{k: v.astype(np.int32) for k, v in records.items()})
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -585,7 +584,7 @@ def run_network(torch, dist, dev, world, rank, name, steps, warm):
     the ranks: all steps in one cooperative launch per GPU with the spike exchange inside the
     kernel.  Timed with CUDA events, maximum over ranks.  The per-step spike counts are
     compared with the committed record of the one-GPU run (``tests/golden/network_counts.npz``,
-    written by ``--write-fixtures``).  The large recipe has heterogeneous weights: it is timed
+    written by ``--write-fixtures FILE``).  The large recipe has heterogeneous weights: it is timed
     with float32 sums and run once more with fixed-point sums, whose counts do not depend on
     the order of the adds and so must equal the record at any number of GPUs."""
     from brainstate_b200.sim import from_preset, preset
@@ -835,8 +834,9 @@ def main():
                     'calls and the training step')
     ap.add_argument('--no-network', action='store_true', help='skip the sharded network runs reported beside the headline')
     ap.add_argument('--no-large', action='store_true', help='skip the 8e6-neuron network')
-    ap.add_argument('--write-fixtures', action='store_true',
-                    help='one GPU: write the per-step spike counts of the network runs to gpurun_out/network_counts.npz')
+    ap.add_argument('--write-fixtures', default=None, metavar='FILE.npz',
+                    help='one GPU: write the per-step spike counts of the network runs to this file (the record '
+                         'committed as tests/golden/network_counts.npz was made this way)')
     ap.add_argument('--profile', action='store_true',
                     help='run only the device-resident loop (for ncu); prints no bench line')
     ap.add_argument('--only', default=None, choices=['training', 'single', 'homogeneous'],

@@ -419,6 +419,19 @@ class EINetOracle:
         self.history = self.history[-(max(self.delay_e, self.delay_i) + 1):]
         dg_e = event_vecmat_rows(s_e[:self.n_exc], self.idx_e, self.w_e, self.n, self.indptr_e, self.fixed_point)
         dg_i = event_vecmat_rows(s_i[self.n_exc:], self.idx_i, self.w_i, self.n, self.indptr_i, self.fixed_point)
+        return self.advance(dg_e, dg_i)
+
+    def projections(self, s_global):
+        """Synaptic input one spike vector of the whole network sends to this instance's neurons:
+        ``(dg_e, dg_i)``, no delay applied (the caller decides at which step it acts)."""
+        s = np.asarray(s_global, bool)
+        return (event_vecmat_rows(s[:self.n_exc], self.idx_e, self.w_e, self.n, self.indptr_e, self.fixed_point),
+                event_vecmat_rows(s[self.n_exc:], self.idx_i, self.w_i, self.n, self.indptr_i, self.fixed_point))
+
+    def advance(self, dg_e, dg_i):
+        """The neuron update of one step for given synaptic increments (steps 3-6 of the class
+        docstring, plus the background drive).  Returns ``(spikes, dg_e, dg_i)``."""
+        dg_e, dg_i = np.asarray(dg_e, F32), np.asarray(dg_i, F32)
         if self.ext_threshold:
             gid = np.arange(self.first, self.first + self.n, dtype=np.uint32)
             fire = self.drive_hash(self.ext_seed, gid, self.t) < np.uint32(min(self.ext_threshold, 0xffffffff))

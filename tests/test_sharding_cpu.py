@@ -96,3 +96,90 @@ def test_two_gloo_ranks_reproduce_the_unsharded_raster(tmp_path, bsx):
                          eo.fixed_num_indices(101, n_inh, n, K), np.float32(-9.0), V0=V0).run(steps)
     assert ref.sum() > 20
     assert np.array_equal(got, ref)
+
+
+def _rank_lists(rank, world, port, steps, delays, slack, cuts, out_dir):
+    """One rank of the id-list exchange, restated on the CPU: every step a rank updates its
+    neurons from row ``s % ring`` of its increment ring, sends the ids of its spiking neurons
+    tagged with the exchange sequence number, adds its own spikes to the rows of the steps at
+    which they act and does the same for the lists of step ``s - slack`` of the other ranks;
+    the last ``slack`` lists are drained at the end of every launch (``cuts``)."""
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        from brainstate_b200.sim import shard_bounds, sharded_block
+        n_exc, n_inh, K = 320, 96, 12
+        n = n_exc + n_inh
+        de, di = delays
+        ring = max(de, di) + 2
+        first, last = shard_bounds(n, world, rank)
+        n_local = last - first
+        ie, pe = sharded_block(100, n_exc, n, K, first, last)
+        ii, pi = sharded_block(101, n_inh, n, K, first, last)
+        V0 = np.random.RandomState(102).uniform(-60, -50, n).astype(np.float32)
+        net = eo.EINetOracle(n_exc, n_inh, ie, np.float32(1.62), ii, np.float32(-9.0), V0=V0[first:last],
+                             indptr_e=pe, indptr_i=pi, n_local=n_local, first=first)
+        incr_e = np.zeros((ring, n_local), np.float32)
+        incr_i = np.zeros((ring, n_local), np.float32)
+        inbox = {}                                     # (sequence number, source rank) -> ids
+
+        def scatter(ids, fired):
+            s = np.zeros(n, bool)
+            s[ids] = True
+            dg_e, dg_i = net.projections(s)
+            incr_e[(fired + 1 + de) % ring] += dg_e
+            incr_i[(fired + 1 + di) % ring] += dg_i
+
+        def consume(seq, fired):
+            for src in range(world):
+                if src != rank:
+                    scatter(inbox.pop((seq, src)), fired)
+
+        raster = np.zeros((steps, n), bool)
+        step = seq = 0
+        for launch in cuts:
+            for t in range(launch):
+                row = step % ring
+                spk, _, _ = net.advance(incr_e[row].copy(), incr_i[row].copy())
+                incr_e[row] = 0
+                incr_i[row] = 0
+                mine = first + np.nonzero(spk)[0]
+                lists = [None] * world
+                dist.all_gather_object(lists, (seq, mine))          # the push: tag + ids to every peer
+                for src, (tag, ids) in enumerate(lists):
+                    assert tag == seq
+                    inbox[(seq, src)] = ids
+                    raster[step, ids] = True
+                inbox.pop((seq, rank))
+                scatter(mine, step)                                  # own spikes, at once
+                if t >= slack:
+                    consume(seq - slack, step - slack)               # received spikes, `slack` steps late
+                step += 1
+                seq += 1
+            for back in range(min(slack, launch), 0, -1):            # drain before the launch ends
+                consume(seq - back, step - back)
+            assert not inbox
+        if rank == 0:
+            np.save(os.path.join(out_dir, 'raster_lists.npy'), raster)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('delays,slack', [((0, 0), 0), ((1, 2), 1), ((3, 2), 2), ((3, 2), 0)])
+def test_id_list_exchange_with_increment_ring_and_slack(delays, slack, tmp_path, bsx):
+    """The protocol of the sharded step kernel (spike-id lists instead of packed words, delays by
+    the row a spike is added to, lists consumed `slack` steps late, drained at launch ends) gives
+    the unsharded oracle's raster on two gloo ranks."""
+    cuts = (1, 40, 2, 77)
+    steps = sum(cuts)
+    mp.spawn(_rank_lists, args=(2, _free_port(), steps, delays, slack, cuts, str(tmp_path)), nprocs=2, join=True)
+    got = np.load(tmp_path / 'raster_lists.npy')
+    n_exc, n_inh, K = 320, 96, 12
+    n = n_exc + n_inh
+    V0 = np.random.RandomState(102).uniform(-60, -50, n).astype(np.float32)
+    ref = eo.EINetOracle(n_exc, n_inh, eo.fixed_num_indices(100, n_exc, n, K), np.float32(1.62),
+                         eo.fixed_num_indices(101, n_inh, n, K), np.float32(-9.0), V0=V0,
+                         delay_e=delays[0], delay_i=delays[1]).run(steps)
+    assert ref.sum() > 20
+    assert np.array_equal(got, ref)
