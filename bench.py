@@ -632,6 +632,22 @@ def run_network(torch, dist, dev, world, rank, name, steps, warm):
                      else 'net_run_sharded_kernel (state in global memory)',
            'exchange': 'spike-id lists pushed by peer stores inside the step kernel' if world > 1 else 'none (one GPU)',
            'accumulation': 'float32 atomics'}
+    if world > 1 and not hetero:
+        # the plain-library form of the same step, for comparison: split-phase launches and one NCCL
+        # all-gather of the packed spike words per step (launch-bound; 200 steps)
+        lib_net = from_preset(name, dev, group, exchange='nccl')
+        lib_net.run(20, record=False)
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        lib_net.run(200, record=False)
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out['nccl_all_gather_us_per_step'] = float(t.item()) * 1e3 / 200
+        lib_net.close()
     fixture = dict(np.load(FIXTURE)) if os.path.exists(FIXTURE) else {}
     written = {}
     if hetero:

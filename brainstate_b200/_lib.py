@@ -130,6 +130,8 @@ SIGNATURES = {
     'bsx_vecmat_vjp_batched_workspace_bytes': (_sz, [_i64, _i64]),
     'bsx_vecmat_vjp_batched': (_i32, [_connp, _vp, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     'bsx_dense_event_vecmat': (_i32, [_vp, _i32, _vp, _i64, _i64, _i64, _vp, _vp]),
+    'bsx_dense_event_dw': (_i32, [_vp, _i32, _vp, _i64, _i64, _i64, _vp, _vp]),
+    'bsx_dense_event_scalar': (_i32, [_vp, _i32, _vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp]),
     'bsx_net_run': (_i32, [_netp, _lifp, _i32, _i64, _vp, _vp, _i32, _vp]),
     'bsx_net_update': (_i32, [_netp, _lifp, _i64, _vp, _vp]),
     'bsx_net_list_from_bits': (_i32, [_netp, _i64, _vp]),

@@ -13,11 +13,13 @@
 // range of the rank's spike words.  A step of one block:
 //
 //   1. update its neurons (synapse decay + pending increment, membrane, threshold),
-//      collecting the ones that spiked in a shared-memory list;
-//   2. link warps (one per peer) push that list into the peer's inbox — 64-bit words
+//      collecting the ones that spiked in a shared-memory list; a warp that finds spikes
+//      stores their ids into every peer's inbox right away — 64-bit words
 //      (tag << 32 | payload), tag = exchange sequence number + 1, so that every word
-//      validates itself and neither a fence nor a separate flag is needed — and then
-//      poll their own inbox for the list the same block index of that peer pushed;
+//      validates itself and neither a fence nor a separate flag is needed;
+//   2. link warps (one per peer) complete the list with its header (the count) and then
+//      poll their own inbox for the list the same block index of that peer pushed,
+//      fetching the header and the first 31 ids in one round trip;
 //   3. meanwhile the other warps scatter the block's own spikes along the rank's rows
 //      into the increments of the step at which they act;
 //   4. all warps scatter the received spikes;
@@ -312,7 +314,6 @@ net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t
     }
   }
   __syncthreads();
-  __syncthreads();
   unsigned barriers = 0;
   int status = 0;
   for (int t = 0; t < steps; ++t) {
@@ -331,15 +332,17 @@ net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t
     const bool early = links > 0 && (L.flags & 1);
     const unsigned long long push_tag = (unsigned long long)(uint32_t)(seq + 1) << 32;
     // ---- 1. neuron update ----
-    for (int64_t wl0 = wid; wl0 < my_words; wl0 += kShWarps * WPW) {
+    // (word and neuron numbers fit 32 bits: n_global < 2^31)
+    const int my_w = (int)my_words, n0i = (int)n0, n_loc = (int)a.n_local;
+    for (int wl0 = wid; wl0 < my_w; wl0 += kShWarps * WPW) {
       T de[WPW], di[WPW];
       float v[WPW], ge[WPW], gi[WPW];
       int32_t rr[WPW];
 #pragma unroll
       for (int k = 0; k < WPW; ++k) {
-        const int64_t wl = wl0 + (int64_t)k * kShWarps;
-        const int64_t i = n0 + wl * 32 + lane;
-        const bool valid = wl < my_words && i < a.n_local;
+        const int wl = wl0 + k * kShWarps;
+        const int i = n0i + wl * 32 + lane;
+        const bool valid = wl < my_w && i < n_loc;
         de[k] = valid ? cur_e[i] : T(0);
         di[k] = valid ? cur_i[i] : T(0);
         if (!RESIDENT) {
@@ -351,16 +354,16 @@ net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t
       }
 #pragma unroll
       for (int k = 0; k < WPW; ++k) {
-        const int64_t wl = wl0 + (int64_t)k * kShWarps;
-        if (wl >= my_words) break;                       // uniform across the warp
-        const int64_t li = wl * 32 + lane;
-        const int64_t i = n0 + li;
+        const int wl = wl0 + k * kShWarps;
+        if (wl >= my_w) break;                           // uniform across the warp
+        const int li = wl * 32 + lane;
+        const int i = n0i + li;
         bool spk = false;
-        if (i < a.n_local) {
+        if (i < n_loc) {
           const int32_t r = RESIDENT ? (int32_t)sref[li] : rr[k];
           const NeuronOut o = neuron_math(a.p, I::value(de[k]), I::value(di[k]), RESIDENT ? sge[li] : ge[k],
                                           RESIDENT ? sgi[li] : gi[k], RESIDENT ? sV[li] : v[k], r,
-                                          (uint32_t)(a.first + i), step);
+                                          (uint32_t)a.first + (uint32_t)i, step);
           if (I::nonzero(de[k])) cur_e[i] = T(0);
           if (I::nonzero(di[k])) cur_i[i] = T(0);
           if (RESIDENT) {
@@ -391,7 +394,7 @@ net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t
             const int pos = base + __popc(m & ((1u << lane) - 1u));
             smine[pos] = (uint16_t)li;
             if (early)       // the id is on its way to every peer before the rest of the block has finished
-              for (int p = 0; p < links; ++p) st_relaxed_sys(s_out[p] + 1 + pos, push_tag | (uint32_t)(a.first + i));
+              for (int p = 0; p < links; ++p) st_relaxed_sys(s_out[p] + 1 + pos, push_tag | ((uint32_t)a.first + (uint32_t)i));
           }
         }
       }

@@ -3,9 +3,10 @@
 
 ``EventLinear.update(spk)``: with a scalar weight every output receives
 ``count(spk != 0) * w`` (``float_as_event``) or ``sum(spk) * w``; with a matrix
-weight the output is ``[spk != 0] @ W`` (event kernel in ``libbsx.so``) or the
-plain ``spk @ W``.  The plain dense product and the dense cotangents are ordinary
-GEMMs and go to ``torch.matmul``; the event-driven forward is the library's.
+weight the output is ``[spk != 0] @ W`` or the plain ``spk @ W``.  The event-driven
+forward, its weight cotangent ``[spk != 0]^T @ ct`` and the scalar-weight form are
+kernels of ``libbsx.so``; the plain dense product and the input cotangent ``ct @ W^T``
+are ordinary dense GEMMs and go to ``torch.matmul``.
 """
 from __future__ import annotations
 
@@ -54,8 +55,15 @@ class _DenseEvent(torch.autograd.Function):
         if ctx.needs_input_grad[0] and spk.dtype.is_floating_point:
             d_spk = ct @ weight.t()
         if ctx.needs_input_grad[1]:
-            a = (spk != 0).to(torch.float32).reshape(-1, spk.shape[-1])
-            d_w = a.t() @ ct.reshape(-1, ct.shape[-1])
+            n_pre, n_post = weight.shape
+            sb, _ = _flatten_batch(spk, n_pre)
+            ctb = ct.reshape(-1, n_post).to(torch.float32).contiguous()
+            if n_pre <= 65535 and sb.dtype in (torch.bool, torch.uint8, torch.float32):
+                d_w = torch.empty((n_pre, n_post), dtype=torch.float32, device=ct.device)
+                _lib.check(_lib.lib().bsx_dense_event_dw(_lib.ptr(sb), spike_format_of(sb), _lib.ptr(ctb), sb.shape[0],
+                                                         n_pre, n_post, _lib.ptr(d_w), _lib.current_stream()))
+            else:
+                d_w = (sb != 0).to(torch.float32).t() @ ctb
         return d_spk, d_w
 
     @staticmethod
@@ -68,6 +76,45 @@ class _DenseEvent(torch.autograd.Function):
             term = _DenseEvent.apply(spk, w_dot)
             out = term if out is None else out + term
         return out
+
+
+class _DenseScalar(torch.autograd.Function):
+    """``y[..., :] = r * w`` with ``r`` the event count or the value sum of the last axis of ``spk``
+    (``_event_linear.py:77-97``).  The cotangent of a float ``spk`` is ``w * sum_j ct[..., j]`` for
+    every input (the reference routes the gradient through the value sum, ``:84-91``)."""
+
+    @staticmethod
+    def forward(spk, weight, float_as_event, n_post):
+        _require_cuda(spk, 'spikes')
+        n_pre = spk.shape[-1]
+        sb, lead = _flatten_batch(spk, n_pre)
+        if sb.dtype not in (torch.bool, torch.uint8, torch.float32):
+            sb = sb.to(torch.float32)
+        out = torch.empty((sb.shape[0], n_post), dtype=torch.float32, device=spk.device)
+        reduced = torch.empty(sb.shape[0], dtype=torch.float32, device=spk.device)
+        w = weight.reshape(1).to(torch.float32).contiguous()
+        _lib.check(_lib.lib().bsx_dense_event_scalar(_lib.ptr(sb), spike_format_of(sb), _lib.ptr(w), int(float_as_event),
+                                                     sb.shape[0], n_pre, n_post, _lib.ptr(out), _lib.ptr(reduced),
+                                                     _lib.current_stream()))
+        return out.reshape(lead + (n_post,)), reduced.reshape(lead)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        spk, weight, _, _ = inputs
+        ctx.save_for_backward(weight, output[1])
+        ctx.spk_shape, ctx.spk_float = spk.shape, spk.dtype.is_floating_point
+        ctx.mark_non_differentiable(output[1])
+
+    @staticmethod
+    def backward(ctx, ct, _):
+        weight, reduced = ctx.saved_tensors
+        row = ct.sum(dim=-1)                                     # (batch dims)
+        d_spk = d_w = None
+        if ctx.needs_input_grad[0] and ctx.spk_float:
+            d_spk = (row * weight.reshape(())).unsqueeze(-1).expand(ctx.spk_shape)
+        if ctx.needs_input_grad[1]:
+            d_w = (row * reduced).sum().reshape(weight.shape)
+        return d_spk, d_w, None, None
 
 
 def dense_event_matmul(spk: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
@@ -103,18 +150,8 @@ class EventLinear(Module):
     def update(self, spk: torch.Tensor) -> torch.Tensor:
         weight = self.weight.value
         if weight.numel() == 1:
-            # homogeneous weight: reduce, then broadcast (_event_linear.py:77-97)
-            if self.float_as_event:
-                n_events = (spk != 0).sum(dim=-1).to(torch.float32)
-                if spk.dtype.is_floating_point:
-                    value_sum = spk.sum(dim=-1)
-                    reduced = n_events + (value_sum - value_sum.detach())
-                else:
-                    reduced = n_events
-            else:
-                reduced = spk.to(torch.float32).sum(dim=-1)
-            ones = torch.ones(self.out_size, dtype=torch.float32, device=weight.device)
-            return ones * (reduced * weight.reshape(()))[..., None]
+            # homogeneous weight: reduce, then broadcast (_event_linear.py:77-97), one kernel
+            return _DenseScalar.apply(spk, weight, self.float_as_event, self.out_size[-1])[0]
         if self.float_as_event:
             return dense_event_matmul(spk, weight)
         return spk.to(torch.float32) @ weight

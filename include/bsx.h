@@ -292,6 +292,23 @@ int bsx_float_matvec(const bsx_conn_t* conn, const float* v, int64_t batch, floa
 int bsx_dense_event_vecmat(const void* spikes, int spike_format, const float* weight, int64_t batch,
                            int64_t n_pre, int64_t n_post, float* out, bsx_stream_t stream);
 
+/*
+ * Weight cotangent of the dense event product:      brainstate/nn/_event_linear.py:99-100,
+ *   dW[i, :] = sum over b with spk[b,i] != 0 of ct[b, :]        tests _event_linear_test.py:51-124
+ * (ascending b, no atomics).  dW (n_pre, n_post) is overwritten; n_pre <= 65535 per call.
+ * The input cotangent of that product, ct @ W^T, is a plain dense GEMM and is left to a GEMM library.
+ */
+int bsx_dense_event_dw(const void* spikes, int spike_format, const float* ct, int64_t batch, int64_t n_pre,
+                       int64_t n_post, float* dw, bsx_stream_t stream);
+/*
+ * Scalar-weight form of the dense event layer       brainstate/nn/_event_linear.py:77-97
+ *   y[b, :] = r[b] * w,  r[b] = count(spk[b, :] != 0) (float_as_event) or sum(spk[b, :])
+ * weight points at ONE float; reduced (may be NULL) receives r (batch).
+ */
+int bsx_dense_event_scalar(const void* spikes, int spike_format, const float* weight, int float_as_event,
+                           int64_t batch, int64_t n_pre, int64_t n_post, float* out, float* reduced,
+                           bsx_stream_t stream);
+
 /* ---- reverse-mode products --------------------------------------------- */
 /*
  * Cotangents of y = x @ conn for output cotangent ct (batch, n_post), one pass

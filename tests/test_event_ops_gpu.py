@@ -435,6 +435,45 @@ def test_event_linear(cuda):
     close(W.grad, ((spk != 0).float()[:, None] * torch.ones(6, device=cuda)).cpu().numpy())
 
 
+def test_event_linear_kernels_at_a_realistic_size(bsx, cuda):
+    """The dense event layer at 8192 x 4096 with a batch of 24: forward, the weight cotangent
+    ``[spk != 0]^T @ ct`` (own kernel, ascending batch order, rows that never fired are zeros)
+    and the scalar-weight form with its gradients, against NumPy in float64."""
+    from brainstate_b200.nn import EventLinear
+    rs = np.random.RandomState(11)
+    n_in, n_out, B = 8192, 4096, 24
+    W = rs.standard_normal((n_in, n_out)).astype(np.float32)
+    s = rs.random_sample((B, n_in)) < 0.02
+    s[:, 5] = False                                             # a neuron that never fires
+    sf = (s * rs.uniform(0.5, 2, s.shape)).astype(np.float32)
+    ct = rs.standard_normal((B, n_out)).astype(np.float32)
+    Wt = torch.from_numpy(W).to(cuda).requires_grad_(True)
+    x = torch.from_numpy(sf).to(cuda).requires_grad_(True)
+    layer = EventLinear(n_in, n_out, Wt)
+    y = layer(x)
+    ref = s.astype(np.float64) @ W.astype(np.float64)
+    np.testing.assert_allclose(y.detach().cpu().numpy(), ref, rtol=1e-5, atol=2e-4)
+    (y * torch.from_numpy(ct).to(cuda)).sum().backward()
+    dW = s.astype(np.float64).T @ ct.astype(np.float64)
+    np.testing.assert_allclose(Wt.grad.cpu().numpy(), dW, rtol=1e-5, atol=1e-5)
+    assert bool((Wt.grad[5] == 0).all())
+    np.testing.assert_allclose(x.grad.cpu().numpy(), ct.astype(np.float64) @ W.astype(np.float64).T, rtol=1e-4, atol=2e-3)
+    # boolean spikes take the same kernels
+    yb = layer(torch.from_numpy(s).to(cuda))
+    assert torch.equal(yb, y.detach())
+    # scalar weight: count or value sum, broadcast; gradients through the value sum
+    for fae in (True, False):
+        w0 = torch.tensor(1.5, device=cuda, requires_grad=True)
+        xs = torch.from_numpy(sf).to(cuda).requires_grad_(True)
+        ys = EventLinear(n_in, n_out, w0, float_as_event=fae)(xs)
+        r = s.sum(axis=1).astype(np.float64) if fae else sf.astype(np.float64).sum(axis=1)
+        np.testing.assert_allclose(ys.detach().cpu().numpy(), np.repeat((r * 1.5)[:, None], n_out, 1), rtol=1e-5)
+        (ys * torch.from_numpy(ct).to(cuda)).sum().backward()
+        row = ct.astype(np.float64).sum(axis=1)
+        np.testing.assert_allclose(float(w0.grad), float((row * r).sum()), rtol=1e-4)
+        np.testing.assert_allclose(xs.grad.cpu().numpy(), np.repeat((1.5 * row)[:, None], n_in, 1), rtol=1e-4, atol=1e-5)
+
+
 @pytest.fixture(scope='module')
 def microbench(cuda, c_oracle):
     """The standalone microbenchmark matrix at full size: 65 536^2, p = 0.01."""
