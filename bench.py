@@ -277,17 +277,21 @@ class DevicePass:
         if self.sliced:       # copies whose rows are grouped by output slice, built once like the matrix
             self.st_s = self.conn._sliced_struct(self.tw)
             self.scale_s = self.conn._fixed_scale('s', self.st_s, self.tw)       # fixed-point sums: order-free, faster
+            # compressed form: 16-bit column offsets inside the slice, weights stored in fixed point
+            self.loc_s, self.q_s = self.conn._packed('s', self.st_s, self.tw, self.scale_s)
             if self.matvec_method == 'scatter':
                 self.st_t = self.conn._transposed_sliced_struct(self.tw)
                 self.scale_t = self.conn._fixed_scale('ts', self.st_t, self.tw)
+                self.loc_t, self.q_t = self.conn._packed('ts', self.st_t, self.tw, self.scale_t)
         # for the gather: transpose-pack + one pass per 16 vectors
         self.launches_per_pass = per_scatter + (per_scatter if self.matvec_method == 'scatter' else 1 + self.passes)
 
     def vecmat(self, spk_dev, stream):
         if self.sliced:
-            self._lib.check(self.lib.bsx_event_vecmat_sliced_fixed(C.byref(self.st_s), spk_dev.data_ptr(),
-                                                                   self._lib.SPK_BOOL8, self.T, self.y_vecmat.data_ptr(),
-                                                                   0, self.scale_s, stream))
+            self._lib.check(self.lib.bsx_event_vecmat_sliced16(C.byref(self.st_s), self.loc_s.data_ptr(),
+                                                               self.q_s.data_ptr(), spk_dev.data_ptr(),
+                                                               self._lib.SPK_BOOL8, self.T, self.y_vecmat.data_ptr(),
+                                                               0, self.scale_s, stream))
             return
         self._lib.check(self.lib.bsx_event_vecmat(C.byref(self.st), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
                                                   self.T, self.y_vecmat.data_ptr(), 0, self.ws.data_ptr(),
@@ -295,9 +299,10 @@ class DevicePass:
 
     def matvec(self, spk_dev, stream):
         if self.matvec_method == 'scatter' and self.sliced:
-            self._lib.check(self.lib.bsx_event_vecmat_sliced_fixed(C.byref(self.st_t), spk_dev.data_ptr(),
-                                                                   self._lib.SPK_BOOL8, self.T, self.y_matvec.data_ptr(),
-                                                                   0, self.scale_t, stream))
+            self._lib.check(self.lib.bsx_event_vecmat_sliced16(C.byref(self.st_t), self.loc_t.data_ptr(),
+                                                               self.q_t.data_ptr(), spk_dev.data_ptr(),
+                                                               self._lib.SPK_BOOL8, self.T, self.y_matvec.data_ptr(),
+                                                               0, self.scale_t, stream))
         elif self.matvec_method == 'scatter':
             self._lib.check(self.lib.bsx_event_vecmat(C.byref(self.st_t), spk_dev.data_ptr(), self._lib.SPK_BOOL8,
                                                       self.T, self.y_matvec.data_ptr(), 0, self.ws.data_ptr(),
@@ -500,11 +505,12 @@ def run_ours(args):
     smem_variant = facts['scatter_variant'] == _lib.VECMAT_SHARED_SLICES
     what = 'spike@W over the rows' + (' and W@spike over the transposed copy' if facts['matvec_method'] == 'scatter' else '')
     if smem_variant:
-        r_s = roof('scatter_smem_kernel<hetero, fixed-point>', s_bytes, s_launch_s, ms_scatter / ms_total,
+        r_s = roof('scatter_smem_kernel<hetero, fixed-point, 16-bit offsets>', s_bytes, s_launch_s, ms_scatter / ms_total,
                    what + '; one block per (spike vector, 32768-column slice of the output held in shared memory) '
-                   'over the copy whose rows are grouped by slice; weights summed as 2^-s fixed point with native '
-                   'shared-memory integer atomics (order-free: deterministic); algorithmic bytes can exceed the DRAM '
-                   'traffic because rows shared between vectors are served by L2')
+                   'over the copy whose rows are grouped by slice, columns stored as 16-bit offsets inside the slice '
+                   'and weights as 2^-s fixed point (6 bytes per synapse read; the algorithmic bytes count 8), summed '
+                   'with native shared-memory integer atomics (order-free: deterministic); algorithmic bytes can '
+                   'exceed the DRAM traffic also because rows shared between vectors are served by L2')
     else:
         r_s = roof('scatter_queue_kernel<hetero> (+compact)', s_bytes, s_launch_s, ms_scatter / ms_total,
                    what + '; limited by the L2 rate of red.global.add.f32 (about 190 G adds/s in a stand-alone '
@@ -530,7 +536,7 @@ def run_ours(args):
             if smem_variant:
                 # L2 serves rows that several vectors share, so DRAM traffic does not grow in proportion
                 # to the vectors: the capture is of this launch size and is used for no other
-                r_s['traffic'] = float(tr.get('scatter_smem_kernel_fixed_296_vectors', tr['scatter_smem_kernel_296_vectors'])) if T == 296 else None
+                r_s['traffic'] = float(tr['scatter_smem_kernel_packed_296_vectors']) if T == 296 and 'scatter_smem_kernel_packed_296_vectors' in tr else None
             else:
                 r_s['traffic'] = float(tr['scatter_queue_kernel_per_16_vectors']) * T / 16  # grows with the events
         except Exception:
@@ -730,11 +736,27 @@ def run_cases(torch, dev, dp, peak, rates=(0.001, 0.01, 0.1)):
                 _lib.check(lib.bsx_event_vecmat_sliced_fixed(C.byref(st_ts), sd.data_ptr(), _lib.SPK_BOOL8, T,
                                                              dp.y_matvec.data_ptr(), 0, scale_ts, stream))
 
+            loc_s, q_s = conn._packed('s', st_s, conn.data, scale_s)
+            loc_ts, q_ts = conn._packed('ts', st_ts, conn.data, scale_ts)
+
+            def vecmat_packed():
+                _lib.check(lib.bsx_event_vecmat_sliced16(C.byref(st_s), loc_s.data_ptr(), _lib.ptr(q_s), sd.data_ptr(),
+                                                         _lib.SPK_BOOL8, T, dp.y_vecmat.data_ptr(), 0, scale_s, stream))
+
+            def matvec_packed():
+                _lib.check(lib.bsx_event_vecmat_sliced16(C.byref(st_ts), loc_ts.data_ptr(), _lib.ptr(q_ts),
+                                                         sd.data_ptr(), _lib.SPK_BOOL8, T, dp.y_matvec.data_ptr(), 0,
+                                                         scale_ts, stream))
+
             scatter_bytes = events * (4 + 4 * h) + T * (n + 4 * n)
+            packed = (('spike@W, scatter over 16-bit offsets' + (' and fixed-point weights (deterministic)' if h else ''),
+                       vecmat_packed, scatter_bytes),
+                      ('W@spike, scatter over 16-bit offsets of the transposed copy' + (' (deterministic)' if h else ''),
+                       matvec_packed, scatter_bytes))
             fixed = (('spike@W, fixed-point scatter (deterministic)', vecmat_fixed, scatter_bytes),
                      ('W@spike, fixed-point scatter over the transposed copy (deterministic)', matvec_fixed,
                       scatter_bytes)) if h else ()
-            for prod, fn, alg in fixed + (('spike@W, scatter (output slices in shared memory)', vecmat_sliced, scatter_bytes),
+            for prod, fn, alg in packed + fixed + (('spike@W, scatter (output slices in shared memory)', vecmat_sliced, scatter_bytes),
                                   ('W@spike, event-driven scatter over the transposed copy', matvec_sliced, scatter_bytes),
                                   ('W@spike, deterministic gather (16 vectors per pass)', matvec_b16,
                                    dp.passes * (n * K * 4 + 2 * n) + T * 4 * n + events * 4 * h)):

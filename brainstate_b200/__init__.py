@@ -10,7 +10,7 @@ from . import _lib
 from . import event
 from . import nn
 from . import host
-from .event import EventArray, FixedPostNumConn, CSR
+from .event import EventArray, FixedPostNumConn, CSR, FixedPreNumConn, CSC
 
 __version__ = '0.1.0'
-__all__ = ['event', 'nn', 'host', 'EventArray', 'FixedPostNumConn', 'CSR']
+__all__ = ['event', 'nn', 'host', 'EventArray', 'FixedPostNumConn', 'CSR', 'FixedPreNumConn', 'CSC']

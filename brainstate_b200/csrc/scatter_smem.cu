@@ -32,27 +32,31 @@ constexpr int kSsList = 2048;     // active rows listed per round (row, start, l
 constexpr int kSsUnroll = 3;      // 128-bit loads in flight per lane and array
 constexpr int kSsDeal = 12;       // 32-entry stretches in flight per warp over the sliced layout
 
-__device__ __forceinline__ void smem_add_f32(float* p, float v) {
-  asm volatile("red.shared.add.f32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "f"(v) : "memory");
-}
-__device__ __forceinline__ void smem_count(float* p) {   // the slot holds a uint32 hit count
-  asm volatile("red.shared.add.u32 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)) : "memory");
-}
+// Adds into slot `cc` of the slice at shared address `sbase` when cc < ncol.  The test is a predicate
+// on the atomic itself: written as a C++ `if` around an asm statement it becomes a divergent branch
+// with its convergence barrier — three more instructions per add than the add itself.
 // COUNT (homogeneous weights, event input): the slice holds integer hit counts, added with the
 // native shared-memory integer atomic (the float add is a load + compare-and-swap loop), and
 // is multiplied by the weight once when it is written out.
 // FIXED: the slot holds a signed 32-bit fixed-point sum; v arrives already scaled by 2^s.  Integer
 // addition is associative, so the result does not depend on the order of the adds.
+__device__ __forceinline__ void smem_red_s32_if(uint32_t sbase, uint32_t cc, uint32_t ncol, int32_t q) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %1, %2;\n\t@p red.shared.add.s32 [%0], %3;\n\t}"
+               ::"r"(sbase + (cc << 2)), "r"(cc), "r"(ncol), "r"(q) : "memory");
+}
+__device__ __forceinline__ void smem_count_if(uint32_t sbase, uint32_t cc, uint32_t ncol) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %1, %2;\n\t@p red.shared.add.u32 [%0], 1;\n\t}"
+               ::"r"(sbase + (cc << 2)), "r"(cc), "r"(ncol) : "memory");
+}
+__device__ __forceinline__ void smem_red_f32_if(uint32_t sbase, uint32_t cc, uint32_t ncol, float v) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %1, %2;\n\t@p red.shared.add.f32 [%0], %3;\n\t}"
+               ::"r"(sbase + (cc << 2)), "r"(cc), "r"(ncol), "f"(v) : "memory");
+}
 template <bool COUNT, bool FIXED = false>
-__device__ __forceinline__ void smem_add(float* p, float v) {
-  if (COUNT) {
-    smem_count(p);
-  } else if (FIXED) {
-    const int q = __float2int_rn(v);
-    asm volatile("red.shared.add.s32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "r"(q) : "memory");
-  } else {
-    smem_add_f32(p, v);
-  }
+__device__ __forceinline__ void smem_add_if(uint32_t sbase, uint32_t cc, uint32_t ncol, float v) {
+  if (COUNT) smem_count_if(sbase, cc, ncol);
+  else if (FIXED) smem_red_s32_if(sbase, cc, ncol, __float2int_rn(v));
+  else smem_red_f32_if(sbase, cc, ncol, v);
 }
 
 // Active spikes among the positions [i0, i1) of batch row b; their positions go to dst
@@ -98,16 +102,18 @@ __device__ __forceinline__ int list_span(const void* __restrict__ spikes, int64_
 }
 
 template <bool HETERO, bool COUNT>
-__device__ __forceinline__ void add_four(float* acc, int32_t col0, uint32_t ncol, const int4 j, const float4 t, float v) {
-  const uint32_t c0 = (uint32_t)(j.x - col0), c1 = (uint32_t)(j.y - col0), c2 = (uint32_t)(j.z - col0),
-                 c3 = (uint32_t)(j.w - col0);
-  if (c0 < ncol) smem_add<COUNT>(acc + c0, HETERO ? __fmul_rn(v, t.x) : v);
-  if (c1 < ncol) smem_add<COUNT>(acc + c1, HETERO ? __fmul_rn(v, t.y) : v);
-  if (c2 < ncol) smem_add<COUNT>(acc + c2, HETERO ? __fmul_rn(v, t.z) : v);
-  if (c3 < ncol) smem_add<COUNT>(acc + c3, HETERO ? __fmul_rn(v, t.w) : v);
+__device__ __forceinline__ void add_four(uint32_t sbase, int32_t col0, uint32_t ncol, const int4 j, const float4 t, float v) {
+  smem_add_if<COUNT>(sbase, (uint32_t)(j.x - col0), ncol, HETERO ? __fmul_rn(v, t.x) : v);
+  smem_add_if<COUNT>(sbase, (uint32_t)(j.y - col0), ncol, HETERO ? __fmul_rn(v, t.y) : v);
+  smem_add_if<COUNT>(sbase, (uint32_t)(j.z - col0), ncol, HETERO ? __fmul_rn(v, t.z) : v);
+  smem_add_if<COUNT>(sbase, (uint32_t)(j.w - col0), ncol, HETERO ? __fmul_rn(v, t.w) : v);
 }
 
-template <bool HETERO, bool HAS_X, int FORMAT, bool SLICED, bool FIXED = false>
+// PACKED (over the sliced layout only): `idx` holds 16-bit column offsets inside the slice and, for
+// heterogeneous weights, `w` holds the weights already in fixed point (int32, scaled by 2^s): six
+// bytes per synapse instead of eight (two instead of four for homogeneous weights), and no
+// subtraction, multiplication or conversion per event.
+template <bool HETERO, bool HAS_X, int FORMAT, bool SLICED, bool FIXED = false, bool PACKED = false>
 __global__ void __launch_bounds__(kSsThreads, 1)
 scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
                     const void* __restrict__ spikes, const float* __restrict__ x, int64_t n_pre,
@@ -116,6 +122,7 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
   constexpr bool COUNT = !HETERO && !HAS_X;     // every event adds the same value: count, multiply once
   extern __shared__ __align__(16) unsigned char ss_raw[];
   float* acc = reinterpret_cast<float*>(ss_raw);
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(acc);
   // per listed row: where its entries start, how many there are, and which row it is
   int64_t* row_start = reinterpret_cast<int64_t*>(ss_raw + sizeof(float) * kSsSlice);
   int32_t* row_len = reinterpret_cast<int32_t*>(row_start + kSsList);
@@ -224,23 +231,46 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
       float v = HAS_X ? __ldg(x + b * n_pre + row) : 1.0f;
       if (!HETERO) v = __fmul_rn(v, w0);
       if (FIXED) v = __fmul_rn(v, scale);            // a power of two: exact
+      if (SLICED && PACKED) {
+        const uint16_t* __restrict__ gl = reinterpret_cast<const uint16_t*>(idx) + s;
+        const int32_t* __restrict__ gq = reinterpret_cast<const int32_t*>(w) + s;
+        const int len = row_len[t];
+        for (int p0 = lane; p0 < len; p0 += 32 * kSsDeal) {
+          uint32_t cc[kSsDeal];
+          int32_t q[kSsDeal];
+#pragma unroll
+          for (int u = 0; u < kSsDeal; ++u) {
+            const bool in = p0 + 32 * u < len;
+            cc[u] = in ? (uint32_t)__ldg(gl + p0 + 32 * u) : 0xffffu;
+            q[u] = (HETERO && in) ? __ldg(gq + p0 + 32 * u) : 0;
+          }
+#pragma unroll
+          for (int u = 0; u < kSsDeal; ++u) {
+            if (HETERO) smem_red_s32_if(sbase, cc[u], ncol, q[u]);
+            else smem_count_if(sbase, cc[u], ncol);
+          }
+        }
+        continue;
+      }
       if (SLICED) {
         // the group is laid out in 32-entry stretches whose entries fall into distinct banks:
         // one coalesced 4-byte load per lane and stretch, all issued before the first add
-        for (int64_t p0 = s + lane; p0 < e; p0 += 32 * kSsDeal) {
+        // (32-bit offsets from the group's start: one 64-bit address per array and group)
+        const int32_t* __restrict__ gi = idx + s;
+        const float* __restrict__ gw = w + s;
+        const int len = row_len[t];
+        for (int p0 = lane; p0 < len; p0 += 32 * kSsDeal) {
           int32_t j[kSsDeal];
           float t[kSsDeal];
 #pragma unroll
           for (int u = 0; u < kSsDeal; ++u) {
-            const bool in = p0 + 32 * u < e;
-            j[u] = in ? __ldg(idx + p0 + 32 * u) : -1;
-            t[u] = (HETERO && in) ? __ldg(w + p0 + 32 * u) : 0.0f;
+            const bool in = p0 + 32 * u < len;
+            j[u] = in ? __ldg(gi + p0 + 32 * u) : -1;
+            t[u] = (HETERO && in) ? __ldg(gw + p0 + 32 * u) : 0.0f;
           }
 #pragma unroll
-          for (int u = 0; u < kSsDeal; ++u) {
-            const uint32_t cc = (uint32_t)(j[u] - col0);
-            if (cc < ncol) smem_add<COUNT, FIXED>(acc + cc, HETERO ? __fmul_rn(v, t[u]) : v);
-          }
+          for (int u = 0; u < kSsDeal; ++u)
+            smem_add_if<COUNT, FIXED>(sbase, (uint32_t)(j[u] - col0), ncol, HETERO ? __fmul_rn(v, t[u]) : v);
         }
         continue;
       }
@@ -274,16 +304,13 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
           else t4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
-        for (int u = 0; u < kSsUnroll; ++u) add_four<HETERO, COUNT>(acc, col0, ncol, j[u], t4[u], v);
+        for (int u = 0; u < kSsUnroll; ++u) add_four<HETERO, COUNT>(sbase, col0, ncol, j[u], t4[u], v);
       }
       if (vec_ok) {
-        const uint32_t cc = (uint32_t)(hj - col0);
-        if (cc < ncol) smem_add<COUNT>(acc + cc, HETERO ? __fmul_rn(v, hw) : v);
+        smem_add_if<COUNT>(sbase, (uint32_t)(hj - col0), ncol, HETERO ? __fmul_rn(v, hw) : v);
       } else {
-        for (int64_t p = s + lane; p < e; p += 32) {
-          const uint32_t cc = (uint32_t)(__ldg(idx + p) - col0);
-          if (cc < ncol) smem_add<COUNT>(acc + cc, HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
-        }
+        for (int64_t p = s + lane; p < e; p += 32)
+          smem_add_if<COUNT>(sbase, (uint32_t)(__ldg(idx + p) - col0), ncol, HETERO ? __fmul_rn(v, __ldg(w + p)) : v);
       }
     }
     __syncthreads();
@@ -449,6 +476,57 @@ static int launch_scatter_smem_fixed(const bsx_conn_t* conn, const void* spikes,
 #undef BSX_SSF
   BSX_LAUNCH_CHECK("scatter_smem_kernel<fixed>");
   return BSX_OK;
+}
+
+// The same over 16-bit column offsets and (heterogeneous) weights stored in fixed point.
+static int launch_scatter_smem_packed(const bsx_conn_t* conn, const uint16_t* local, const int32_t* qweights,
+                                      const void* spikes, int format, int64_t batch, float* out, int accumulate,
+                                      cudaStream_t st, int row_mul, int scale_log2) {
+  if (sm_count() <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  const int64_t slices = (conn->n_post + kSsSlice - 1) / kSsSlice;
+  const dim3 grid((unsigned)slices, (unsigned)batch, 1);
+  const size_t smem = sizeof(float) * kSsSlice + (sizeof(int64_t) + 2 * sizeof(int32_t)) * kSsList;
+  const RowMap rm = make_rowmap(conn);
+  const float scale = ldexpf(1.0f, scale_log2), inv_scale = ldexpf(1.0f, -scale_log2);
+  const int32_t* idx = reinterpret_cast<const int32_t*>(local);
+  const float* w = conn->hetero ? reinterpret_cast<const float*>(qweights) : conn->weights;
+#define BSX_SSP(H, F)                                                                                               \
+  do {                                                                                                              \
+    BSX_CUDA(cudaFuncSetAttribute(scatter_smem_kernel<H, false, F, true, H, true>,                                  \
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                         \
+    scatter_smem_kernel<H, false, F, true, H, true><<<grid, kSsThreads, smem, st>>>(                                \
+        rm, idx, w, spikes, nullptr, conn->n_pre, conn->n_post, out, accumulate, false, row_mul, scale, inv_scale); \
+  } while (0)
+#define BSX_SSP_F(H)                                           \
+  do {                                                         \
+    if (format == BSX_SPK_BOOL8) BSX_SSP(H, BSX_SPK_BOOL8);    \
+    else if (format == BSX_SPK_F32) BSX_SSP(H, BSX_SPK_F32);   \
+    else BSX_SSP(H, BSX_SPK_BITS32);                           \
+  } while (0)
+  if (conn->hetero) BSX_SSP_F(true); else BSX_SSP_F(false);
+#undef BSX_SSP_F
+#undef BSX_SSP
+  BSX_LAUNCH_CHECK("scatter_smem_kernel<packed>");
+  return BSX_OK;
+}
+
+__global__ void __launch_bounds__(256)
+compress_local_kernel(const int32_t* __restrict__ idx, int64_t nnz, int32_t last_slice, uint16_t* __restrict__ local) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < nnz; p += stride) {
+    const int32_t c = __ldg(idx + p);
+    // a column is stored relative to the start of its slice; negative or too large columns (which
+    // bsx_validate_conn reports) get an offset no slice accepts
+    const int32_t sl = c / kSsSlice;
+    local[p] = (c < 0 || sl > last_slice) ? (uint16_t)0xffffu : (uint16_t)(c - sl * kSsSlice);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+quantize_kernel(const float* __restrict__ w, int64_t n, float scale, int32_t* __restrict__ q) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n; p += stride)
+    q[p] = __float2int_rn(__fmul_rn(__ldg(w + p), scale));
 }
 
 // |w| summed per output column as 2^-32 fixed point (order-free), then the largest column.
@@ -622,6 +700,61 @@ int bsx_event_vecmat_sliced_fixed(const bsx_conn_t* sliced, const void* spikes, 
   if (S > 4 || batch > 65535) return fail(BSX_ERR_UNSUPPORTED, "the sliced scatter covers up to 131072 columns and 65535 vectors");
   return launch_scatter_smem_fixed(sliced, spikes, spike_format, batch, out, accumulate, as_stream(stream), (int)S,
                                    scale_log2);
+}
+
+int bsx_sliced_compress(const bsx_conn_t* sliced, uint16_t* local, bsx_stream_t stream) {
+  BSX_TRACE("bsx_sliced_compress");
+  const int rc = check_conn(sliced);
+  if (rc) return rc;
+  const int64_t S = bsx_sliced_slices(sliced->n_post);
+  if (S < 1 || S > 4) return fail(BSX_ERR_UNSUPPORTED, "the sliced layout covers 1 to 131072 columns");
+  if (sliced->nnz == 0) return BSX_OK;
+  if (!local) return fail(BSX_ERR_INVALID_ARG, "local is NULL");
+  const int sms = sm_count();
+  if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  compress_local_kernel<<<(unsigned)(sms * 8), 256, 0, as_stream(stream)>>>(sliced->indices, sliced->nnz, (int32_t)(S - 1), local);
+  BSX_LAUNCH_CHECK("compress_local_kernel");
+  return BSX_OK;
+}
+
+int bsx_quantize_f32(const float* w, int64_t n, int32_t scale_log2, int32_t* q, bsx_stream_t stream) {
+  BSX_TRACE("bsx_quantize_f32");
+  if (n < 0) return fail(BSX_ERR_INVALID_ARG, "negative n");
+  if (scale_log2 < -60 || scale_log2 > 30) return fail(BSX_ERR_INVALID_ARG, "scale_log2 out of range (see bsx_fixed_scale_log2)");
+  if (n == 0) return BSX_OK;
+  if (!w || !q) return fail(BSX_ERR_INVALID_ARG, "w or q is NULL");
+  const int sms = sm_count();
+  if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  quantize_kernel<<<(unsigned)(sms * 8), 256, 0, as_stream(stream)>>>(w, n, ldexpf(1.0f, scale_log2), q);
+  BSX_LAUNCH_CHECK("quantize_kernel");
+  return BSX_OK;
+}
+
+int bsx_event_vecmat_sliced16(const bsx_conn_t* sliced, const uint16_t* local, const int32_t* qweights,
+                              const void* spikes, int spike_format, int64_t batch, float* out, int accumulate,
+                              int32_t scale_log2, bsx_stream_t stream) {
+  BSX_TRACE("bsx_event_vecmat_sliced16");
+  const int rc = check_conn(sliced);
+  if (rc) return rc;
+  if (!sliced->indptr || !sliced->indptr_is_64)
+    return fail(BSX_ERR_INVALID_ARG, "the sliced layout has 64-bit group offsets in indptr");
+  if (batch < 0) return fail(BSX_ERR_INVALID_ARG, "negative batch");
+  if (scale_log2 < -60 || scale_log2 > 30) return fail(BSX_ERR_INVALID_ARG, "scale_log2 out of range (see bsx_fixed_scale_log2)");
+  if (batch == 0 || sliced->n_post == 0) return BSX_OK;
+  if (!out) return fail(BSX_ERR_INVALID_ARG, "out is NULL");
+  if (sliced->n_pre == 0 || sliced->nnz == 0)
+    return accumulate ? BSX_OK : launch_zero(out, batch * sliced->n_post, as_stream(stream));
+  if (!spikes) return fail(BSX_ERR_INVALID_ARG, "input vector is NULL");
+  if (!local) return fail(BSX_ERR_INVALID_ARG, "local is NULL");
+  if (sliced->hetero && !qweights) return fail(BSX_ERR_INVALID_ARG, "heterogeneous weights need qweights (bsx_quantize_f32)");
+  if ((reinterpret_cast<uintptr_t>(local) & 1) || (reinterpret_cast<uintptr_t>(qweights) & 3))
+    return fail(BSX_ERR_INVALID_ARG, "local or qweights misaligned");
+  if (spike_format != BSX_SPK_BOOL8 && spike_format != BSX_SPK_F32 && spike_format != BSX_SPK_BITS32)
+    return fail(BSX_ERR_UNSUPPORTED, "the sliced scatter takes byte, float or packed spikes");
+  const int64_t S = bsx_sliced_slices(sliced->n_post);
+  if (S > 4 || batch > 65535) return fail(BSX_ERR_UNSUPPORTED, "the sliced scatter covers up to 131072 columns and 65535 vectors");
+  return launch_scatter_smem_packed(sliced, local, qweights, spikes, spike_format, batch, out, accumulate,
+                                    as_stream(stream), (int)S, scale_log2);
 }
 
 }  // extern "C"

@@ -22,8 +22,13 @@ import torch
 from . import _lib
 from ._lib import BsxConn, check, lib, ptr
 
-__all__ = ['EventArray', 'FixedPostNumConn', 'CSR', 'event_vecmat', 'float_vecmat',
+__all__ = ['EventArray', 'FixedPostNumConn', 'CSR', 'FixedPreNumConn', 'CSC', 'event_vecmat', 'float_vecmat',
            'event_matvec', 'float_matvec', 'pack_spikes', 'spike_format_of']
+
+
+# The batched scatter reads the compressed form of the sliced copy (16-bit column offsets, weights
+# stored in fixed point) wherever its sums are order-free; False keeps the 32-bit arrays.
+PACKED_SLICES = True
 
 
 def _require_cuda(t: torch.Tensor, what: str):
@@ -57,6 +62,8 @@ class EventArray:
     def __matmul__(self, other):
         if isinstance(other, _SparseConn):
             return other._vecmat(self.value, event=True)
+        if isinstance(other, _InDegreeConn):
+            return other._gather(self.value, event=True)
         if isinstance(other, torch.Tensor):       # dense event product (EventLinear)
             from .nn._event_linear import dense_event_matmul
             return dense_event_matmul(self.value, other)
@@ -292,6 +299,45 @@ class _SparseConn:
         self._derived['scale_' + layout] = (key, int(s.value), misses)
         return int(s.value)
 
+    def _packed(self, layout: str, st: BsxConn, weights: torch.Tensor, scale: int):
+        """Compressed form of a sliced copy: 16-bit column offsets inside the slice (built once)
+        and, for heterogeneous weights, the weights in ``2^-scale`` fixed point (kept until the
+        weight tensor or the scale changes)."""
+        dev = self.indices.device
+        loc = self._derived.get('loc_' + layout)
+        if loc is None:
+            loc = torch.empty(max(self.nnz, 1), dtype=torch.int16, device=dev)
+            check(lib().bsx_sliced_compress(C.byref(st), ptr(loc), _lib.current_stream()))
+            self._derived['loc_' + layout] = loc
+        q = None
+        if self.hetero:
+            wsrc = weights.contiguous()
+            key = (wsrc.data_ptr(), wsrc._version, wsrc.numel(), scale)
+            cached = self._derived.get('q_' + layout)
+            if cached is not None and cached[0] == key:
+                q = cached[1]
+            else:
+                q = torch.empty(max(self.nnz, 1), dtype=torch.int32, device=dev)
+                check(lib().bsx_quantize_f32(st.weights, self.nnz, scale, ptr(q), _lib.current_stream()))
+                self._derived['q_' + layout] = (key, q, wsrc)
+        return loc, q
+
+    def _sliced_call(self, layout: str, st: BsxConn, weights: torch.Tensor, scale, xb, fmt, batch, out, accumulate):
+        """One launch of the scatter that keeps output slices in shared memory, over the sliced copy
+        ``st`` (``layout``: ``'s'`` forward, ``'ts'`` transposed).  ``scale`` None: float sums
+        (heterogeneous) over the 32-bit layout.  Otherwise order-free sums over the compressed
+        layout (``PACKED_SLICES``) or the 32-bit one."""
+        stream = _lib.current_stream()
+        if scale is None and self.hetero:
+            check(lib().bsx_event_vecmat_sliced(C.byref(st), ptr(xb), fmt, batch, ptr(out), int(accumulate), stream))
+        elif PACKED_SLICES:
+            loc, q = self._packed(layout, st, weights, scale or 0)
+            check(lib().bsx_event_vecmat_sliced16(C.byref(st), ptr(loc), ptr(q), ptr(xb), fmt, batch, ptr(out),
+                                                  int(accumulate), scale or 0, stream))
+        else:
+            check(lib().bsx_event_vecmat_sliced_fixed(C.byref(st), ptr(xb), fmt, batch, ptr(out), int(accumulate),
+                                                      scale or 0, stream))
+
     @staticmethod
     def _fixed_applies(n_out: int, batch: int) -> bool:
         """The fixed-point scatter keeps output slices in shared memory: batches of 16 and more
@@ -339,6 +385,81 @@ class CSR(_SparseConn):
         super().__init__(data, indices, indptr, shape)
 
 
+class _InDegreeConn:
+    """Connectivity stored by POSTSYNAPTIC neuron: every column of the ``(n_pre, n_post)`` matrix
+    lists its presynaptic partners (a fixed number of them, or compressed sparse columns).
+
+    The arrays are exactly those of an out-degree layout of the transposed matrix, so the
+    products run on the same kernels with the roles swapped: ``x @ conn`` is the row-gather
+    ``M @ x`` over ``M = conn^T`` (every output is summed by one warp in a fixed order, hence
+    deterministic), ``conn @ v`` is the scatter ``v @ M``.  ``matvec_method`` selects the
+    event-driven form of ``EventArray(spk) @ conn`` (``'scatter'``, over a presynaptic-major copy
+    built once) as for the out-degree containers.
+    """
+
+    def __init__(self, mirror: _SparseConn, shape):
+        self.shape = (int(shape[0]), int(shape[1]))
+        self._m = mirror                   # out-degree layout of the transposed matrix
+        self.matvec_method = 'gather'
+
+    data = property(lambda self: self._m.data)
+    indices = property(lambda self: self._m.indices)
+    indptr = property(lambda self: self._m.indptr)
+    hetero = property(lambda self: self._m.hetero)
+    nnz = property(lambda self: self._m.nnz)
+
+    def with_data(self, data):
+        new = object.__new__(type(self))
+        new.__dict__.update(self.__dict__)
+        new._m = self._m.with_data(data)
+        return new
+
+    def validate(self):
+        self._m.validate()
+        return self
+
+    def _gather(self, x, event: bool):
+        return _MatVec.apply(x, self._m.data, self._m, event, self.matvec_method)
+
+    def __rmatmul__(self, x):              # x @ conn -> (…, n_post)
+        if isinstance(x, EventArray):
+            return self._gather(x.value, event=True)
+        if isinstance(x, torch.Tensor):
+            return self._gather(x, event=False)
+        return NotImplemented
+
+    def __matmul__(self, v):               # conn @ v -> (…, n_pre)
+        if isinstance(v, EventArray):
+            return self._m._vecmat(v.value, event=True)
+        if isinstance(v, torch.Tensor):
+            return self._m._vecmat(v, event=False)
+        return NotImplemented
+
+
+class FixedPreNumConn(_InDegreeConn):
+    """``(weight, indices)`` with a fixed number of presynaptic partners per postsynaptic
+    neuron: ``indices`` has shape ``(n_post, conn_num)`` with values in ``[0, n_pre)``
+    (``brainevent.FixedPreNumConn``, the layout the reference's ``efferent_target='pre'``
+    branch names, ``_event_fixedprob.py:123-140``)."""
+
+    def __init__(self, data_indices, shape):
+        data, indices = data_indices
+        if indices.dim() != 2 or indices.shape[0] != shape[1]:
+            raise ValueError('indices must have shape (n_post, conn_num)')
+        super().__init__(FixedPostNumConn((data, indices), (shape[1], shape[0])), shape)
+
+
+class CSC(_InDegreeConn):
+    """``(weight, indices, indptr)`` compressed sparse columns: ``indptr`` has ``n_post + 1``
+    entries and ``indices`` holds presynaptic ids (``brainevent.CSC``)."""
+
+    def __init__(self, data_indices_indptr, shape):
+        data, indices, indptr = data_indices_indptr
+        if indptr.numel() != shape[1] + 1:
+            raise ValueError('indptr must have n_post + 1 entries')
+        super().__init__(CSR((data, indices, indptr), (shape[1], shape[0])), shape)
+
+
 # ----------------------------------------------------------------------------
 # raw calls (no autograd)
 # ----------------------------------------------------------------------------
@@ -368,8 +489,7 @@ def _raw_vecmat(conn: _SparseConn, x: torch.Tensor, weights: torch.Tensor, event
         if event and conn._fixed_applies(n_post, batch):
             st_s = conn._sliced_struct(weights)
             scale = conn._fixed_scale('s', st_s, weights)
-            check(lib().bsx_event_vecmat_sliced_fixed(C.byref(st_s), ptr(xb), spike_format_of(xb), batch, ptr(out),
-                                                      int(accumulate), scale, stream))
+            conn._sliced_call('s', st_s, weights, scale, xb, spike_format_of(xb), batch, out, accumulate)
             return out.reshape(lead + (n_post,))
         method = 'gather' if event else 'scatter'
     if event and method == 'gather':
@@ -394,12 +514,7 @@ def _raw_vecmat(conn: _SparseConn, x: torch.Tensor, weights: torch.Tensor, event
         # shared memory) unless float sums are asked for.
         st_s = conn._sliced_struct(weights)
         scale = conn._fixed_scale('s', st_s, weights, if_settled=True) if conn.hetero and method != 'float' else None
-        if scale is not None:
-            check(lib().bsx_event_vecmat_sliced_fixed(C.byref(st_s), ptr(xb), spike_format_of(xb), batch, ptr(out),
-                                                      int(accumulate), scale, stream))
-        else:
-            check(lib().bsx_event_vecmat_sliced(C.byref(st_s), ptr(xb), spike_format_of(xb), batch, ptr(out),
-                                                int(accumulate), stream))
+        conn._sliced_call('s', st_s, weights, scale, xb, spike_format_of(xb), batch, out, accumulate)
         return out.reshape(lead + (n_post,))
     ws_bytes = lib().bsx_event_vecmat_workspace_bytes(batch, n_pre)
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
@@ -457,8 +572,7 @@ def event_matvec(conn: _SparseConn, spk: torch.Tensor, bits: bool = False, metho
         if conn._fixed_applies(n_pre, batch):
             st_ts = conn._transposed_sliced_struct(conn.data)
             scale = conn._fixed_scale('ts', st_ts, conn.data)
-            check(lib().bsx_event_vecmat_sliced_fixed(C.byref(st_ts), ptr(xb), fmt, batch, ptr(out), 0, scale,
-                                                      _lib.current_stream()))
+            conn._sliced_call('ts', st_ts, conn.data, scale, xb, fmt, batch, out, False)
             return out.reshape(lead + (n_pre,))
         method = 'gather'
     if method in ('scatter', 'float'):
@@ -467,12 +581,7 @@ def event_matvec(conn: _SparseConn, spk: torch.Tensor, bits: bool = False, metho
             st_ts = conn._transposed_sliced_struct(conn.data)
             scale = (conn._fixed_scale('ts', st_ts, conn.data, if_settled=True)
                      if conn.hetero and method == 'scatter' else None)
-            if scale is not None:
-                check(lib().bsx_event_vecmat_sliced_fixed(C.byref(st_ts), ptr(xb), fmt, batch, ptr(out), 0, scale,
-                                                          _lib.current_stream()))
-            else:
-                check(lib().bsx_event_vecmat_sliced(C.byref(st_ts), ptr(xb), fmt, batch, ptr(out), 0,
-                                                    _lib.current_stream()))
+            conn._sliced_call('ts', st_ts, conn.data, scale, xb, fmt, batch, out, False)
             return out.reshape(lead + (n_pre,))
         ws_bytes = lib().bsx_event_vecmat_workspace_bytes(batch, n_post)
         ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=spk.device)
@@ -488,7 +597,7 @@ def event_matvec(conn: _SparseConn, spk: torch.Tensor, bits: bool = False, metho
 
 
 def float_matvec(conn: _SparseConn, v: torch.Tensor, weights: Optional[torch.Tensor] = None):
-    """``conn @ v`` for float ``v``."""
+    """``conn @ v`` for float ``v`` (not recorded by autograd; the in-degree containers wrap it)."""
     _require_cuda(v, 'v')
     n_pre, n_post = conn.shape
     vb, lead = _flatten_batch(v.to(torch.float32), n_post)
@@ -578,5 +687,54 @@ class _VecMat(torch.autograd.Function):
         if w_dot is not None:
             wd = w_dot.to(torch.float32)
             term = _raw_vecmat(conn.with_data(wd), x, wd, event=ctx.event)
+            out = term if out is None else out + term
+        return out
+
+
+class _MatVec(torch.autograd.Function):
+    """``y = M @ x`` over an out-degree layout ``M`` (``y[j] = sum_k w[j,k] x[idx[j,k]]``): the
+    product of the in-degree containers.  ``dx = ct @ M`` is a scatter of the cotangent,
+    ``dw[j,k] = ct[j] * x[idx[j,k]]`` (the event indicator for an event input) is the weight
+    cotangent of the scatter product with the operands exchanged."""
+
+    @staticmethod
+    def forward(x, weights, conn, event, method):
+        c = conn.with_data(weights)
+        if event:
+            return event_matvec(c, x, method=method)
+        return float_matvec(c, x, weights)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        x, weights, conn, event, method = inputs
+        ctx.conn, ctx.event, ctx.method = conn, event, method
+        ctx.save_for_backward(x, weights)
+        ctx.save_for_forward(x, weights)
+        ctx.x_differentiable = x.dtype.is_floating_point
+
+    @staticmethod
+    def backward(ctx, ct):
+        x, weights = ctx.saved_tensors
+        conn = ctx.conn
+        ct = ct.contiguous().to(torch.float32)
+        dx = dw = None
+        if ctx.needs_input_grad[0] and ctx.x_differentiable:
+            dx = _raw_vecmat(conn, ct, weights, event=False).to(x.dtype)
+        if ctx.needs_input_grad[1]:
+            xv = (x != 0).to(torch.float32) if ctx.event else x.to(torch.float32)
+            _, dw = _raw_vjp(conn, ct, weights, xv, event=False, need_dx=False, need_dw=True)
+        return dx, dw, None, None, None
+
+    @staticmethod
+    def jvp(ctx, x_dot, w_dot, *_):
+        x, weights = ctx.saved_tensors
+        conn = ctx.conn
+        out = None
+        if x_dot is not None:
+            out = float_matvec(conn, x_dot.to(torch.float32), weights)
+        if w_dot is not None:
+            wd = w_dot.to(torch.float32)
+            c = conn.with_data(wd)
+            term = event_matvec(c, x, method=ctx.method) if ctx.event else float_matvec(c, x, wd)
             out = term if out is None else out + term
         return out

@@ -70,6 +70,12 @@ class HostEventProducts:
                 self.scale_f = conn._fixed_scale('s', self.st_f, conn.data) if forward else None
                 self.scale_t = (conn._fixed_scale('ts', self.st_t, conn.data)
                                 if reverse and reverse_method == 'scatter' else None)
+            from . import event as _event
+            if _event.PACKED_SLICES:       # the compressed copies are built here, not inside the first call
+                if forward:
+                    conn._packed('s', self.st_f, conn.data, self.scale_f or 0)
+                if reverse and reverse_method == 'scatter':
+                    conn._packed('ts', self.st_t, conn.data, self.scale_t or 0)
 
     def __call__(self, spk_host: torch.Tensor, y_fwd_host: Optional[torch.Tensor] = None,
                  y_rev_host: Optional[torch.Tensor] = None):
@@ -103,22 +109,16 @@ class HostEventProducts:
                 if c >= self.slots:
                     self.s_comp.wait_event(ev_out[c - self.slots])     # the slot's results were downloaded
                 stream = self.s_comp.cuda_stream
-                if self.forward and self.sliced and self.scale_f is not None:
-                    check(l.bsx_event_vecmat_sliced_fixed(C.byref(self.st_f), self.spk[slot].data_ptr(), _lib.SPK_BOOL8,
-                                                          nb, self.y_fwd[slot].data_ptr(), 0, self.scale_f, stream))
-                elif self.forward and self.sliced:
-                    check(l.bsx_event_vecmat_sliced(C.byref(self.st_f), self.spk[slot].data_ptr(), _lib.SPK_BOOL8, nb,
-                                                    self.y_fwd[slot].data_ptr(), 0, stream))
+                if self.forward and self.sliced:
+                    self.conn._sliced_call('s', self.st_f, self.conn.data, self.scale_f, self.spk[slot], _lib.SPK_BOOL8,
+                                           nb, self.y_fwd[slot], False)
                 elif self.forward:
                     check(l.bsx_event_vecmat(C.byref(self.st), self.spk[slot].data_ptr(), _lib.SPK_BOOL8, nb,
                                              self.y_fwd[slot].data_ptr(), 0, self.ws_f.data_ptr(), self.ws_f_bytes,
                                              stream))
-                if self.reverse and self.reverse_method == 'scatter' and self.sliced and self.scale_t is not None:
-                    check(l.bsx_event_vecmat_sliced_fixed(C.byref(self.st_t), self.spk[slot].data_ptr(), _lib.SPK_BOOL8,
-                                                          nb, self.y_rev[slot].data_ptr(), 0, self.scale_t, stream))
-                elif self.reverse and self.reverse_method == 'scatter' and self.sliced:
-                    check(l.bsx_event_vecmat_sliced(C.byref(self.st_t), self.spk[slot].data_ptr(), _lib.SPK_BOOL8, nb,
-                                                    self.y_rev[slot].data_ptr(), 0, stream))
+                if self.reverse and self.reverse_method == 'scatter' and self.sliced:
+                    self.conn._sliced_call('ts', self.st_t, self.conn.data, self.scale_t, self.spk[slot],
+                                           _lib.SPK_BOOL8, nb, self.y_rev[slot], False)
                 elif self.reverse and self.reverse_method == 'scatter':
                     check(l.bsx_event_vecmat(C.byref(self.st_t), self.spk[slot].data_ptr(), _lib.SPK_BOOL8, nb,
                                              self.y_rev[slot].data_ptr(), 0, self.ws_r.data_ptr(), self.ws_r_bytes,

@@ -784,3 +784,177 @@ def test_fixed_point_scatter_is_deterministic_and_close(layout, bsx, cuda):
     yh = event_vecmat(hom, ts, method='fixed')
     counts = eo.event_vecmat(spk, idx_h, np.float32(1.0), n)
     assert np.array_equal(yh.cpu().numpy(), (counts * np.float32(0.1)).astype(np.float32))
+
+
+@pytest.mark.parametrize('shape', [(30, 20, 3), (513, 257, 131), (96, 1000, 7)])
+@pytest.mark.parametrize('hetero', [False, True])
+@pytest.mark.parametrize('layout', ['fixed', 'csc'])
+def test_in_degree_layouts_match_oracle(shape, hetero, layout, cuda):
+    """Connectivity stored by postsynaptic neuron (a fixed number of presynaptic partners, or CSC):
+    the arrays are those of the transposed matrix in out-degree form, so the oracle products are
+    the matvec / vecmat of that mirror."""
+    from brainstate_b200 import EventArray, FixedPreNumConn, CSC
+    n_pre, n_post, K = shape
+    rs = np.random.RandomState(31)
+    if layout == 'fixed':
+        idx = eo.fixed_num_indices(17, n_post, n_pre, K)            # (n_post, K) presynaptic ids
+        indptr = None
+    else:
+        idx, indptr, _ = eo.afferent_csr(17, n_post, n_pre, K, 0.6)
+    w = rs.uniform(0.05, 0.15, size=idx.shape).astype(np.float32) if hetero else np.float32(0.1)
+    ti, tw = torch.from_numpy(idx).to(cuda), torch.as_tensor(w, device=cuda)
+    if layout == 'fixed':
+        conn = FixedPreNumConn((tw, ti), shape=(n_pre, n_post))
+    else:
+        conn = CSC((tw, ti, torch.from_numpy(indptr).to(cuda)), shape=(n_pre, n_post))
+    conn.validate()
+    for batch in (None, 5):
+        size = (n_pre,) if batch is None else (batch, n_pre)
+        spk = rs.random_sample(size) < 0.2
+        ref = np.stack([eo.event_matvec(s, idx, w, n_post, indptr) for s in np.atleast_2d(spk)]).reshape(
+            size[:-1] + (n_post,))
+        y = EventArray(torch.from_numpy(spk).to(cuda)) @ conn
+        assert tuple(y.shape) == size[:-1] + (n_post,)
+        close(y, ref)
+        y2 = EventArray(torch.from_numpy(spk).to(cuda)) @ conn           # one warp per output, fixed order
+        assert torch.equal(y, y2)
+        conn.matvec_method = 'scatter'                                    # event-driven form, same sums
+        close(EventArray(torch.from_numpy(spk).to(cuda)) @ conn, ref)
+        conn.matvec_method = 'gather'
+        x = rs.standard_normal(size).astype(np.float32)
+        refx = np.stack([eo.float_matvec(v, idx, w, n_post, indptr) for v in np.atleast_2d(x)]).reshape(
+            size[:-1] + (n_post,))
+        close(torch.from_numpy(x).to(cuda) @ conn, refx, scale=float(np.abs(x).sum() / x.size * K * 10 + 1))
+        v = rs.standard_normal(size[:-1] + (n_post,)).astype(np.float32)
+        refv = np.stack([eo.float_vecmat(u, idx, w, n_pre, indptr) for u in np.atleast_2d(v)]).reshape(size)
+        close(conn @ torch.from_numpy(v).to(cuda), refv, scale=float(K * 10 + 1))
+        sp = rs.random_sample(size[:-1] + (n_post,)) < 0.3
+        refe = np.stack([eo.event_vecmat(u, idx, w, n_pre, indptr) for u in np.atleast_2d(sp)]).reshape(size)
+        close(conn @ EventArray(torch.from_numpy(sp).to(cuda)), refe)
+
+
+@pytest.mark.parametrize('event', [True, False])
+def test_in_degree_layout_reverse_and_forward_mode(event, cuda):
+    from brainstate_b200 import EventArray, FixedPreNumConn
+    n_pre, n_post, K = 60, 45, 7
+    rs = np.random.RandomState(5)
+    idx = eo.fixed_num_indices(23, n_post, n_pre, K)
+    w = rs.uniform(0.05, 0.15, size=idx.shape).astype(np.float32)
+    x = (rs.random_sample((3, n_pre)) < 0.4) * rs.uniform(0.5, 2.0, (3, n_pre))
+    x = x.astype(np.float32)
+    ct = rs.standard_normal((3, n_post)).astype(np.float32)
+    tw = torch.tensor(w, device=cuda, requires_grad=True)
+    tx = torch.tensor(x, device=cuda, requires_grad=True)
+    conn = FixedPreNumConn((tw, torch.from_numpy(idx).to(cuda)), shape=(n_pre, n_post))
+    y = (EventArray(tx) if event else tx) @ conn
+    y.backward(torch.from_numpy(ct).to(cuda))
+    xv = (x != 0).astype(np.float32) if event else x
+    # y[b,j] = sum_k w[j,k] xv[b, idx[j,k]]
+    dw = np.einsum('bj,bjk->jk', ct.astype(np.float64), xv[:, idx].astype(np.float64))
+    dx = np.zeros((3, n_pre))
+    for j in range(n_post):
+        for k in range(K):
+            dx[:, idx[j, k]] += ct[:, j].astype(np.float64) * w[j, k]
+    np.testing.assert_allclose(tw.grad.cpu().numpy(), dw, rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(tx.grad.cpu().numpy(), dx, rtol=1e-5, atol=1e-5)
+    # forward mode: y_dot = M_w @ x_dot + M_wdot @ x
+    import torch.autograd.forward_ad as fwad
+    xd = rs.standard_normal((3, n_pre)).astype(np.float32)
+    wd = rs.standard_normal(idx.shape).astype(np.float32)
+    with fwad.dual_level():
+        dxt = fwad.make_dual(torch.tensor(x, device=cuda), torch.from_numpy(xd).to(cuda))
+        dwt = fwad.make_dual(torch.tensor(w, device=cuda), torch.from_numpy(wd).to(cuda))
+        c2 = FixedPreNumConn((dwt, torch.from_numpy(idx).to(cuda)), shape=(n_pre, n_post))
+        out = (EventArray(dxt) if event else dxt) @ c2
+        tangent = fwad.unpack_dual(out).tangent
+    ref = np.einsum('jk,bjk->bj', w.astype(np.float64), xd[:, idx]) + np.einsum('jk,bjk->bj', wd.astype(np.float64),
+                                                                                xv[:, idx])
+    np.testing.assert_allclose(tangent.cpu().numpy(), ref, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize('n_post', [1000, 40000, 70001])
+@pytest.mark.parametrize('hetero', [False, True])
+def test_compressed_sliced_layout_equals_the_32_bit_one(n_post, hetero, bsx, cuda):
+    """16-bit column offsets inside the slice and weights stored in fixed point: the same sums, bit
+    for bit, as the fixed-point (heterogeneous) / counting (homogeneous) scatter over the 32-bit
+    sliced copy, and the oracle's within the float tolerance; bool, float and packed spikes;
+    accumulate; both products."""
+    from brainstate_b200 import _lib, event
+    from brainstate_b200.event import event_matvec, event_vecmat, pack_spikes
+    n_pre, K, B = 900, 53, 40
+    conn, idx, _, w = make(n_pre, n_post, K, 61, hetero, cuda)
+    spk = np.random.RandomState(62).random_sample((B, n_pre)) < 0.1
+    ts = torch.from_numpy(spk).to(cuda)
+    assert event.PACKED_SLICES
+    y16 = event_vecmat(conn, ts, method='fixed')
+    loc = conn._derived['loc_s']
+    assert loc.dtype == torch.int16 and loc.numel() == conn.nnz
+    s_idx = conn._derived['sliced'][1].cpu().numpy()
+    assert np.array_equal(loc.cpu().numpy().view(np.uint16), (s_idx % 32768).astype(np.uint16))
+    try:
+        event.PACKED_SLICES = False
+        y32 = event_vecmat(conn, ts, method='fixed')
+    finally:
+        event.PACKED_SLICES = True
+    assert torch.equal(y16, y32)
+    ref = np.stack([eo.event_vecmat(s, idx, w, n_post) for s in spk])
+    close(y16, ref, scale=3)
+    # the C entry point itself: float spikes, packed spikes, accumulate
+    st_s = conn._sliced_struct(conn.data)
+    scale = conn._fixed_scale('s', st_s, conn.data)
+    loc, q = conn._packed('s', st_s, conn.data, scale)
+    if hetero:
+        wq = conn._derived['w_s'][1].cpu().numpy()
+        assert np.array_equal(q.cpu().numpy(), np.rint(wq.astype(np.float64) * 2.0 ** scale).astype(np.int32))
+    stream = torch.cuda.current_stream().cuda_stream
+    for t, fmt, batch in ((ts.to(torch.float32) * 3.0, _lib.SPK_F32, B), (pack_spikes(ts), _lib.SPK_BITS32, B)):
+        out = torch.full((B, n_post), 2.0, dtype=torch.float32, device=cuda)
+        _lib.check(bsx.bsx_event_vecmat_sliced16(C.byref(st_s), loc.data_ptr(), None if q is None else q.data_ptr(),
+                                                 t.data_ptr(), fmt, batch, out.data_ptr(), 1, scale, stream))
+        assert torch.equal(out, y32 + 2.0)
+    # the transposed product through the compressed copy of the transposed layout
+    conn2, idx2, _, w2 = make(n_post, n_pre, 7, 63, hetero, cuda)        # (n_post x n_pre): outputs = n_post rows
+    sp2 = np.random.RandomState(64).random_sample((B, n_pre)) < 0.1
+    z16 = event_matvec(conn2, torch.from_numpy(sp2).to(cuda), method='fixed')
+    try:
+        event.PACKED_SLICES = False
+        z32 = event_matvec(conn2, torch.from_numpy(sp2).to(cuda), method='fixed')
+    finally:
+        event.PACKED_SLICES = True
+    assert torch.equal(z16, z32)
+    close(z16, eo.event_matvec(sp2, idx2, w2, n_post), scale=3)
+    # hetero without qweights is refused
+    if hetero:
+        out = torch.empty((B, n_post), dtype=torch.float32, device=cuda)
+        assert bsx.bsx_event_vecmat_sliced16(C.byref(st_s), loc.data_ptr(), None, ts.data_ptr(), _lib.SPK_BOOL8, B,
+                                             out.data_ptr(), 0, scale, stream) == _lib.BSX_ERR_INVALID_ARG
+
+
+def test_bit_packed_spike_delay_feeds_the_event_product(cuda):
+    """Ring of packed spike vectors: what was stored d steps ago comes back bit for bit, as words
+    for the packed-input product and as bools."""
+    from brainstate_b200.nn import SpikeDelay
+    from brainstate_b200.event import event_matvec
+    n, K = 1000, 11
+    conn, idx, _, w = make(300, n, K, 71, True, cuda)
+    d = SpikeDelay(n, entries={'syn': 0.5}, dt=0.1, device=cuda)
+    assert d.max_length == 6
+    d.init_state()
+    rs = np.random.RandomState(72)
+    past = []
+    for t in range(15):
+        spk = rs.random_sample(n) < 0.1
+        past.append(spk)
+        d.update(torch.from_numpy(spk).to(cuda))
+        for k in range(min(len(past), 6)):
+            assert np.array_equal(d.retrieve_at_step(k, bits=False).cpu().numpy(), past[-1 - k])
+            assert np.array_equal(d.retrieve_at_step(k).cpu().numpy().view(np.uint32), eo.pack_bits(past[-1 - k]))
+    y = event_matvec(conn, d.at('syn'), bits=True)
+    close(y, eo.event_matvec(past[-6], idx, w, 300))
+    with pytest.raises(ValueError):
+        d.retrieve_at_step(6)
+    db = SpikeDelay(n, time=2, device=cuda)
+    db.init_state(batch_size=3)
+    s3 = rs.random_sample((3, n)) < 0.2
+    db.update(torch.from_numpy(s3).to(cuda))
+    assert np.array_equal(db.retrieve_at_step(0, bits=False).cpu().numpy(), s3)
