@@ -641,19 +641,24 @@ def run_network(torch, dist, dev, world, rank, name, steps, warm):
     if world > 1 and not hetero:
         # the plain-library form of the same step, for comparison: split-phase launches and one NCCL
         # all-gather of the packed spike words per step (launch-bound; 200 steps)
-        lib_net = from_preset(name, dev, group, exchange='nccl')
-        lib_net.run(20, record=False)
-        torch.cuda.synchronize()
-        dist.barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        lib_net.run(200, record=False)
-        b.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        out['nccl_all_gather_us_per_step'] = float(t.item()) * 1e3 / 200
-        lib_net.close()
+        def time_nccl(overlap, graph_steps):
+            lib_net = from_preset(name, dev, group, exchange='nccl', overlap=overlap, conn=(net.conn_e, net.conn_i))
+            lib_net.run(100, record=False, graph_steps=graph_steps)       # warm-up; captures the graph
+            torch.cuda.synchronize()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            lib_net.run(200, record=False, graph_steps=graph_steps)
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            lib_net.close()
+            return float(t.item()) * 1e3 / 200
+
+        out['nccl_all_gather_us_per_step'] = time_nccl(False, 0)          # eager: bound by the host's launches
+        out['nccl_graph_replay_us_per_step'] = time_nccl(False, 50)       # 50 captured steps per replay
+        out['nccl_graph_replay_overlapped_us_per_step'] = time_nccl(True, 50)   # own-spike scatter during the all-gather
     fixture = dict(np.load(FIXTURE)) if os.path.exists(FIXTURE) else {}
     written = {}
     if hetero:

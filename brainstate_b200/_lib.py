@@ -138,6 +138,8 @@ SIGNATURES = {
     'bsx_net_run': (_i32, [_netp, _lifp, _i32, _i64, _vp, _vp, _i32, _vp]),
     'bsx_net_update': (_i32, [_netp, _lifp, _i64, _vp, _vp]),
     'bsx_net_list_from_bits': (_i32, [_netp, _i64, _vp]),
+    'bsx_net_list_from_bits_part': (_i32, [_netp, _i64, _i64, _i64, _i32, _vp, _vp]),
+    'bsx_net_scatter_part': (_i32, [_netp, _i64, _vp, _i32, _vp]),
     'bsx_net_scatter': (_i32, [_netp, _i64, _vp]),
     'bsx_net_shard_geometry': (_i32, [_i64, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     'bsx_net_inbox_bytes': (_sz, [_i32, _i32, _i32, _i32]),

@@ -63,11 +63,13 @@ __device__ __forceinline__ void scatter_one(const ProjDev& pr, int64_t row, int 
 // Phase A for one list = [count, global ids...]; do_exc / do_inh select which
 // population's rows are taken from it (the two projections may have different delays).
 __device__ __forceinline__ void scatter_list(const NetDev& a, const int32_t* __restrict__ list, bool do_exc,
-                                             bool do_inh, int64_t warp, int64_t nwarps, int lane) {
+                                             bool do_inh, int64_t warp, int64_t nwarps, int lane,
+                                             int64_t from = 0, int64_t to = -1) {
   const int64_t count = list[0];
+  if (to < 0 || to > count) to = count;
   const int cpr = a.exc.cpr > a.inh.cpr ? a.exc.cpr : a.inh.cpr;
-  const int64_t items = count * cpr;
-  for (int64_t it = warp; it < items; it += nwarps) {
+  const int64_t items = to * cpr;
+  for (int64_t it = from * cpr + warp; it < items; it += nwarps) {
     const int64_t q = it / cpr;
     const int c = (int)(it - q * cpr);
     const int64_t id = list[1 + q];
@@ -490,6 +492,26 @@ __global__ void __launch_bounds__(256) net_scatter_kernel(NetDev a, int64_t step
   phase_scatter(a, step, warp, nwarps, lane);
 }
 
+// Phase A restricted to one section of every list: entries [0, mark) (`rest` == 0) or
+// [mark, count) (`rest` != 0), where marks[slot] is the list's length when its first section
+// was complete.  A driver that lists its own spikes first can scatter them while the other
+// ranks' spike words are still on their way.
+__global__ void __launch_bounds__(256)
+net_scatter_part_kernel(NetDev a, int64_t step, const int32_t* __restrict__ marks, int rest) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t te = step - 1 - a.delay_e, ti = step - 1 - a.delay_i;
+  if (te >= 0) {
+    const int64_t mk = marks[te % a.ring];
+    scatter_list(a, a.slot(te), true, te == ti, warp, nwarps, lane, rest ? mk : 0, rest ? -1 : mk);
+  }
+  if (ti >= 0 && ti != te) {
+    const int64_t mk = marks[ti % a.ring];
+    scatter_list(a, a.slot(ti), false, true, warp, nwarps, lane, rest ? mk : 0, rest ? -1 : mk);
+  }
+}
+
 __global__ void __launch_bounds__(256)
 net_update_kernel(NetDev a, int64_t step, int32_t* __restrict__ local_count) {
   const int lane = threadIdx.x & 31;
@@ -515,15 +537,17 @@ net_update_kernel(NetDev a, int64_t step, int32_t* __restrict__ local_count) {
 
 // Compacts the packed spike words of the whole network into a list of global ids.
 __global__ void __launch_bounds__(256)
-net_list_kernel(const uint32_t* __restrict__ bits, int64_t n_global, int32_t* __restrict__ list) {
+net_list_kernel(const uint32_t* __restrict__ bits, int64_t n_global, int32_t* __restrict__ list,
+                int64_t word0 = 0, int64_t word1 = -1, int64_t skip0 = 0, int64_t skip1 = 0) {
   const int lane = threadIdx.x & 31;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
-  const int64_t words = (n_global + 31) >> 5;
-  for (int64_t g0 = tid - lane; g0 < words; g0 += nthreads) {
+  const int64_t all_words = (n_global + 31) >> 5;
+  const int64_t words = word1 < 0 || word1 > all_words ? all_words : word1;
+  for (int64_t g0 = word0 + tid - lane; g0 < words; g0 += nthreads) {
     const int64_t g = g0 + lane;
     uint32_t m = 0;
-    if (g < words) {
+    if (g < words && !(g >= skip0 && g < skip1)) {
       m = bits[g];
       const int64_t left = n_global - g * 32;
       if (left < 32) m &= (1u << left) - 1u;
@@ -695,6 +719,52 @@ int bsx_net_list_from_bits(const bsx_net_t* net, int64_t step, bsx_stream_t stre
   if (blocks < 1) blocks = 1;
   net_list_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(a.bits, a.n_global, list);
   BSX_LAUNCH_CHECK("net_list_kernel");
+  return BSX_OK;
+}
+
+int bsx_net_scatter_part(const bsx_net_t* net, int64_t step, const int32_t* marks, int32_t rest, bsx_stream_t stream) {
+  BSX_TRACE("bsx_net_scatter_part");
+  if (step < 0) return fail(BSX_ERR_INVALID_ARG, "negative step");
+  if (!marks) return fail(BSX_ERR_INVALID_ARG, "marks is NULL");
+  NetDev a;
+  int rc = make_net(net, nullptr, &a);
+  if (rc) return rc;
+  int sms = sm_count();
+  if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  net_scatter_part_kernel<<<(unsigned)(sms * 4), 256, 0, as_stream(stream)>>>(a, step, marks, rest);
+  BSX_LAUNCH_CHECK("net_scatter_part_kernel");
+  return BSX_OK;
+}
+
+int bsx_net_list_from_bits_part(const bsx_net_t* net, int64_t step, int64_t word0, int64_t word1, int32_t rest,
+                                int32_t* marks, bsx_stream_t stream) {
+  BSX_TRACE("bsx_net_list_from_bits_part");
+  if (step < 0) return fail(BSX_ERR_INVALID_ARG, "negative step");
+  NetDev a;
+  int rc = make_net(net, nullptr, &a);
+  if (rc) return rc;
+  const int64_t words = (a.n_global + 31) >> 5;
+  if (word0 < 0 || word1 < word0 || word1 > words) return fail(BSX_ERR_INVALID_ARG, "word range outside the network");
+  if (!rest && !marks) return fail(BSX_ERR_INVALID_ARG, "marks is NULL");
+  int sms = sm_count();
+  if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
+  cudaStream_t st = as_stream(stream);
+  int32_t* list = net->lists + (step % net->ring) * (net->n_global + 1);
+  const int64_t span = rest ? words : word1 - word0;
+  int64_t blocks = (span + 255) / 256;
+  if (blocks > (int64_t)sms * 4) blocks = (int64_t)sms * 4;
+  if (blocks < 1) blocks = 1;
+  if (!rest) {
+    // first section: the words [word0, word1) into an emptied list; its length becomes the mark
+    BSX_CUDA(cudaMemsetAsync(list, 0, sizeof(int32_t), st));
+    net_list_kernel<<<(unsigned)blocks, 256, 0, st>>>(a.bits, a.n_global, list, word0, word1, 0, 0);
+    BSX_LAUNCH_CHECK("net_list_kernel");
+    BSX_CUDA(cudaMemcpyAsync(marks + (step % net->ring), list, sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
+  } else {
+    // second section: every other word, appended
+    net_list_kernel<<<(unsigned)blocks, 256, 0, st>>>(a.bits, a.n_global, list, 0, -1, word0, word1);
+    BSX_LAUNCH_CHECK("net_list_kernel");
+  }
   return BSX_OK;
 }
 

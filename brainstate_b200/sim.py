@@ -215,15 +215,20 @@ class EINet:
         are shared instead of drawn again (a second network over the same synapses).
     shard_kernel : on one GPU, ``True`` runs the kernel of ``exchange='p2p'`` (increment rows,
         one grid-wide barrier per step whatever the delays) instead of the spike-list kernels.
+    overlap : with ``exchange='nccl'``, run the all-gather of a step on the process group's stream
+        while the rank's own spikes are scattered for the next step (default); ``False`` keeps the
+        strictly sequential scatter -> update -> all-gather -> list.
     """
 
     def __init__(self, n_exc: int, n_inh: int, conn_num, w_e, w_i, *, seed_e: int, seed_i: int,
                  V0, params: Optional[LIFParams] = None, device=None, group=None, delay_e: int = 0,
                  delay_i: int = 0, exchange: str = 'p2p', deterministic: bool = False,
-                 slack: Optional[int] = None, shard_kernel: Optional[bool] = None, conn=None):
+                 slack: Optional[int] = None, shard_kernel: Optional[bool] = None, conn=None,
+                 overlap: bool = True):
         if exchange not in ('nccl', 'p2p'):
             raise ValueError("exchange must be 'nccl' or 'p2p'")
         self.exchange = exchange
+        self.overlap = bool(overlap)
         self.deterministic = bool(deterministic)
         self._links = None
         self._seq = 0
@@ -290,6 +295,7 @@ class EINet:
             self._net = None
         else:
             self.lists = torch.zeros((self.ring, self.n + 1), dtype=torch.int32, device=dev)
+            self.marks = torch.zeros(self.ring, dtype=torch.int32, device=dev)
             self._net = self._make_struct()
 
     def _make_struct(self) -> BsxNet:
@@ -317,14 +323,16 @@ class EINet:
         return s
 
     # ------------------------------------------------------------------
-    def run(self, steps: int, record: bool = True, blocks: int = 0):
+    def run(self, steps: int, record: bool = True, blocks: int = 0, graph_steps: int = 0):
         """Advances ``steps`` steps.  Returns ``(raster, counts)``: the packed spike
         words ``(steps, ceil(n/32))`` int32 (``None`` without ``record``) and the
-        number of spikes of every step ``(steps,)`` int32."""
+        number of spikes of every step ``(steps,)`` int32.  ``graph_steps`` (only with
+        ``exchange='nccl'`` on several GPUs): replay chunks of that many steps from a captured
+        CUDA graph."""
         if self.shard_kernel:
             return self._run_shard_kernel(steps, record)
         if self.world > 1:
-            return self._run_sharded(steps, record)
+            return self._run_sharded(steps, record, graph_steps)
         dev = self.dev
         raster = torch.empty((steps, self.words), dtype=torch.int32, device=dev) if record else None
         counts = torch.empty(steps, dtype=torch.int32, device=dev)
@@ -334,18 +342,37 @@ class EINet:
         return raster, counts
 
     def _sharded_step(self, t: int, counts, raster_rows):
-        """Enqueues one step on the current stream: scatter the previous step's spikes
-        (all ranks' spikes, this rank's targets), update the local neurons, all-gather
-        the packed spike words, rebuild the spike list."""
+        """Enqueues one step on the current stream: scatter the delayed spikes (all ranks'
+        spikes, this rank's targets), update the local neurons, all-gather the packed spike
+        words, rebuild the spike list.
+
+        With ``overlap`` the all-gather runs on the process group's own stream while the
+        current stream scatters this rank's OWN spikes of the lists the next step reads (they
+        are known without the exchange: the list's first section, ``marks`` holds its length);
+        the other ranks' section of each list is scattered at the start of the next step.
+        Between steps the increments ``delta_e`` / ``delta_i`` then already hold the own-spike
+        part of the next step's input, which is why a checkpoint records the mode."""
         import torch.distributed as dist
         l = lib()
         stream = _lib.current_stream()
         net, ps = C.byref(self._net), C.byref(self._pstruct)
         step = self.step_count
-        check(l.bsx_net_scatter(net, step, stream))
-        check(l.bsx_net_update(net, ps, step, counts[t:t + 1].data_ptr(), stream))
-        dist.all_gather_into_tensor(self.bits, self._mine, group=self.group)
-        check(l.bsx_net_list_from_bits(net, step, stream))
+        if not self.overlap:
+            check(l.bsx_net_scatter(net, step, stream))
+            check(l.bsx_net_update(net, ps, step, counts[t:t + 1].data_ptr(), stream))
+            dist.all_gather_into_tensor(self.bits, self._mine, group=self.group)
+            check(l.bsx_net_list_from_bits(net, step, stream))
+        else:
+            w0 = self.rank * self.wpr
+            w1 = min(w0 + self.wpr, self.words)
+            marks = self.marks.data_ptr()
+            check(l.bsx_net_scatter_part(net, step, marks, 1, stream))            # the other ranks' spikes
+            check(l.bsx_net_update(net, ps, step, counts[t:t + 1].data_ptr(), stream))
+            check(l.bsx_net_list_from_bits_part(net, step, w0, w1, 0, marks, stream))
+            work = dist.all_gather_into_tensor(self.bits, self._mine, group=self.group, async_op=True)
+            check(l.bsx_net_scatter_part(net, step + 1, marks, 0, stream))        # own spikes, during the exchange
+            work.wait()
+            check(l.bsx_net_list_from_bits_part(net, step, w0, w1, 1, marks, stream))
         if raster_rows is not None:
             raster_rows[t].copy_(self.bits[:self.words])
         self.step_count += 1
@@ -545,12 +572,13 @@ class EINet:
         torch.cuda.synchronize()
 
     # -- checkpoint / resume --------------------------------------------------
-    _STATE = ('V', 'g_e', 'g_i', 'ref', 'delta_e', 'delta_i', 'bits', 'lists', 'incr_e', 'incr_i')
+    _STATE = ('V', 'g_e', 'g_i', 'ref', 'delta_e', 'delta_i', 'bits', 'lists', 'marks', 'incr_e', 'incr_i')
 
     def _meta(self) -> dict:
         return {'n_exc': self.n_exc, 'n_inh': self.n_inh, 'conn_num': self.conn_num, 'ring': self.ring,
                 'first': self.first, 'n_local': self.n_local, 'shard_kernel': self.shard_kernel,
-                'deterministic': self.deterministic}
+                'deterministic': self.deterministic,
+                'own_spikes_scattered_ahead': bool(self.world > 1 and not self.shard_kernel and self.overlap)}
 
     def state_dict(self) -> dict:
         """Everything a resumed run needs that cannot be regenerated: the rank's neuron

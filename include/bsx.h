@@ -422,6 +422,16 @@ int bsx_net_scatter(const bsx_net_t* net, int64_t step, bsx_stream_t stream);
 int bsx_net_update(const bsx_net_t* net, const bsx_lif_params_t* params, int64_t step, int32_t* local_count,
                    bsx_stream_t stream);
 int bsx_net_list_from_bits(const bsx_net_t* net, int64_t step, bsx_stream_t stream);
+/* The same pieces for a driver that overlaps the exchange with the scatter of the rank's own
+ * spikes.  bsx_net_list_from_bits_part with rest == 0 empties list step % ring, lists the words
+ * [word0, word1) of `bits` (the rank's own words, valid before the exchange) and stores the list's
+ * length in marks[step % ring] (device memory, `ring` entries); with rest != 0 it appends all words
+ * outside [word0, word1) (after the exchange).  bsx_net_scatter_part scatters, of every list that
+ * bsx_net_scatter(step) would read, the entries before its mark (rest == 0) or from its mark on
+ * (rest != 0); the two calls together equal bsx_net_scatter(step). */
+int bsx_net_list_from_bits_part(const bsx_net_t* net, int64_t step, int64_t word0, int64_t word1, int32_t rest,
+                                int32_t* marks, bsx_stream_t stream);
+int bsx_net_scatter_part(const bsx_net_t* net, int64_t step, const int32_t* marks, int32_t rest, bsx_stream_t stream);
 /*
  * One rank's shard of an E/I network for bsx_net_run_sharded.  Neurons and projections
  * as in bsx_net_t (the rank owns neurons [first, first + n_local) and the synapses that

@@ -45,7 +45,8 @@ def _small_net(dev, group, coba, exchange='p2p', delay_e=1, delay_i=0, **kw):
 def _rank_main(rank, world, port, steps, coba, exchange, delays, slack, out_dir):
     dev, dist = _init(rank, world, port)
     try:
-        net = _small_net(dev, dist.group.WORLD, coba, exchange, delays[0], delays[1], slack=slack)
+        kw = {'overlap': False} if exchange == 'nccl-serial' else {}
+        net = _small_net(dev, dist.group.WORLD, coba, exchange.split('-')[0], delays[0], delays[1], slack=slack, **kw)
         r1, c1 = net.run(steps // 2)
         r2, c2 = net.run(steps - steps // 2)
         raster, counts = torch.cat([r1, r2]), torch.cat([c1, c2])
@@ -59,12 +60,14 @@ def _rank_main(rank, world, port, steps, coba, exchange, delays, slack, out_dir)
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize('exchange,delays,slack', [('nccl', (1, 0), None), ('p2p', (1, 0), None), ('p2p', (0, 0), None),
+@pytest.mark.parametrize('exchange,delays,slack', [('nccl', (1, 0), None), ('nccl', (0, 0), None), ('nccl', (3, 2), None),
+                                                   ('nccl-serial', (1, 0), None), ('p2p', (1, 0), None), ('p2p', (0, 0), None),
                                                    ('p2p', (3, 2), None), ('p2p', (3, 2), 0), ('p2p', (3, 2), 1)])
 @pytest.mark.parametrize('coba', [False, True])
 def test_sharded_network_equals_single_gpu(coba, exchange, delays, slack, tmp_path):
     """In-kernel exchange with and without slack (spikes consumed `slack` steps after they
-    were pushed; default = the smaller delay), and the NCCL all-gather path."""
+    were pushed; default = the smaller delay), and the NCCL all-gather path with the own-spike
+    scatter overlapping the all-gather (default) or strictly in sequence ('nccl-serial')."""
     if torch.cuda.device_count() < 2:
         pytest.skip('needs at least two GPUs')
     import torch.multiprocessing as mp
