@@ -216,15 +216,17 @@ class EINet:
     shard_kernel : on one GPU, ``True`` runs the kernel of ``exchange='p2p'`` (increment rows,
         one grid-wide barrier per step whatever the delays) instead of the spike-list kernels.
     overlap : with ``exchange='nccl'``, run the all-gather of a step on the process group's stream
-        while the rank's own spikes are scattered for the next step (default); ``False`` keeps the
-        strictly sequential scatter -> update -> all-gather -> list.
+        while the rank's own spikes are scattered for the next step, instead of the strictly
+        sequential scatter -> update -> all-gather -> list.  It doubles the launches per step, so it
+        pays only when the steps are replayed from a CUDA graph (``run(..., graph_steps=)``:
+        32 against 36 us per step on two GPUs at 10^6 neurons; eager 69 against 41).
     """
 
     def __init__(self, n_exc: int, n_inh: int, conn_num, w_e, w_i, *, seed_e: int, seed_i: int,
                  V0, params: Optional[LIFParams] = None, device=None, group=None, delay_e: int = 0,
                  delay_i: int = 0, exchange: str = 'p2p', deterministic: bool = False,
                  slack: Optional[int] = None, shard_kernel: Optional[bool] = None, conn=None,
-                 overlap: bool = True):
+                 overlap: bool = False):
         if exchange not in ('nccl', 'p2p'):
             raise ValueError("exchange must be 'nccl' or 'p2p'")
         self.exchange = exchange

@@ -45,7 +45,7 @@ def _small_net(dev, group, coba, exchange='p2p', delay_e=1, delay_i=0, **kw):
 def _rank_main(rank, world, port, steps, coba, exchange, delays, slack, out_dir):
     dev, dist = _init(rank, world, port)
     try:
-        kw = {'overlap': False} if exchange == 'nccl-serial' else {}
+        kw = {'overlap': True} if exchange == 'nccl-overlap' else {}
         net = _small_net(dev, dist.group.WORLD, coba, exchange.split('-')[0], delays[0], delays[1], slack=slack, **kw)
         r1, c1 = net.run(steps // 2)
         r2, c2 = net.run(steps - steps // 2)
@@ -60,14 +60,14 @@ def _rank_main(rank, world, port, steps, coba, exchange, delays, slack, out_dir)
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize('exchange,delays,slack', [('nccl', (1, 0), None), ('nccl', (0, 0), None), ('nccl', (3, 2), None),
-                                                   ('nccl-serial', (1, 0), None), ('p2p', (1, 0), None), ('p2p', (0, 0), None),
+@pytest.mark.parametrize('exchange,delays,slack', [('nccl', (1, 0), None), ('nccl-overlap', (1, 0), None), ('nccl-overlap', (0, 0), None),
+                                                   ('nccl-overlap', (3, 2), None), ('p2p', (1, 0), None), ('p2p', (0, 0), None),
                                                    ('p2p', (3, 2), None), ('p2p', (3, 2), 0), ('p2p', (3, 2), 1)])
 @pytest.mark.parametrize('coba', [False, True])
 def test_sharded_network_equals_single_gpu(coba, exchange, delays, slack, tmp_path):
     """In-kernel exchange with and without slack (spikes consumed `slack` steps after they
     were pushed; default = the smaller delay), and the NCCL all-gather path with the own-spike
-    scatter overlapping the all-gather (default) or strictly in sequence ('nccl-serial')."""
+    scatter strictly in sequence with the all-gather, or overlapping it ('nccl-overlap')."""
     if torch.cuda.device_count() < 2:
         pytest.skip('needs at least two GPUs')
     import torch.multiprocessing as mp
@@ -173,11 +173,11 @@ def test_restoring_an_earlier_checkpoint_on_two_gpus(tmp_path):
     assert torch.equal(raster.cpu(), got['raster'])
 
 
-def _rank_graph(rank, world, port, out_dir):
+def _rank_graph(rank, world, port, overlap, out_dir):
     dev, dist = _init(rank, world, port)
     try:
-        net = _small_net(dev, dist.group.WORLD, False, 'nccl', 2, 0)
-        raster, counts = net._run_sharded(120, True, graph_steps=24)      # ring of 4 lists: 24 steps per replay
+        net = _small_net(dev, dist.group.WORLD, False, 'nccl', 2, 0, overlap=overlap)
+        raster, counts = net.run(120, graph_steps=24)                     # ring of 4 lists: 24 steps per replay
         torch.cuda.synchronize()
         if rank == 0:
             torch.save({'raster': raster.cpu(), 'counts': counts.cpu()}, os.path.join(out_dir, 'graph.pt'))
@@ -187,14 +187,16 @@ def _rank_graph(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
-def test_graph_replay_of_the_all_gather_path_equals_eager(tmp_path):
+@pytest.mark.parametrize('overlap', [False, True])
+def test_graph_replay_of_the_all_gather_path_equals_eager(overlap, tmp_path):
     """Replaying captured split-phase steps (the launches carry their step number by value)
     gives the eager raster: the capture starts only after every delayed list exists, and a
-    network with a background drive refuses it."""
+    network with a background drive refuses it.  With ``overlap`` the captured all-gather runs
+    on the process group's stream beside the scatter of the rank's own spikes."""
     if torch.cuda.device_count() < 2:
         pytest.skip('needs at least two GPUs')
     import torch.multiprocessing as mp
-    mp.spawn(_rank_graph, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_rank_graph, args=(2, _free_port(), overlap, str(tmp_path)), nprocs=2, join=True)
     got = torch.load(tmp_path / 'graph.pt')
     raster, counts = _small_net('cuda:0', None, False, delay_e=2, delay_i=0).run(120)
     assert int(counts.sum()) > 50
