@@ -222,8 +222,10 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
     __syncthreads();
     // ---- warps take listed rows one at a time
     for (;;) {
+      // (compressed layout, one weight: a group costs 12 registers, so a warp takes two at a time)
+      constexpr int kTake = (SLICED && PACKED && !HETERO) ? 2 : 1;
       int t = 0;
-      if (lane == 0) t = atomicAdd(&s_next, 1);
+      if (lane == 0) t = atomicAdd(&s_next, kTake);
       t = __shfl_sync(0xffffffffu, t, 0);
       if (t >= total) break;
       const int64_t row = list[t];
@@ -235,6 +237,26 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
         const uint16_t* __restrict__ gl = reinterpret_cast<const uint16_t*>(idx) + s;
         const int32_t* __restrict__ gq = reinterpret_cast<const int32_t*>(w) + s;
         const int len = row_len[t];
+        if (!HETERO) {
+          const bool two = t + 1 < total;
+          const uint16_t* __restrict__ gl2 = reinterpret_cast<const uint16_t*>(idx) + (two ? row_start[t + 1] : s);
+          const int len2 = two ? row_len[t + 1] : 0;
+          const int top = len > len2 ? len : len2;
+          for (int p0 = lane; p0 < top; p0 += 32 * kSsDeal) {
+            uint32_t cc[kSsDeal], c2[kSsDeal];
+#pragma unroll
+            for (int u = 0; u < kSsDeal; ++u) {
+              cc[u] = p0 + 32 * u < len ? (uint32_t)__ldg(gl + p0 + 32 * u) : 0xffffu;
+              c2[u] = p0 + 32 * u < len2 ? (uint32_t)__ldg(gl2 + p0 + 32 * u) : 0xffffu;
+            }
+#pragma unroll
+            for (int u = 0; u < kSsDeal; ++u) {
+              smem_count_if(sbase, cc[u], ncol);
+              smem_count_if(sbase, c2[u], ncol);
+            }
+          }
+          continue;
+        }
         for (int p0 = lane; p0 < len; p0 += 32 * kSsDeal) {
           uint32_t cc[kSsDeal];
           int32_t q[kSsDeal];
@@ -242,13 +264,10 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
           for (int u = 0; u < kSsDeal; ++u) {
             const bool in = p0 + 32 * u < len;
             cc[u] = in ? (uint32_t)__ldg(gl + p0 + 32 * u) : 0xffffu;
-            q[u] = (HETERO && in) ? __ldg(gq + p0 + 32 * u) : 0;
+            q[u] = in ? __ldg(gq + p0 + 32 * u) : 0;
           }
 #pragma unroll
-          for (int u = 0; u < kSsDeal; ++u) {
-            if (HETERO) smem_red_s32_if(sbase, cc[u], ncol, q[u]);
-            else smem_count_if(sbase, cc[u], ncol);
-          }
+          for (int u = 0; u < kSsDeal; ++u) smem_red_s32_if(sbase, cc[u], ncol, q[u]);
         }
         continue;
       }
