@@ -89,6 +89,15 @@ def test_argument_validation_needs_no_gpu(bsx):
     assert b'64-bit' in bsx.bsx_last_error_string()
     assert bsx.bsx_event_vecmat_variant(C.byref(st), 9, 4) == BSX_ERR_INVALID_ARG
     assert bsx.bsx_event_vecmat_variant(C.byref(st), 0, 4) in (0, 1)
+    # compressed form of the sliced layout
+    assert bsx.bsx_event_vecmat_sliced16(C.byref(st), None, None, None, 0, 1, None, 0, 0, None) == BSX_ERR_INVALID_ARG
+    assert b'64-bit' in bsx.bsx_last_error_string()
+    assert bsx.bsx_event_vecmat_sliced16(C.byref(st), None, None, None, 0, 1, None, 0, 31, None) == BSX_ERR_INVALID_ARG
+    assert bsx.bsx_quantize_f32(None, 8, 3, None, None) == BSX_ERR_INVALID_ARG
+    assert b'NULL' in bsx.bsx_last_error_string()
+    assert bsx.bsx_quantize_f32(None, 0, 3, None, None) == 0             # nothing to do
+    assert bsx.bsx_quantize_f32(C.addressof(dummy), 8, 40, C.addressof(dummy), None) == BSX_ERR_INVALID_ARG
+    assert b'scale_log2' in bsx.bsx_last_error_string()
 
 
 def test_no_cpu_fallback(bsx):
