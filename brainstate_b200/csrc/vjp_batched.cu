@@ -67,6 +67,18 @@ vjp_dx_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* _
   const int half = lane >> 4, quad = lane & 15;
   const int64_t wstep = (int64_t)gridDim.x * (blockDim.x >> 5);
   for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < n_pre; row += wstep) {
+    // the index and weight lines of the warp's next row go to L2 now (rows of a fixed length: their
+    // place is known without a load): every 32-synapse stretch below starts with a load of them
+    if (!rm.p64 && !rm.p32 && row + wstep < n_pre) {
+      const char* fi = reinterpret_cast<const char*>(idx + (row + wstep) * rm.K);
+      const char* li = fi - (reinterpret_cast<uintptr_t>(fi) & 127) + 128 * lane;
+      if (li < fi + rm.K * 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(li));
+      if (HETERO) {
+        const char* fw = reinterpret_cast<const char*>(w + (row + wstep) * rm.K);
+        const char* lw = fw - (reinterpret_cast<uintptr_t>(fw) & 127) + 128 * lane;
+        if (lw < fw + rm.K * 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(lw));
+      }
+    }
     int64_t s, e;
     rm.range(row, s, e);
     float acc_e = 0.f, acc_o = 0.f;
@@ -153,6 +165,13 @@ vjp_dw_batched_kernel(RowMap rm, const int32_t* __restrict__ idx, const void* __
   float homo_acc = 0.f;
   const int64_t wstep = (int64_t)gridDim.x * (blockDim.x >> 5);
   for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < n_pre; row += wstep) {
+    // the index lines of the warp's next row go to L2 now (rows of a fixed length: their place is
+    // known without a load), so that the row's first loads do not wait for DRAM
+    if (!rm.p64 && !rm.p32 && row + wstep < n_pre) {
+      const char* first = reinterpret_cast<const char*>(idx + (row + wstep) * rm.K);
+      const char* line = first - (reinterpret_cast<uintptr_t>(first) & 127) + 128 * lane;
+      if (line < first + rm.K * 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+    }
     const float a_lo = has_lo ? act_at<XFORMAT>(x, blo * n_pre + row, event) : 0.f;
     const float a_hi = has_hi ? act_at<XFORMAT>(x, bhi * n_pre + row, event) : 0.f;
     const uint32_t act_lo = __ballot_sync(0xffffffffu, a_lo != 0.f);
