@@ -656,9 +656,15 @@ def run_network(torch, dist, dev, world, rank, name, steps, warm):
             lib_net.close()
             return float(t.item()) * 1e3 / 200
 
-        out['nccl_all_gather_us_per_step'] = time_nccl(False, 0)          # eager: bound by the host's launches
-        out['nccl_graph_replay_us_per_step'] = time_nccl(False, 50)       # 50 captured steps per replay
-        out['nccl_graph_replay_overlapped_us_per_step'] = time_nccl(True, 50)   # own-spike scatter during the all-gather
+        # (a comparison beside the measurement: a failure here is recorded, it does not end the run)
+        for key, overlap, graph_steps in (('nccl_all_gather_us_per_step', False, 0),             # eager: bound by the host's launches
+                                          ('nccl_graph_replay_us_per_step', False, 50),          # 50 captured steps per replay
+                                          ('nccl_graph_replay_overlapped_us_per_step', True, 50)):  # own-spike scatter during the all-gather
+            try:
+                out[key] = time_nccl(overlap, graph_steps)
+            except Exception as exc:        # noqa: BLE001
+                out[key] = None
+                out.setdefault('nccl_errors', []).append(f'{key}: {type(exc).__name__}: {exc}'[:200])
     fixture = dict(np.load(FIXTURE)) if os.path.exists(FIXTURE) else {}
     written = {}
     if hetero:
