@@ -638,6 +638,15 @@ def run_network(torch, dist, dev, world, rank, name, steps, warm):
                      else 'net_run_sharded_kernel (state in global memory)',
            'exchange': 'spike-id lists pushed by peer stores inside the step kernel' if world > 1 else 'none (one GPU)',
            'accumulation': 'float32 atomics'}
+    # algorithmic bytes of the whole network per step: neuron state (4 words read + 4 written per
+    # neuron), the packed spike words, 4 (+4 with per-synapse weights) bytes per synaptic event;
+    # against the HBM peak of the N GPUs together (state kept in shared memory moves none of these
+    # bytes through HBM: the figure says how the step compares with a kernel that streams its state)
+    alg = n * 32 + n / 8 + (spikes / steps) * K * (8 if hetero else 4)
+    peak_gbs, _ = measured_hbm_peak()
+    out['algorithmic_bytes_per_step'] = alg
+    out['algorithmic_GBps'] = alg / (ms * 1e-3 / steps) / 1e9
+    out['frac_of_hbm_peak_all_gpus'] = out['algorithmic_GBps'] / (peak_gbs * world)
     if world > 1 and not hetero:
         # the plain-library form of the same step, for comparison: split-phase launches and one NCCL
         # all-gather of the packed spike words per step (launch-bound; 200 steps)
