@@ -183,6 +183,28 @@ def build_projection(seed: int, n_pre: int, n_post: int, conn_num: int, weight, 
     return CSR((float(weight), idx, indptr), shape=(n_pre, n_cols))
 
 
+def build_projection_in_degree(seed: int, n_pre: int, n_post: int, k_in: int, weight, device, row0: int = 0,
+                               row1: Optional[int] = None):
+    """One projection with a fixed IN-degree: every postsynaptic neuron draws ``k_in`` presynaptic
+    partners, ``RandomState(seed).randint(0, n_pre, (n_post, k_in))`` — the same generator call as
+    ``brainstate/nn/_event_fixedprob.py:165-171`` with the roles exchanged.  ``[row0, row1)`` selects
+    the postsynaptic shard (its rows of the one seeded stream).  The step kernels scatter along
+    presynaptic rows, so the result is the presynaptic-major CSR copy (built on the device by
+    ``bsx_transpose_build``), local column ids.  Homogeneous weights only."""
+    if not isinstance(weight, (int, float)):
+        raise NotImplementedError('fixed in-degree projections take one weight per projection')
+    row1 = n_post if row1 is None else row1
+    n_local = row1 - row0
+    buf = np.empty(max(n_local * k_in, 1), np.int32)
+    n = lib().bsx_host_fixed_num_indices(C.c_uint32(int(seed) & 0xffffffff), n_post, n_pre, k_in, row0, row1, 0, 0,
+                                        buf.ctypes.data, None)
+    check(int(n))
+    idx_in = torch.from_numpy(buf[:n_local * k_in].reshape(n_local, k_in)).to(device)
+    mirror = FixedPostNumConn((float(weight), idx_in), shape=(n_local, n_pre))     # rows: local postsynaptic neurons
+    t = mirror.transposed()
+    return CSR((float(weight), t.indices, t.indptr), shape=(n_pre, n_local))
+
+
 class EINet:
     """E/I network of LIF neurons with exponential synapses.
 
@@ -215,6 +237,9 @@ class EINet:
         are shared instead of drawn again (a second network over the same synapses).
     shard_kernel : on one GPU, ``True`` runs the kernel of ``exchange='p2p'`` (increment rows,
         one grid-wide barrier per step whatever the delays) instead of the spike-list kernels.
+    degree : ``'out'`` — every neuron has ``conn_num`` targets (the reference's ``efferent_target='post'``
+        layout); ``'in'`` — every neuron has ``conn_num`` presynaptic partners, ``conn_num * n_exc / n`` of
+        them excitatory (fixed in-degree; homogeneous weights).
     overlap : with ``exchange='nccl'``, run the all-gather of a step on the process group's stream
         while the rank's own spikes are scattered for the next step, instead of the strictly
         sequential scatter -> update -> all-gather -> list.  It doubles the launches per step, so it
@@ -226,7 +251,7 @@ class EINet:
                  V0, params: Optional[LIFParams] = None, device=None, group=None, delay_e: int = 0,
                  delay_i: int = 0, exchange: str = 'p2p', deterministic: bool = False,
                  slack: Optional[int] = None, shard_kernel: Optional[bool] = None, conn=None,
-                 overlap: bool = False):
+                 overlap: bool = False, degree: str = 'out'):
         if exchange not in ('nccl', 'p2p'):
             raise ValueError("exchange must be 'nccl' or 'p2p'")
         self.exchange = exchange
@@ -252,10 +277,18 @@ class EINet:
         self.conn_num = K
         dev = self.dev
         hetero = isinstance(w_e, Lognormal) or isinstance(w_i, Lognormal)
+        if degree not in ('out', 'in'):
+            raise ValueError("degree must be 'out' or 'in'")
+        self.degree = degree
         if conn is not None:
             self.conn_e, self.conn_i = conn
             if self.conn_e.shape != (self.n_exc, self.n_local) or self.conn_i.shape != (self.n_inh, self.n_local):
                 raise ValueError('conn: projections of another network or shard')
+        elif degree == 'in':
+            k_e = int(round(K * self.n_exc / self.n))
+            self.in_degree = (k_e, K - k_e)                 # presynaptic partners per neuron: excitatory, inhibitory
+            self.conn_e = build_projection_in_degree(seed_e, self.n_exc, self.n, k_e, w_e, dev, self.first, self.last)
+            self.conn_i = build_projection_in_degree(seed_i, self.n_inh, self.n, K - k_e, w_i, dev, self.first, self.last)
         elif self.world == 1 and not hetero and self.n * K < (1 << 31):
             self.E = EventFixedProb(self.n_exc, self.n, K, float(w_e), seed=seed_e, device=dev)
             self.I = EventFixedProb(self.n_inh, self.n, K, float(w_i), seed=seed_i, device=dev)
@@ -579,7 +612,7 @@ class EINet:
     def _meta(self) -> dict:
         return {'n_exc': self.n_exc, 'n_inh': self.n_inh, 'conn_num': self.conn_num, 'ring': self.ring,
                 'first': self.first, 'n_local': self.n_local, 'shard_kernel': self.shard_kernel,
-                'deterministic': self.deterministic,
+                'deterministic': self.deterministic, 'degree': self.degree,
                 'own_spikes_scattered_ahead': bool(self.world > 1 and not self.shard_kernel and self.overlap)}
 
     def state_dict(self) -> dict:

@@ -42,11 +42,16 @@ def _small_net(dev, group, coba, exchange='p2p', delay_e=1, delay_i=0, **kw):
                  device=dev, group=group, exchange=exchange, delay_e=delay_e, delay_i=delay_i, **kw)
 
 
+def _variant(exchange):
+    """Constructor keywords of the test variants named after the exchange."""
+    return {'nccl-overlap': {'overlap': True}, 'p2p-indegree': {'degree': 'in'}}.get(exchange, {})
+
+
 def _rank_main(rank, world, port, steps, coba, exchange, delays, slack, out_dir):
     dev, dist = _init(rank, world, port)
     try:
-        kw = {'overlap': True} if exchange == 'nccl-overlap' else {}
-        net = _small_net(dev, dist.group.WORLD, coba, exchange.split('-')[0], delays[0], delays[1], slack=slack, **kw)
+        net = _small_net(dev, dist.group.WORLD, coba, exchange.split('-')[0], delays[0], delays[1], slack=slack,
+                         **_variant(exchange))
         r1, c1 = net.run(steps // 2)
         r2, c2 = net.run(steps - steps // 2)
         raster, counts = torch.cat([r1, r2]), torch.cat([c1, c2])
@@ -62,12 +67,14 @@ def _rank_main(rank, world, port, steps, coba, exchange, delays, slack, out_dir)
 
 @pytest.mark.parametrize('exchange,delays,slack', [('nccl', (1, 0), None), ('nccl-overlap', (1, 0), None), ('nccl-overlap', (0, 0), None),
                                                    ('nccl-overlap', (3, 2), None), ('p2p', (1, 0), None), ('p2p', (0, 0), None),
-                                                   ('p2p', (3, 2), None), ('p2p', (3, 2), 0), ('p2p', (3, 2), 1)])
+                                                   ('p2p', (3, 2), None), ('p2p', (3, 2), 0), ('p2p', (3, 2), 1),
+                                                   ('p2p-indegree', (1, 0), None)])
 @pytest.mark.parametrize('coba', [False, True])
 def test_sharded_network_equals_single_gpu(coba, exchange, delays, slack, tmp_path):
     """In-kernel exchange with and without slack (spikes consumed `slack` steps after they
     were pushed; default = the smaller delay), and the NCCL all-gather path with the own-spike
-    scatter strictly in sequence with the all-gather, or overlapping it ('nccl-overlap')."""
+    scatter strictly in sequence with the all-gather, or overlapping it ('nccl-overlap'); 'p2p-indegree':
+    every neuron draws its presynaptic partners, each rank its own rows of the one seeded stream."""
     if torch.cuda.device_count() < 2:
         pytest.skip('needs at least two GPUs')
     import torch.multiprocessing as mp
@@ -76,7 +83,8 @@ def test_sharded_network_equals_single_gpu(coba, exchange, delays, slack, tmp_pa
     mp.spawn(_rank_main, args=(world, _free_port(), steps, coba, exchange, delays, slack, str(tmp_path)), nprocs=world,
              join=True)
     got = torch.load(tmp_path / 'sharded.pt')
-    net = _small_net('cuda:0', None, coba, delay_e=delays[0], delay_i=delays[1])
+    net = _small_net('cuda:0', None, coba, delay_e=delays[0], delay_i=delays[1],
+                     **{k: v for k, v in _variant(exchange).items() if k == 'degree'})
     raster, counts = net.run(steps)
     assert int(counts.sum()) > 50
     assert torch.equal(raster.cpu(), got['raster'])

@@ -436,3 +436,43 @@ def test_state_resident_in_shared_memory_equals_oracle_and_global_state_kernel(c
         assert torch.equal(x, y)
     np.testing.assert_allclose(a.V.cpu().numpy(), orc.V, rtol=1e-5, atol=1e-6)
     assert np.array_equal(a.ref.cpu().numpy(), orc.ref)
+
+
+def _in_degree_csr(seed, n_pre, n_post, k_in):
+    """Presynaptic-major CSR of ``RandomState(seed).randint(0, n_pre, (n_post, k_in))`` in NumPy."""
+    idx_in = np.random.RandomState(seed).randint(0, n_pre, size=(n_post, k_in))
+    flat = idx_in.reshape(-1)
+    order = np.argsort(flat, kind='stable')
+    posts = (order // k_in).astype(np.int32)
+    indptr = np.zeros(n_pre + 1, np.int64)
+    np.cumsum(np.bincount(flat, minlength=n_pre), out=indptr[1:])
+    return posts, indptr, idx_in
+
+
+@pytest.mark.parametrize('coba,shard_kernel', [(False, False), (True, True)])
+def test_fixed_in_degree_network_matches_oracle(coba, shard_kernel, cuda):
+    """Every neuron draws its presynaptic partners (64 excitatory + 16 inhibitory of 80) instead of its
+    targets; the step kernels run over the presynaptic-major copy built on the device.  Rasters
+    equal the oracle's over the same connectivity built in NumPy."""
+    from brainstate_b200.sim import EINet, LIFParams, unpack_raster
+    n_exc, n_inh, K = 3200, 800, 80
+    n = n_exc + n_inh
+    w_e, w_i, R = (0.6, 6.7, 0.1) if coba else (1.62, -9.0, 1.0)
+    V0 = np.random.RandomState(102).uniform(-60, -50, n).astype(np.float32)
+    net = EINet(n_exc, n_inh, K, w_e, w_i, seed_e=100, seed_i=101, V0=V0, params=LIFParams(coba=coba, R=R),
+                device=cuda, degree='in', shard_kernel=shard_kernel)
+    assert net.in_degree == (64, 16)
+    pe, ipe, raw_e = _in_degree_csr(100, n_exc, n, 64)
+    pi, ipi, _ = _in_degree_csr(101, n_inh, n, 16)
+    # the device copy holds the same synapses: every neuron has exactly 64 excitatory partners
+    assert int(net.conn_e.indptr[-1]) == n * 64
+    assert np.array_equal(np.bincount(net.conn_e.indices.cpu().numpy(), minlength=n), np.full(n, 64))
+    assert np.array_equal(net.conn_e.indptr.cpu().numpy(), ipe)
+    orc = eo.EINetOracle(n_exc, n_inh, pe, np.float32(w_e), pi, np.float32(w_i), coba=coba, V0=V0, R=R,
+                         indptr_e=ipe, indptr_i=ipi)
+    steps = 250
+    raster, counts = net.run(steps)
+    ref = orc.run(steps)
+    assert ref.sum() > 100
+    assert np.array_equal(counts.cpu().numpy(), ref.sum(axis=1))
+    assert np.array_equal(unpack_raster(raster, n), ref)
