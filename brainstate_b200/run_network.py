@@ -36,6 +36,8 @@ def main():
     ap.add_argument('--shard-kernel', action='store_true',
                     help='one GPU: run the kernel the sharded runs use (increment rows, one barrier per step)')
     ap.add_argument('--deterministic', action='store_true', help='fixed-point synaptic sums: order-free rasters')
+    ap.add_argument('--degree', default='out', choices=['out', 'in'],
+                    help="'in': every neuron draws its presynaptic partners (fixed in-degree) instead of its targets")
     ap.add_argument('--record', action='store_true', help='keep the bit-packed raster (memory: steps * n / 8 bytes)')
     args = ap.parse_args()
 
@@ -62,7 +64,8 @@ def main():
     t0 = time.perf_counter()
     net = EINet(n_exc, n_inh, K, p['w_e'], p['w_i'], seed_e=p['seed_e'], seed_i=p['seed_i'], V0=V0, params=params,
                 device=dev, group=dist.group.WORLD if world > 1 else None, exchange=args.exchange,
-                deterministic=args.deterministic, shard_kernel=True if args.shard_kernel else None)
+                deterministic=args.deterministic, shard_kernel=True if args.shard_kernel else None,
+                degree=args.degree)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
     mem_gb = torch.cuda.max_memory_allocated(dev) / 1e9
@@ -81,7 +84,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     spikes = int(counts.sum().item())
-    out = {'preset': args.preset, 'n_gpus': world, 'neurons': n, 'targets_per_neuron': K, 'synapses': n * K,
+    out = {'preset': args.preset, 'n_gpus': world, 'neurons': n, 'targets_per_neuron': K, 'degree': args.degree,
+           'synapses': n * K,
            'steps': args.steps, 'warmup': args.warmup, 'exchange': args.exchange if world > 1 else 'none',
            'build_s': build_s, 'device_memory_gb_rank0': mem_gb, 'ms_total': ms,
            'us_per_step': ms * 1e3 / args.steps, 'spikes': spikes,
