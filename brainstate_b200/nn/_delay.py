@@ -29,6 +29,30 @@ _NEAREST = ('nearest', 'round')
 _LINEAR = ('linear', 'linear_interp')
 
 
+def _tap_weights(method: str, t: float):
+    """Weights of the ring slots ``floor(f) + (-1, 0, 1, 2)`` for a fractional slot position
+    ``f = floor(f) + t`` (a larger slot position is a more recent sample), for the four
+    higher-order methods of ``brainstate/nn/_delay.py:193-350``: Catmull-Rom spline, cubic
+    Hermite with central-difference tangents, and the Lagrange polynomials through 3 and 4
+    neighbouring samples."""
+    t2, t3 = t * t, t * t * t
+    if method == 'cubic':
+        return (-0.5 * t3 + t2 - 0.5 * t, 1.5 * t3 - 2.5 * t2 + 1.0, -1.5 * t3 + 2.0 * t2 + 0.5 * t, 0.5 * t3 - 0.5 * t2)
+    if method == 'hermite':
+        h00, h10, h01, h11 = 2 * t3 - 3 * t2 + 1, t3 - 2 * t2 + t, -2 * t3 + 3 * t2, t3 - t2
+        # value = h00 v0 + h10 (v1 - v-1)/2 + h01 v1 + h11 (v2 - v0)/2
+        return (-0.5 * h10, h00 - 0.5 * h11, h01 + 0.5 * h10, 0.5 * h11)
+    if method == 'polynomial2':
+        return (0.5 * t * (t - 1), (1 - t) * (1 + t), 0.5 * t * (t + 1), 0.0)
+    if method == 'polynomial3':
+        return (-t * (t - 1) * (t - 2) / 6, (t + 1) * (t - 1) * (t - 2) / 2, -t * (t + 1) * (t - 2) / 2,
+                t * (t + 1) * (t - 1) / 6)
+    raise ValueError(method)
+
+
+_HIGHER = ('cubic', 'hermite', 'polynomial2', 'polynomial3')
+
+
 def _delay_steps(time, dt: float):
     """``ceil(time / dt)`` as the reference's ``_get_delay`` (``_delay.py:351-360``), whose ceiling is
     taken in float32 (so 0.3 / 0.1 and 0.9 / 0.3 give 3, not 3 and 4); tensors give tensors."""
@@ -53,7 +77,9 @@ class Delay(Module):
         ``init_state``).
     init : number, tensor or ``callable(shape, dtype=..., device=...)`` filling the history before t0.
     entries : ``{name: delay_time}`` or ``{name: (delay_time, *indices)}``.
-    interpolation : ``'nearest'`` (``'round'``) or ``'linear'`` for ``retrieve_at_time``.
+    interpolation : for ``retrieve_at_time``: ``'nearest'`` (``'round'``), ``'linear'``, ``'cubic'``,
+        ``'hermite'``, ``'polynomial2'``, ``'polynomial3'``, or a callable
+        ``f(history, indices, float_slot, max_length)`` as the reference's registry takes.
     update_every : write a slot only every that much time (a multiple of ``dt``); ``update`` is
         still called every step.
     """
@@ -62,9 +88,12 @@ class Delay(Module):
                  interpolation: str = 'linear', update_every: Optional[float] = None, *, dt: float = 1.0,
                  name: Optional[str] = None):
         super().__init__(name=name)
-        if interpolation not in _NEAREST + _LINEAR:
-            raise ValueError(f'Unknown interpolation method: {interpolation}. Available methods: '
-                             f'{list(_NEAREST + _LINEAR)}')
+        if isinstance(interpolation, str):
+            if interpolation not in _NEAREST + _LINEAR + _HIGHER:
+                raise ValueError(f'Unknown interpolation method: {interpolation}. Available methods: '
+                                 f'{list(_NEAREST + _LINEAR + _HIGHER)}')
+        elif not callable(interpolation):
+            raise TypeError(f'interpolation must be str or callable, got {type(interpolation)}')
         if init is not None and not isinstance(init, (int, float, torch.Tensor)) and not callable(init):
             raise TypeError(f'init should be Array, Callable, or None. But got {init}')
         self.dt = float(dt)
@@ -175,6 +204,17 @@ class Delay(Module):
             raise ValueError(f'The request delay time should be within '
                              f'[{current_time - self.max_time - self.dt}, {current_time}], but we got {delay_time}')
         f = (current_time - delay_time) / self._slot_dt
+        if callable(self.interp_method) or self.interp_method in _HIGHER:
+            slot = (self.write_ptr - 1) // self.update_every_step - f        # fractional position in the ring
+            if callable(self.interp_method):
+                return self.interp_method(self.history, tuple(indices), slot, self.max_length)
+            i0 = math.floor(slot)
+            out = None
+            for k, wk in zip((-1, 0, 1, 2), _tap_weights(self.interp_method, slot - i0)):
+                if wk != 0.0:
+                    term = self.history[((i0 + k) % self.max_length,) + tuple(indices)] * wk
+                    out = term if out is None else out + term
+            return out
         if self.interp_method in _NEAREST:
             return self.retrieve_at_step(int(round(f)), *indices)
         lo, hi = int(math.floor(f + 1e-12)), int(math.ceil(f - 1e-12))

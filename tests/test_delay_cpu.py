@@ -90,3 +90,50 @@ def test_state_with_delay_reads_the_target_state():
         c.V.value = torch.full((3,), float(t))
         d.update()
     assert torch.equal(d.retrieve_at_step(2), torch.full((3,), 1.0))
+
+
+def _filled(method, fn, length=12, dt=0.5):
+    d = Delay(torch.zeros(2, dtype=torch.float64), time=(length - 1) * dt, dt=dt, interpolation=method)
+    d.init_state()
+    for k in range(length):                                   # sample k holds fn(k * dt)
+        d.update(torch.tensor([fn(k * dt), 2 * fn(k * dt)], dtype=torch.float64))
+    return d, (length - 1) * dt
+
+
+@pytest.mark.parametrize('method', ['cubic', 'hermite', 'polynomial2', 'polynomial3'])
+def test_higher_order_interpolation(method):
+    """Each method reproduces the polynomials it must: all four are exact on straight lines, the 3- and
+    4-point Lagrange forms on parabolas, the 4-point form on cubics; Catmull-Rom and the Hermite form
+    with central-difference tangents are the same spline."""
+    line = lambda t: 3.0 - 2.0 * t
+    para = lambda t: 1.0 + t - 0.5 * t * t
+    cube = lambda t: 0.25 * t ** 3 - t + 2.0
+    for t_query in (2.1, 3.25, 3.5, 4.9):
+        d, now = _filled(method, line)
+        assert torch.allclose(d.retrieve_at_time(t_query, now), torch.tensor([line(t_query), 2 * line(t_query)], dtype=torch.float64))
+        if method.startswith('polynomial'):
+            d, now = _filled(method, para)
+            assert torch.allclose(d.retrieve_at_time(t_query, now)[0], torch.tensor(para(t_query), dtype=torch.float64))
+        if method == 'polynomial3':
+            d, now = _filled(method, cube)
+            assert torch.allclose(d.retrieve_at_time(t_query, now)[0], torch.tensor(cube(t_query), dtype=torch.float64))
+    a, now = _filled('cubic', cube)
+    b, _ = _filled('hermite', cube)
+    assert torch.allclose(a.retrieve_at_time(3.3, now), b.retrieve_at_time(3.3, now))
+    # at a sample every method returns the sample
+    assert torch.allclose(a.retrieve_at_time(3.0, now)[0], torch.tensor(cube(3.0), dtype=torch.float64))
+
+
+def test_custom_interpolation_callable():
+    seen = {}
+
+    def pick(history, indices, slot, max_length):
+        seen['slot'] = slot
+        return history[(int(round(slot)) % max_length,) + indices]
+    d = Delay(torch.zeros(1), time=3.0, dt=1.0, interpolation=pick)
+    d.init_state()
+    for k in range(4):
+        d.update(torch.tensor([float(k)]))
+    assert d.retrieve_at_time(1.0, 3.0).item() == 1.0 and seen['slot'] % 4 == 1.0       # the ring position, up to whole turns
+    with pytest.raises(TypeError, match='str or callable'):
+        Delay(torch.zeros(1), interpolation=3)
