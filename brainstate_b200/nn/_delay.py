@@ -3,8 +3,8 @@
 ``Delay`` follows ``brainstate.nn.Delay`` (``brainstate/nn/_delay.py:399-958``): a ring of
 ``max_length = ceil(max delay / dt) + 1`` past values with a write pointer that counts
 ``update`` calls, named entries, retrieval by step (``:768-817``: slot
-``(write_ptr - 1 - delay_step) mod max_length``), retrieval by time with nearest or linear
-interpolation (``:819-901``), per-element delays through index arguments, and a slower write
+``(write_ptr - 1 - delay_step) mod max_length``), retrieval by time with nearest, linear, cubic,
+Hermite or Lagrange interpolation (``:163-350,819-901``), per-element delays through index arguments, and a slower write
 cadence (``update_every``, ``:903-958``).  Values are CUDA tensors; time is a plain float in the
 unit of ``dt`` (physical units are not modelled).
 
