@@ -130,8 +130,14 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
   __shared__ int32_t warp_tot[kSsWarps];
   __shared__ int32_t s_next;
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-  const int64_t b = blockIdx.y;
-  const int32_t col0 = (int32_t)blockIdx.x * kSsSlice;
+  // Over the sliced layout the blocks of one slice are neighbours in launch order (grid x = spike
+  // vector, y = slice): the blocks resident together then read groups of the same half of the
+  // matrix, whose working set (about 130 MB at 65 536 x 655) the L2 nearly holds, so the rows that
+  // several vectors share are found there.  Over unsliced rows both blocks of a vector read the same
+  // rows, so there the two slices of a vector are neighbours (x = slice, y = spike vector).
+  const int64_t b = SLICED ? blockIdx.x : blockIdx.y;
+  const int slice_id = SLICED ? (int)blockIdx.y : (int)blockIdx.x;
+  const int32_t col0 = (int32_t)slice_id * kSsSlice;
   const uint32_t ncol = (uint32_t)((n_post - col0) < kSsSlice ? (n_post - col0) : kSsSlice);
   for (int i = tid; i < kSsSlice / 4; i += kSsThreads) reinterpret_cast<float4*>(acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   const float w0 = HETERO ? 1.0f : __ldg(w);
@@ -215,7 +221,7 @@ scatter_smem_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __r
     for (int t = tid; t < total; t += kSsThreads) {
       const int64_t row = list[t];
       int64_t s, e;
-      rm.range(SLICED ? row * row_mul + blockIdx.x : row, s, e);
+      rm.range(SLICED ? row * row_mul + slice_id : row, s, e);
       row_start[t] = s;
       row_len[t] = (int32_t)(e - s);
     }
@@ -498,7 +504,7 @@ static int launch_scatter_smem_fixed(const bsx_conn_t* conn, const void* spikes,
                                      int accumulate, cudaStream_t st, int row_mul, int scale_log2) {
   if (sm_count() <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
   const int64_t slices = (conn->n_post + kSsSlice - 1) / kSsSlice;
-  const dim3 grid((unsigned)slices, (unsigned)batch, 1);
+  const dim3 grid((unsigned)batch, (unsigned)slices, 1);      // sliced layout: x = spike vector, y = slice
   const size_t smem = sizeof(float) * kSsSlice + (sizeof(int64_t) + 2 * sizeof(int32_t)) * kSsList;
   const bool vec_ok = aligned16(conn->indices) && aligned16(conn->weights);
   const RowMap rm = make_rowmap(conn);
@@ -525,7 +531,7 @@ static int launch_scatter_smem_packed(const bsx_conn_t* conn, const uint16_t* lo
                                       cudaStream_t st, int row_mul, int scale_log2) {
   if (sm_count() <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
   const int64_t slices = (conn->n_post + kSsSlice - 1) / kSsSlice;
-  const dim3 grid((unsigned)slices, (unsigned)batch, 1);
+  const dim3 grid((unsigned)batch, (unsigned)slices, 1);      // sliced layout: x = spike vector, y = slice
   const size_t smem = sizeof(float) * kSsSlice + (sizeof(int64_t) + 2 * sizeof(int32_t)) * kSsList;
   const RowMap rm = make_rowmap(conn);
   const float scale = ldexpf(1.0f, scale_log2), inv_scale = ldexpf(1.0f, -scale_log2);
@@ -597,7 +603,8 @@ int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, 
                         float* out, int accumulate, cudaStream_t st, int row_mul) {
   if (sm_count() <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
   const int64_t slices = (conn->n_post + kSsSlice - 1) / kSsSlice;
-  const dim3 grid((unsigned)slices, (unsigned)batch, 1);
+  const dim3 grid = row_mul >= 1 ? dim3((unsigned)batch, (unsigned)slices, 1)       // sliced: x = spike vector, y = slice
+                                 : dim3((unsigned)slices, (unsigned)batch, 1);
   const size_t smem = sizeof(float) * kSsSlice + (sizeof(int64_t) + 2 * sizeof(int32_t)) * kSsList;
   const bool vec_ok = aligned16(conn->indices) && (!conn->hetero || aligned16(conn->weights));
   const RowMap rm = make_rowmap(conn);
