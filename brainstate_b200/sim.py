@@ -98,6 +98,8 @@ def sharded_block(seed: int, n_pre: int, n_post: int, conn_num: int, col0: int, 
     """CSR block (host arrays) of the fixed-number matrix ``RandomState(seed).randint(0,
     n_post, (n_pre, conn_num))`` restricted to targets in ``[col0, col1)``; column
     ids are local (minus ``col0``).  Returns ``(indices int32, indptr int64)``."""
+    if col1 <= col0:        # an empty shard (more ranks than spike words); an empty column range would mean "no filter"
+        return np.empty(0, np.int32), np.zeros(n_pre + 1, np.int64)
     buf = np.empty(n_pre * conn_num, np.int32)
     counts = np.empty(n_pre, np.int32)
     n = lib().bsx_host_fixed_num_indices(C.c_uint32(int(seed) & 0xffffffff), n_pre, n_post, conn_num, 0, n_pre,
@@ -131,6 +133,12 @@ def build_projection(seed: int, n_pre: int, n_post: int, conn_num: int, weight, 
     """
     l = lib()
     col1 = n_post if col1 is None else col1
+    if col1 <= col0:        # an empty shard (more ranks than spike words): no synapse targets it
+        if isinstance(weight, Lognormal):
+            return CSR((torch.empty(0, dtype=torch.float32, device=device), torch.empty(0, dtype=torch.int32, device=device),
+                        torch.zeros(n_pre + 1, dtype=torch.int64, device=device)), shape=(n_pre, 0))
+        return CSR((float(weight), torch.empty(0, dtype=torch.int32, device=device),
+                    torch.zeros(n_pre + 1, dtype=torch.int64, device=device)), shape=(n_pre, 0))
     filtered = not (col0 == 0 and col1 == n_post)
     if chunk_rows is None:
         chunk_rows = max(1, (1 << 26) // max(conn_num, 1))          # 64 Mi entries per chunk

@@ -166,14 +166,16 @@ def _rank_lists(rank, world, port, steps, delays, slack, cuts, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize('delays,slack', [((0, 0), 0), ((1, 2), 1), ((3, 2), 2), ((3, 2), 0)])
-def test_id_list_exchange_with_increment_ring_and_slack(delays, slack, tmp_path, bsx):
+@pytest.mark.parametrize('delays,slack,world', [((0, 0), 0, 2), ((1, 2), 1, 2), ((3, 2), 2, 2), ((3, 2), 0, 2),
+                                                ((1, 2), 1, 8)])
+def test_id_list_exchange_with_increment_ring_and_slack(delays, slack, world, tmp_path, bsx):
     """The protocol of the sharded step kernel (spike-id lists instead of packed words, delays by
     the row a spike is added to, lists consumed `slack` steps late, drained at launch ends) gives
-    the unsharded oracle's raster on two gloo ranks."""
+    the unsharded oracle's raster on two gloo ranks, and on eight (13 spike words over 8 ranks: the
+    last shards are short or empty)."""
     cuts = (1, 40, 2, 77)
     steps = sum(cuts)
-    mp.spawn(_rank_lists, args=(2, _free_port(), steps, delays, slack, cuts, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_rank_lists, args=(world, _free_port(), steps, delays, slack, cuts, str(tmp_path)), nprocs=world, join=True)
     got = np.load(tmp_path / 'raster_lists.npy')
     n_exc, n_inh, K = 320, 96, 12
     n = n_exc + n_inh
