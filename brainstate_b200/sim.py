@@ -110,6 +110,26 @@ def sharded_block(seed: int, n_pre: int, n_post: int, conn_num: int, col0: int, 
     return buf[:n].copy(), indptr
 
 
+class PeerLost(RuntimeError):
+    """A rank of the network did not answer the host-side roll call before a launch."""
+
+
+def wait_for_peers(health_group, timeout_s: float = 5.0) -> None:
+    """Roll call of the ranks on the host, before a launch whose kernels wait for one another:
+    every rank must answer within ``timeout_s`` (``torch.distributed.monitored_barrier`` on a
+    ``gloo`` group over the same ranks).  A rank that has exited, hangs or is later than that
+    raises :class:`PeerLost` on the others — on the host, with no kernel in flight — instead
+    of a device-side wait running out.  The reference has no counterpart (a single-process
+    library)."""
+    import datetime
+    import torch.distributed as dist
+    try:
+        dist.monitored_barrier(group=health_group, timeout=datetime.timedelta(seconds=float(timeout_s)),
+                               wait_all_ranks=True)
+    except RuntimeError as exc:
+        raise PeerLost(f'a rank did not answer within {timeout_s} s: {exc}') from exc
+
+
 @dataclass
 class Lognormal:
     """Heterogeneous weights ``scale * exp(mu + sigma * z)``, ``z`` standard normal keyed by
@@ -248,6 +268,9 @@ class EINet:
     degree : ``'out'`` — every neuron has ``conn_num`` targets (the reference's ``efferent_target='post'``
         layout); ``'in'`` — every neuron has ``conn_num`` presynaptic partners, ``conn_num * n_exc / n`` of
         them excitatory (fixed in-degree; homogeneous weights).
+    health_group, health_timeout : a ``gloo`` process group over the same ranks and a patience in
+        seconds: every ``run`` on several GPUs starts with :func:`wait_for_peers`, so a lost or late
+        rank is noticed on the host (``PeerLost``) before anything is launched.
     overlap : with ``exchange='nccl'``, run the all-gather of a step on the process group's stream
         while the rank's own spikes are scattered for the next step, instead of the strictly
         sequential scatter -> update -> all-gather -> list.  It doubles the launches per step, so it
@@ -259,11 +282,12 @@ class EINet:
                  V0, params: Optional[LIFParams] = None, device=None, group=None, delay_e: int = 0,
                  delay_i: int = 0, exchange: str = 'p2p', deterministic: bool = False,
                  slack: Optional[int] = None, shard_kernel: Optional[bool] = None, conn=None,
-                 overlap: bool = False, degree: str = 'out'):
+                 overlap: bool = False, degree: str = 'out', health_group=None, health_timeout: float = 5.0):
         if exchange not in ('nccl', 'p2p'):
             raise ValueError("exchange must be 'nccl' or 'p2p'")
         self.exchange = exchange
         self.overlap = bool(overlap)
+        self.health_group, self.health_timeout = health_group, float(health_timeout)
         self.deterministic = bool(deterministic)
         self._links = None
         self._seq = 0
@@ -372,6 +396,8 @@ class EINet:
         number of spikes of every step ``(steps,)`` int32.  ``graph_steps`` (only with
         ``exchange='nccl'`` on several GPUs): replay chunks of that many steps from a captured
         CUDA graph."""
+        if self.world > 1 and self.health_group is not None:
+            wait_for_peers(self.health_group, self.health_timeout)
         if self.shard_kernel:
             return self._run_shard_kernel(steps, record)
         if self.world > 1:

@@ -185,3 +185,52 @@ def test_id_list_exchange_with_increment_ring_and_slack(delays, slack, world, tm
                          delay_e=delays[0], delay_i=delays[1]).run(steps)
     assert ref.sum() > 20
     assert np.array_equal(got, ref)
+
+
+def _rank_roll_call(rank, world, port, scenario, out_dir):
+    """Host-side failure detection, with no GPU involved: ``lost`` — the last rank leaves between two
+    runs and never answers again; ``late`` — it answers late but within the patience."""
+    import time
+    from brainstate_b200.sim import PeerLost, wait_for_peers
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    result = 'ok'
+    wait_for_peers(dist.group.WORLD, 10.0)                   # everybody is there
+    if scenario == 'lost' and rank == world - 1:
+        os._exit(0)                                          # gone between steps, without a goodbye
+    if scenario == 'late' and rank == world - 1:
+        time.sleep(1.0)
+    t0 = time.monotonic()
+    try:
+        wait_for_peers(dist.group.WORLD, 4.0)
+    except PeerLost as exc:
+        result = f'lost after {time.monotonic() - t0:.1f} s: {exc}'
+    with open(os.path.join(out_dir, f'rank{rank}.txt'), 'w') as f:
+        f.write(result)
+    os._exit(0)                                              # no collective shutdown with a dead peer
+
+
+@pytest.mark.parametrize('scenario', ['lost', 'late'])
+def test_lost_and_late_ranks_are_noticed_on_the_host(scenario, tmp_path):
+    """Before a launch whose kernels wait for one another the ranks call the roll on the host: a rank
+    that left between two runs raises ``PeerLost`` on the others within the patience (no kernel is
+    in flight, no GPU is involved); a rank that is merely late passes."""
+    world = 3
+    ctx = mp.get_context('spawn')
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_roll_call, args=(r, world, port, scenario, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    survivors = range(world - 1) if scenario == 'lost' else range(world)
+    for r in survivors:
+        text = (tmp_path / f'rank{r}.txt').read_text()
+        if scenario == 'lost':
+            assert text.startswith('lost after') and float(text.split()[2]) < 20.0, text
+        else:
+            assert text == 'ok', text
+    if scenario == 'lost':
+        assert 'Ranks 2' in (tmp_path / 'rank0.txt').read_text()             # rank 0 names the missing rank
