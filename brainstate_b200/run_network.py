@@ -91,6 +91,9 @@ def main():
            'us_per_step': ms * 1e3 / args.steps, 'spikes': spikes,
            'mean_rate_hz': spikes / n / (args.steps * params.dt * 1e-3),
            'synaptic_events_per_s': spikes * K / (ms * 1e-3)}
+    if args.record and raster is not None and rank == 0:       # per-population rates need the raster
+        from brainstate_b200.sim import population_rates
+        out['rate_exc_hz'], out['rate_inh_hz'] = population_rates(raster, n_exc, n_inh, params.dt)
     net.close()
     if rank == 0:
         print(json.dumps(out), flush=True)
