@@ -9,9 +9,13 @@
 // touching any of them, and add the entries that fall into the slice with shared-memory
 // atomics — about four times the rate of red.global.add.f32.  The slice is written to
 // global memory once, coalesced: no workspace, no separate clearing of the output.
-// With n_post = 65 536 two blocks share a batch row and each reads every active row;
-// the two are neighbours in launch order, so the second read is served by L2.  Beyond
-// four slices the re-reading outweighs any gain.  Like every atomic scatter, the
+// With n_post = 65 536 two blocks share a batch row.  Over the original rows each of them reads
+// every active row (the two are neighbours in launch order, so the second read is served by
+// L2); over the sliced copy (rows regrouped by slice, bsx_sliced_build) each reads only its own
+// groups, the blocks of one slice are launched together, and every warp prefetches into L2 the
+// group that is handed out one round later.  The compressed form of the sliced copy stores
+// 16-bit column offsets inside the slice and the weights in fixed point.  Beyond four slices
+// the re-reading outweighs any gain.  Like every atomic scatter, the
 // summation order of heterogeneous weights is not fixed.  With homogeneous weights and
 // an event input every event adds the same value, so the slice holds integer hit counts
 // (native integer atomics, no compare-and-swap loop) and every output is count * weight,
