@@ -335,7 +335,7 @@ def run_ours(args):
     if world > 1:
         import datetime
         # a rank that fails must not keep the others waiting for the default ten minutes
-        dist.init_process_group('nccl', device_id=dev, timeout=datetime.timedelta(seconds=180))
+        dist.init_process_group('nccl', device_id=dev, timeout=datetime.timedelta(seconds=420))
 
     from brainstate_b200 import _lib
     from brainstate_b200.nn import EventFixedProb
