@@ -797,8 +797,23 @@ def run_single_vector(torch, dev, dp, peak, calls=64):
     homo = FixedPostNumConn((0.1, dp.ti), shape=(n, n))
     ws_bytes = lib.bsx_event_vecmat_workspace_bytes(1, n)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-    y = torch.empty((calls, n), dtype=torch.float32, device=dev)
+    y = torch.empty((calls + 1, n), dtype=torch.float32, device=dev)
     out = []
+
+    def replayed(burst):
+        burst()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                burst()
+        torch.cuda.current_stream().wait_stream(side)
+        sec = _time(torch, g.replay, reps=10) / calls
+        del g
+        return sec
+
     for r_id, rate in enumerate((0.001, 0.01, 0.1)):
         spk = np.random.RandomState(230 + r_id).random_sample((calls, n)) < rate
         sd = torch.from_numpy(spk).to(dev)
@@ -813,21 +828,27 @@ def run_single_vector(torch, dev, dp, peak, calls=64):
                     _lib.check(lib.bsx_event_vecmat(C.byref(st), sd.data_ptr() + c * n, _lib.SPK_BOOL8, 1,
                                                     y.data_ptr() + 4 * c * n, 0, ws.data_ptr(), ws_bytes, stream))
 
-            burst()
-            torch.cuda.synchronize()
-            side = torch.cuda.Stream(device=dev)
-            side.wait_stream(torch.cuda.current_stream())
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(side):
-                with torch.cuda.graph(g, stream=side):
-                    burst()
-            torch.cuda.current_stream().wait_stream(side)
-            sec = _time(torch, g.replay, reps=10) / calls
+            def chained():
+                # one launch per call: every call adds into its own output row and clears the next call's
+                # (row 0 is cleared by the last call of the previous replay: the chain closes on itself)
+                stream = torch.cuda.current_stream().cuda_stream
+                for c in range(calls):
+                    nxt = (c + 1) % calls
+                    _lib.check(lib.bsx_event_vecmat_chained(C.byref(st), sd.data_ptr() + c * n, _lib.SPK_BOOL8, 1,
+                                                            y.data_ptr() + 4 * c * n, y.data_ptr() + 4 * nxt * n, stream))
+
+            sec = replayed(burst)
+            ref_rows = y[:calls].clone()
+            y[0].zero_()
+            sec_chained = replayed(chained)
+            if h == 0:      # identical addends: the chained calls give the same bits as the plain ones
+                g_check = y[1:calls]                       # row 0 was cleared again by the last call of the chain
+                assert torch.equal(g_check, ref_rows[1:calls]), 'chained single-vector calls differ from the plain calls'
             alg = events * (4 + 4 * h) + n + 4 * n
             out.append({'rate': rate, 'weights': name, 'us_per_call': sec * 1e6, 'events_per_s': events / sec,
                         'algorithmic_GBps': alg / sec / 1e9, 'frac': alg / sec / 1e9 / peak,
-                        'launches_per_call': int(lib.bsx_event_vecmat_launches(C.byref(st), _lib.SPK_BOOL8, 1))})
-            del g
+                        'launches_per_call': int(lib.bsx_event_vecmat_launches(C.byref(st), _lib.SPK_BOOL8, 1)),
+                        'us_per_call_chained': sec_chained * 1e6, 'frac_chained': alg / sec_chained / 1e9 / peak})
     return out
 
 

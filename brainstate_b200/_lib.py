@@ -120,6 +120,7 @@ SIGNATURES = {
     'bsx_fixed_scale_workspace_bytes': (_sz, [_i64]),
     'bsx_fixed_scale_log2': (_i32, [_connp, _vp, _sz, C.POINTER(C.c_int32), _vp]),
     'bsx_event_vecmat_sliced_fixed': (_i32, [_connp, _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
+    'bsx_event_vecmat_chained': (_i32, [_connp, _vp, _i32, _i64, _vp, _vp, _vp]),
     'bsx_sliced_compress': (_i32, [_connp, _vp, _vp]),
     'bsx_quantize_f32': (_i32, [_vp, _i64, _i32, _vp, _vp]),
     'bsx_event_vecmat_sliced16': (_i32, [_connp, _vp, _vp, _vp, _i32, _i64, _vp, _i32, _i32, _vp]),

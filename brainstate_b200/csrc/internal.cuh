@@ -30,7 +30,7 @@ int launch_scatter_smem(const bsx_conn_t* conn, const void* spikes, int format, 
 bool scatter_fused_applies(const bsx_conn_t* conn, const void* spikes, int format, int64_t batch);
 bool scatter_fused_fits(const bsx_conn_t* conn, int format, int64_t batch);
 int launch_scatter_fused(const bsx_conn_t* conn, const void* spikes, int format, const float* x, int64_t batch,
-                         float* out, int accumulate, cudaStream_t st);
+                         float* out, int accumulate, cudaStream_t st, float* clear_next = nullptr);
 
 // (B, n) row-major -> (n, Bp) row-major, zero padded to Bp (a multiple of 32) columns (vjp_batched.cu).
 int launch_transpose_pad(const float* src, int64_t B, int64_t n, int64_t Bp, float* dst, cudaStream_t st);

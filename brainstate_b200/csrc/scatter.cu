@@ -184,6 +184,27 @@ int bsx_event_vecmat_variant(const bsx_conn_t* conn, int spike_format, int64_t b
   return scatter_smem_preferred(conn, spike_format, batch) ? BSX_VECMAT_SHARED_SLICES : BSX_VECMAT_GLOBAL_ATOMICS;
 }
 
+int bsx_event_vecmat_chained(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
+                             float* out, float* next_out, bsx_stream_t stream) {
+  BSX_TRACE("bsx_event_vecmat_chained");
+  const int rc = check_conn(conn);
+  if (rc) return rc;
+  if (batch < 0) return fail(BSX_ERR_INVALID_ARG, "negative batch");
+  if (spike_format != BSX_SPK_BOOL8 && spike_format != BSX_SPK_F32 && spike_format != BSX_SPK_BITS32 &&
+      spike_format != BSX_SPK_LIST)
+    return fail(BSX_ERR_INVALID_ARG, "unknown spike format");
+  if (batch == 0 || conn->n_post == 0) return BSX_OK;
+  if (!out) return fail(BSX_ERR_INVALID_ARG, "out is NULL");
+  if (next_out == out) return fail(BSX_ERR_INVALID_ARG, "next_out must be another buffer than out");
+  cudaStream_t st = as_stream(stream);
+  const bool empty = conn->n_pre == 0 || (!conn->indptr && conn->conn_num == 0);
+  if (empty) return next_out ? launch_zero(next_out, batch * conn->n_post, st) : BSX_OK;
+  if (!spikes) return fail(BSX_ERR_INVALID_ARG, "input vector is NULL");
+  if (!scatter_fused_applies(conn, spikes, spike_format, batch))
+    return fail(BSX_ERR_UNSUPPORTED, "the chained call takes up to 128 KB of 16-byte aligned spike input");
+  return launch_scatter_fused(conn, spikes, spike_format, nullptr, batch, out, /*accumulate=*/1, st, next_out);
+}
+
 int bsx_event_vecmat_launches(const bsx_conn_t* conn, int spike_format, int64_t batch) {
   const int v = bsx_event_vecmat_variant(conn, spike_format, batch);
   if (v < 0) return v;

@@ -32,8 +32,10 @@ __device__ __forceinline__ uint4 load_chunk(const unsigned char* __restrict__ p,
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-__device__ __forceinline__ uint32_t byte_flags(uint32_t v) {   // bit k: byte k of v is nonzero
-  return ((v & 0xffu) ? 1u : 0u) | ((v & 0xff00u) ? 2u : 0u) | ((v & 0xff0000u) ? 4u : 0u) | ((v & 0xff000000u) ? 8u : 0u);
+// bit k: byte k of v is nonzero.  One SIMD compare gives 0x01 per nonzero byte; the multiplication
+// adds byte i shifted to bit i of the top byte (1*b0 + 2*b1 + 4*b2 + 8*b3; no carries: at most 15).
+__device__ __forceinline__ uint32_t byte_flags(uint32_t v) {
+  return ((__vcmpne4(v, 0u) & 0x01010101u) * 0x01020408u) >> 24;
 }
 
 // Active spikes of one chunk as up to four (mask, flat index of bit 0) pairs.
@@ -93,18 +95,34 @@ __global__ void __launch_bounds__(kFuThreads, 1)
 scatter_fused_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __restrict__ w,
                      const unsigned char* __restrict__ spikes, int64_t spike_bytes, const float* __restrict__ x,
                      float* __restrict__ out, int64_t n_pre, int64_t n_post, int64_t batch, int chunks_per_row,
-                     int chunk, bool vec_ok) {
+                     int chunk, bool vec_ok, float* __restrict__ clear_next = nullptr, int64_t clear_count = 0) {
   __shared__ uint32_t s_list[kFuList];
   __shared__ uint32_t s_warp[kFuWarps];
   __shared__ uint32_t s_total;
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int64_t gwarp = (int64_t)blockIdx.x * kFuWarps + wid;
   const int64_t gwarps = (int64_t)gridDim.x * kFuWarps;
+  // ---- 0. a caller that alternates between output buffers has this launch clear the one the
+  // next launch adds into, which saves the separate clearing node of every call
+  if (clear_next) {
+    const int64_t gt = (int64_t)blockIdx.x * kFuThreads + tid, gn = (int64_t)gridDim.x * kFuThreads;
+    if ((reinterpret_cast<uintptr_t>(clear_next) & 15) == 0) {
+      float4* c4 = reinterpret_cast<float4*>(clear_next);
+      for (int64_t i = gt; i < (clear_count >> 2); i += gn) c4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int64_t i = (clear_count & ~int64_t(3)) + gt; i < clear_count; i += gn) clear_next[i] = 0.f;
+    } else {
+      for (int64_t i = gt; i < clear_count; i += gn) clear_next[i] = 0.f;
+    }
+  }
   // ---- 1. the list of active rows (every block builds the same one) ----
   const uint32_t* entries = s_list;
   uint32_t total = 0;
   uint32_t my_off = 0;
   const int64_t words = (n_pre + 31) >> 5;
+  // byte and float inputs: a chunk's spikes are one mask of 16 or 4 bits, kept in a register from
+  // the count pass to the list pass (packed words are four masks per chunk: they are read again)
+  constexpr bool KEEP = FORMAT == BSX_SPK_BOOL8 || FORMAT == BSX_SPK_F32;
+  uint32_t mk[kFuLoads];
   if (FORMAT == BSX_SPK_LIST) {
     const int32_t* list = reinterpret_cast<const int32_t*>(spikes);
     total = (uint32_t)__ldg(list);
@@ -116,11 +134,13 @@ scatter_fused_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __
 #pragma unroll
     for (int j = 0; j < kFuLoads; ++j) {
       const int64_t c = (int64_t)j * kFuThreads + tid;
+      mk[j] = 0;
       if (c * 16 < spike_bytes) {
         uint32_t m[4];
         int64_t base[4];
         chunk_masks<FORMAT>(v[j], c, n_pre, words, m, base);
         cnt += __popc(m[0]) + __popc(m[1]) + __popc(m[2]) + __popc(m[3]);
+        if (KEEP) mk[j] = m[0];
       }
     }
     uint32_t incl = cnt;
@@ -162,14 +182,21 @@ scatter_fused_kernel(RowMap rm, const int32_t* __restrict__ idx, const float* __
       if (r > 0) __syncthreads();                             // the previous round's list has been consumed
       uint32_t pos = my_off;
       uint4 v[kFuLoads];
-      load_my_chunks(spikes, spike_bytes, tid, v);              // L1/L2 hits: the count pass just read them
+      if (!KEEP) load_my_chunks(spikes, spike_bytes, tid, v);   // L1/L2 hits: the count pass just read them
 #pragma unroll
       for (int j = 0; j < kFuLoads; ++j) {
         const int64_t c = (int64_t)j * kFuThreads + tid;
         if (c * 16 < spike_bytes) {
           uint32_t m[4];
           int64_t base[4];
-          chunk_masks<FORMAT>(v[j], c, n_pre, words, m, base);
+          if (KEEP) {
+            m[0] = mk[j];
+            base[0] = c * (FORMAT == BSX_SPK_BOOL8 ? 16 : 4);
+            m[1] = m[2] = m[3] = 0;
+            base[1] = base[2] = base[3] = 0;
+          } else {
+            chunk_masks<FORMAT>(v[j], c, n_pre, words, m, base);
+          }
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             uint32_t mm = m[u];
@@ -224,7 +251,7 @@ bool scatter_fused_applies(const bsx_conn_t* conn, const void* spikes, int forma
 }
 
 int launch_scatter_fused(const bsx_conn_t* conn, const void* spikes, int format, const float* x, int64_t batch,
-                         float* out, int accumulate, cudaStream_t st) {
+                         float* out, int accumulate, cudaStream_t st, float* clear_next) {
   const int sms = sm_count();
   if (sms <= 0) return fail(BSX_ERR_CUDA, "no CUDA device");
   int chunk = 128, cpr = 1;
@@ -247,7 +274,8 @@ int launch_scatter_fused(const bsx_conn_t* conn, const void* spikes, int format,
   const unsigned grid = (unsigned)sms;
 #define BSX_FUSED(H, X, F)                                                                                       \
   scatter_fused_kernel<H, X, F><<<grid, kFuThreads, 0, st>>>(rm, conn->indices, conn->weights, sp, spike_bytes, x, out, \
-                                                             conn->n_pre, conn->n_post, batch, cpr, chunk, vec_ok)
+                                                             conn->n_pre, conn->n_post, batch, cpr, chunk, vec_ok, \
+                                                             clear_next, clear_next ? batch * conn->n_post : 0)
 #define BSX_FUSED_FMT(H, X)                                        \
   switch (format) {                                                \
     case BSX_SPK_BOOL8: BSX_FUSED(H, X, BSX_SPK_BOOL8); break;     \

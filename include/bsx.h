@@ -237,6 +237,18 @@ int bsx_event_vecmat_sliced_fixed(const bsx_conn_t* sliced, const void* spikes, 
                                   float* out, int accumulate, int32_t scale_log2, bsx_stream_t stream);
 
 /*
+ * The per-step call of a simulation loop without its clearing node.  No counterpart in the
+ * reference.  For spike inputs of up to 128 KB (16-byte aligned) bsx_event_vecmat runs a memset
+ * node and one kernel; a loop that alternates between two output buffers can fold the clearing
+ * into the kernel: bsx_event_vecmat_chained ADDS the product to `out` (which the previous call of
+ * the chain, or the caller before the first one, has cleared) and clears `next_out` (batch * n_post
+ * floats, another buffer than `out`; NULL: nothing is cleared) for the call that follows — one
+ * launch per call, no workspace.  Larger inputs answer BSX_ERR_UNSUPPORTED.
+ */
+int bsx_event_vecmat_chained(const bsx_conn_t* conn, const void* spikes, int spike_format, int64_t batch,
+                             float* out, float* next_out, bsx_stream_t stream);
+
+/*
  * Compressed form of the sliced layout (index compression; no counterpart in the reference).
  * Inside a group every column lies in one 32 768-column slice, so 16 bits hold it:
  * bsx_sliced_compress writes local[p] = indices[p] - 32768 * slice (0xffff for a column outside

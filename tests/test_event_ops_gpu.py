@@ -958,3 +958,42 @@ def test_bit_packed_spike_delay_feeds_the_event_product(cuda):
     s3 = rs.random_sample((3, n)) < 0.2
     db.update(torch.from_numpy(s3).to(cuda))
     assert np.array_equal(db.retrieve_at_step(0, bits=False).cpu().numpy(), s3)
+
+
+@pytest.mark.parametrize('hetero', [False, True])
+def test_chained_single_vector_calls(hetero, bsx, cuda):
+    """A loop that alternates between two output buffers: every call adds its product into one and
+    clears the other for the call that follows (one launch per call, no clearing node)."""
+    from brainstate_b200 import _lib
+    n_pre, n_post, K = 3000, 2500, 37
+    conn, idx, _, w = make(n_pre, n_post, K, 81, hetero, cuda)
+    st = conn._struct()
+    rs = np.random.RandomState(82)
+    bufs = [torch.zeros(n_post, dtype=torch.float32, device=cuda), torch.full((n_post,), 7.0, device=cuda)]
+    stream = torch.cuda.current_stream().cuda_stream
+    for step in range(6):
+        spk = rs.random_sample(n_pre) < 0.03
+        ts = torch.from_numpy(spk).to(cuda)
+        out, nxt = bufs[step % 2], bufs[(step + 1) % 2]
+        _lib.check(bsx.bsx_event_vecmat_chained(C.byref(st), ts.data_ptr(), _lib.SPK_BOOL8, 1, out.data_ptr(),
+                                                nxt.data_ptr(), stream))
+        ref = eo.event_vecmat(spk, idx, w, n_post)
+        if hetero:
+            close(out, ref)
+        else:
+            assert np.array_equal(out.cpu().numpy(), ref)
+        assert float(nxt.abs().max()) == 0.0                  # ready for the next call
+    # packed words and a NULL next buffer; the product is ADDED to what the buffer holds
+    spk = rs.random_sample(n_pre) < 0.03
+    from brainstate_b200.event import pack_spikes
+    words = pack_spikes(torch.from_numpy(spk).to(cuda))
+    out = torch.full((n_post,), 1.0, device=cuda)
+    _lib.check(bsx.bsx_event_vecmat_chained(C.byref(st), words.data_ptr(), _lib.SPK_BITS32, 1, out.data_ptr(), None, stream))
+    close(out, eo.event_vecmat(spk, idx, w, n_post) + np.float32(1.0), scale=3)
+    # refusals: the same buffer twice; an input beyond 128 KB
+    assert bsx.bsx_event_vecmat_chained(C.byref(st), words.data_ptr(), _lib.SPK_BITS32, 1, out.data_ptr(), out.data_ptr(),
+                                        stream) == _lib.BSX_ERR_INVALID_ARG
+    big = torch.zeros((64, n_pre), dtype=torch.bool, device=cuda)
+    big_out = torch.zeros((64, n_post), dtype=torch.float32, device=cuda)
+    assert bsx.bsx_event_vecmat_chained(C.byref(st), big.data_ptr(), _lib.SPK_BOOL8, 64, big_out.data_ptr(), None,
+                                        stream) == _lib.BSX_ERR_UNSUPPORTED
