@@ -58,20 +58,25 @@ struct NeuronOut {
   bool spk;
 };
 
-__device__ __forceinline__ NeuronOut neuron_math(const bsx_lif_params_t& p, float de, float di, float ge0,
-                                                 float gi0, float V, int32_t r, uint32_t gid, int64_t step) {
-  if (p.ext_threshold && drive_hash(p.ext_seed, gid, (uint32_t)step) < p.ext_threshold)
+// MODEL 0 reads the synapse model and the background drive from the parameters; 1 and 2 fix them at
+// compile time (conductance-based / current-based, no drive), which takes the uniform branches and
+// the hash out of the loop of a kernel that is bound by instruction issue.
+template <int MODEL>
+__device__ __forceinline__ NeuronOut neuron_math_m(const bsx_lif_params_t& p, float de, float di, float ge0,
+                                                   float gi0, float V, int32_t r, uint32_t gid, int64_t step) {
+  const bool coba = MODEL == 0 ? (p.coba != 0) : MODEL == 1;
+  if (MODEL == 0 && p.ext_threshold && drive_hash(p.ext_seed, gid, (uint32_t)step) < p.ext_threshold)
     de = __fadd_rn(de, p.ext_weight);
   NeuronOut o;
   o.ge = __fadd_rn(__fmul_rn(ge0, p.decay_e), de);
   o.gi = __fadd_rn(__fmul_rn(gi0, p.decay_i), di);
   float cur;
-  if (p.coba) cur = __fadd_rn(__fmul_rn(o.ge, __fsub_rn(p.E_e, V)), __fmul_rn(o.gi, __fsub_rn(p.E_i, V)));
+  if (coba) cur = __fadd_rn(__fmul_rn(o.ge, __fsub_rn(p.E_e, V)), __fmul_rn(o.gi, __fsub_rn(p.E_i, V)));
   else cur = __fadd_rn(o.ge, o.gi);
   const float drive = __fmul_rn(p.R, __fadd_rn(cur, p.I_ext));
   const float num = __fadd_rn(__fsub_rn(p.V_rest, V), drive);
   float Vn;
-  if (p.coba) {
+  if (coba) {
     const float f = __fmul_rn(num, p.inv_tau_m);
     const float gsum = __fadd_rn(o.ge, o.gi);
     const float J = __fmul_rn(-__fadd_rn(1.0f, __fmul_rn(p.R, gsum)), p.inv_tau_m);
@@ -86,6 +91,11 @@ __device__ __forceinline__ NeuronOut neuron_math(const bsx_lif_params_t& p, floa
   o.V = o.spk ? p.V_reset : Vn;
   o.r = o.spk ? p.ref_steps : (r > 0 ? r - 1 : 0);
   return o;
+}
+
+__device__ __forceinline__ NeuronOut neuron_math(const bsx_lif_params_t& p, float de, float di, float ge0,
+                                                 float gi0, float V, int32_t r, uint32_t gid, int64_t step) {
+  return neuron_math_m<0>(p, de, di, ge0, gi0, V, r, gid, step);
 }
 
 inline int make_proj(const bsx_conn_t* c, int chunk, ProjDev* out) {

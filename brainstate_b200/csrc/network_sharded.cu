@@ -277,7 +277,7 @@ __device__ __forceinline__ int recv_list(const ShardDev& a, const LinkDev& L, in
   return (int)count;
 }
 
-template <bool RESIDENT, bool FIXED>
+template <bool RESIDENT, bool FIXED, int MODEL = 0>
 __global__ void __launch_bounds__(kShThreads, 1)
 net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t* __restrict__ raster,
                        int32_t* __restrict__ spike_counts) {
@@ -361,7 +361,7 @@ net_run_sharded_kernel(ShardDev a, LinkDev L, int steps, int64_t step0, uint32_t
         bool spk = false;
         if (i < n_loc) {
           const int32_t r = RESIDENT ? (int32_t)sref[li] : rr[k];
-          const NeuronOut o = neuron_math(a.p, I::value(de[k]), I::value(di[k]), RESIDENT ? sge[li] : ge[k],
+          const NeuronOut o = neuron_math_m<MODEL>(a.p, I::value(de[k]), I::value(di[k]), RESIDENT ? sge[li] : ge[k],
                                           RESIDENT ? sgi[li] : gi[k], RESIDENT ? sV[li] : v[k], r,
                                           (uint32_t)a.first + (uint32_t)i, step);
           if (I::nonzero(de[k])) cur_e[i] = T(0);
@@ -584,6 +584,9 @@ int bsx_net_run_sharded(const bsx_net_shard_t* net, const bsx_lif_params_t* para
                                      : (const void*)net_run_sharded_kernel<true, false>)
                             : (fixed ? (const void*)net_run_sharded_kernel<false, true>
                                      : (const void*)net_run_sharded_kernel<false, false>);
+  // state in shared memory, float sums, no background drive: the synapse model is a compile-time constant
+  if (resident && !fixed && a.p.ext_threshold == 0)
+    fn = a.p.coba ? (const void*)net_run_sharded_kernel<true, false, 1> : (const void*)net_run_sharded_kernel<true, false, 2>;
   const size_t per_neuron = (resident ? 3 * sizeof(float) + sizeof(int16_t) : 0) + sizeof(uint16_t);
   const size_t smem = (size_t)L.cap * per_neuron;
   BSX_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
