@@ -58,14 +58,15 @@ struct NeuronOut {
   bool spk;
 };
 
-// MODEL 0 reads the synapse model and the background drive from the parameters; 1 and 2 fix them at
-// compile time (conductance-based / current-based, no drive), which takes the uniform branches and
-// the hash out of the loop of a kernel that is bound by instruction issue.
+// MODEL 0 reads the synapse model and the background drive from the parameters; the others fix them
+// at compile time (1: conductance-based, no drive; 2: current-based, no drive; 3: current-based with
+// drive), which takes the uniform branches (and, without drive, the hash) out of the loop of a kernel
+// that is bound by instruction issue.
 template <int MODEL>
 __device__ __forceinline__ NeuronOut neuron_math_m(const bsx_lif_params_t& p, float de, float di, float ge0,
                                                    float gi0, float V, int32_t r, uint32_t gid, int64_t step) {
   const bool coba = MODEL == 0 ? (p.coba != 0) : MODEL == 1;
-  if (MODEL == 0 && p.ext_threshold && drive_hash(p.ext_seed, gid, (uint32_t)step) < p.ext_threshold)
+  if ((MODEL == 3 || (MODEL == 0 && p.ext_threshold)) && drive_hash(p.ext_seed, gid, (uint32_t)step) < p.ext_threshold)
     de = __fadd_rn(de, p.ext_weight);
   NeuronOut o;
   o.ge = __fadd_rn(__fmul_rn(ge0, p.decay_e), de);

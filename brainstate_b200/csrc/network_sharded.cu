@@ -584,9 +584,13 @@ int bsx_net_run_sharded(const bsx_net_shard_t* net, const bsx_lif_params_t* para
                                      : (const void*)net_run_sharded_kernel<true, false>)
                             : (fixed ? (const void*)net_run_sharded_kernel<false, true>
                                      : (const void*)net_run_sharded_kernel<false, false>);
-  // state in shared memory, float sums, no background drive: the synapse model is a compile-time constant
-  if (resident && !fixed && a.p.ext_threshold == 0)
-    fn = a.p.coba ? (const void*)net_run_sharded_kernel<true, false, 1> : (const void*)net_run_sharded_kernel<true, false, 2>;
+  // state in shared memory: the synapse model and the presence of a background drive are compile-time constants
+  if (resident) {
+    const int model = a.p.ext_threshold == 0 ? (a.p.coba ? 1 : 2) : (a.p.coba ? 0 : 3);
+    if (model == 1) fn = fixed ? (const void*)net_run_sharded_kernel<true, true, 1> : (const void*)net_run_sharded_kernel<true, false, 1>;
+    if (model == 2) fn = fixed ? (const void*)net_run_sharded_kernel<true, true, 2> : (const void*)net_run_sharded_kernel<true, false, 2>;
+    if (model == 3) fn = fixed ? (const void*)net_run_sharded_kernel<true, true, 3> : (const void*)net_run_sharded_kernel<true, false, 3>;
+  }
   const size_t per_neuron = (resident ? 3 * sizeof(float) + sizeof(int16_t) : 0) + sizeof(uint16_t);
   const size_t smem = (size_t)L.cap * per_neuron;
   BSX_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
